@@ -1,0 +1,120 @@
+// Embedding gather, fused residual-add + RMSNorm, SwiGLU.  float and bfloat16.
+//
+// Rounding points follow the reference's bf16 service so that both precisions
+// come from one template: the residual sum is made in 32-bit and rounded once
+// (acvram/engine/couches.py:427-443); the norm's variance, rsqrt and scaling are
+// 32-bit, the normalised value is rounded to the element type before the
+// multiply by the weight (acvram/engine/layers.py:625-630; kernel
+// acvram/kernels/acvram_kernels.cu:7922-7935); SiLU is 32-bit and rounded before
+// the product with `up` (acvram/kernels/acvram_kernels.cu:8441-8452).
+#include "common.cuh"
+
+// ----------------------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, T* __restrict__ out,
+                             int H, int V) {
+    const int t = blockIdx.x;
+    int tok = tokens[t];
+    tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);  // the host validates ids; never a bad address
+    const T* src = table + (size_t)tok * H;
+    T* dst = out + (size_t)t * H;
+    if ((H * sizeof(T)) % 16 == 0) {
+        const int n = H * sizeof(T) / 16;
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+ACV_API int acv_embed(const void* table, const int* tokens, void* out, int T, int H, int V, int dtype,
+                      cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (dtype == ACV_F32)
+        embed_kernel<float><<<T, 128, 0, stream>>>((const float*)table, tokens, (float*)out, H, V);
+    else if (dtype == ACV_BF16)
+        embed_kernel<bf16><<<T, 128, 0, stream>>>((const bf16*)table, tokens, (bf16*)out, H, V);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- add + RMSNorm
+// One block per row.  The (summed) row is kept in shared memory as float, so the
+// row is read once.  With `rows` given, block b norms row rows[b] into out[b] and
+// leaves x as it is (the final norm of the rows whose logits are wanted).
+template <typename T>
+__global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+                                   T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    extern __shared__ float row[];
+    __shared__ float red[32];
+    const int r_out = blockIdx.x;
+    const int r_in = rows ? rows[r_out] : r_out;
+    T* xr = x + (size_t)r_in * H;
+    const T* dr = delta ? delta + (size_t)r_in * H : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = to_f32(xr[i]);
+        if (dr) {
+            v = round_to<T>(v + to_f32(dr[i]));
+            if (!rows) xr[i] = from_f32<T>(v);
+        }
+        row[i] = v;
+        ss += v * v;
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)H + eps);
+    T* o = out + (size_t)r_out * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(round_to<T>(row[i] * rs) * w[i]);
+}
+
+template <typename T>
+static int launch_add_rmsnorm(void* x, const void* delta, const float* w, void* out, const int* rows, int n_rows,
+                              int H, float eps, cudaStream_t stream) {
+    const size_t smem = (size_t)H * sizeof(float);
+    if (smem > 200 * 1024) return ACV_ERR_SIZE;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
+    add_rmsnorm_kernel<T><<<n_rows, threads, smem, stream>>>((T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
+    return acv_launch_status();
+}
+
+ACV_API int acv_add_rmsnorm(void* x, const void* delta, const float* w, void* out, const int* rows, int n_rows, int H,
+                            float eps, int dtype, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (dtype == ACV_F32) return launch_add_rmsnorm<float>(x, delta, w, out, rows, n_rows, H, eps, stream);
+    if (dtype == ACV_BF16) return launch_add_rmsnorm<bf16>(x, delta, w, out, rows, n_rows, H, eps, stream);
+    return ACV_ERR_DTYPE;
+}
+
+// ----------------------------------------------------------------------------- SwiGLU
+// gu is [T, 2I] (gate columns then up columns, the stacked projection's output).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / I;
+        const int i = (int)(idx - t * I);
+        const float g = to_f32(gu[t * 2 * I + i]);
+        const float u = to_f32(gu[t * 2 * I + I + i]);
+        const float s = round_to<T>(g / (1.f + expf(-g)));
+        out[idx] = from_f32<T>(s * u);
+    }
+}
+
+ACV_API int acv_swiglu(const void* gu, void* out, int T, int I, int dtype, cudaStream_t stream) {
+    const size_t total = (size_t)T * I;
+    if (total == 0) return 0;
+    const int threads = 256;
+    const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
+    if (dtype == ACV_F32)
+        swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gu, (float*)out, I, total);
+    else if (dtype == ACV_BF16)
+        swiglu_kernel<bf16><<<blocks, threads, 0, stream>>>((const bf16*)gu, (bf16*)out, I, total);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}

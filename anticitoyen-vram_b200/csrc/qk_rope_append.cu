@@ -1,0 +1,108 @@
+// Fused per-head RMS norm of q and k, rotary position encoding, and the append of
+// k and v to their cache pages: one launch instead of three, and k never goes
+// back to memory unrotated.
+//
+// For each (token, head) of the stacked projection's output [T, (NH+2NKV)*D]:
+//   q, k:  inv = rsqrt(mean(v^2) + eps);  a = v*inv*w           (32-bit)
+//          out[i]        = a[i]*cos[i] - a[i+R/2]*sin[i]         i < R/2
+//          out[i + R/2]  = a[i+R/2]*cos[i] + a[i]*sin[i]
+//          one rounding at the end; dimensions >= R (partial rotary) are only normed
+//          (the reference's fused kernel, acvram/kernels/acvram_kernels.cu:4397-4430)
+//   q:     written back in place
+//   k, v:  written to page[block_table[seq][pos / page]] at row pos % page; a page
+//          index < 0 writes nothing (the reference's padding-row sentinel,
+//          acvram/kernels/acvram_kernels.cu:4496)
+// Pages are [num_pages, NKV, page_size, D].  Each step is optional (null weight,
+// null table, null pages), so that another position encoding can run between a
+// norm-only and an append-only launch.
+#include "common.cuh"
+
+#define QRA_WARPS 8
+
+template <typename T>
+__global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, int row_stride, int NH, int NKV, int D,
+                                           const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                           const float* __restrict__ cos_sin, int rot, int table_rows,
+                                           const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                           const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pages,
+                                           T* __restrict__ v_pages, int page_size, int num_pages) {
+    extern __shared__ float sm_all[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * QRA_WARPS + warp;
+    const int t = blockIdx.x;
+    if (head >= NH + 2 * NKV) return;
+    float* sm = sm_all + warp * D;
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * D;
+    const bool is_q = head < NH;
+    const bool is_k = !is_q && head < NH + NKV;
+    const bool is_v = !is_q && !is_k;
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    int pos = positions[t];
+
+    float ss = 0.f;
+    for (int e = lane; e < D; e += 32) {
+        const float v = to_f32(src[e]);
+        sm[e] = v;
+        ss += v * v;
+    }
+    if (w) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+        __syncwarp();
+        for (int e = lane; e < D; e += 32) sm[e] = sm[e] * inv * w[e];
+    }
+    __syncwarp();
+
+    T* dst = nullptr;
+    if (is_q) {
+        dst = src;
+    } else if (k_pages) {
+        const int seq = seq_of_token[t];
+        const int pg = block_table[(size_t)seq * bt_stride + pos / page_size];
+        if (pg >= 0 && pg < num_pages) {
+            const int kvh = is_k ? head - NH : head - NH - NKV;
+            T* base = is_k ? k_pages : v_pages;
+            dst = base + (((size_t)pg * NKV + kvh) * page_size + (pos % page_size)) * D;
+        }
+    } else if (is_k) {
+        dst = src;
+    }
+    if (!dst) return;
+
+    const bool rotate = cos_sin && !is_v && pos >= 0 && pos < table_rows;
+    const int half = rot >> 1;
+    const float* cs = cos_sin ? cos_sin + (size_t)(rotate ? pos : 0) * rot : nullptr;
+    for (int e = lane; e < D; e += 32) {
+        float o = sm[e];
+        if (rotate && e < rot) {
+            if (e < half)
+                o = sm[e] * cs[e] - sm[e + half] * cs[half + e];
+            else
+                o = sm[e] * cs[e - half] + sm[e - half] * cs[e];
+        }
+        dst[e] = from_f32<T>(o);
+    }
+}
+
+ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, int NKV, int D, const float* q_w,
+                                    const float* k_w, float eps, const float* cos_sin, int rot, int table_rows,
+                                    const int* positions, const int* seq_of_token, const int* block_table,
+                                    int bt_stride, void* k_pages, void* v_pages, int page_size, int num_pages,
+                                    int dtype, cudaStream_t stream) {
+    if (T <= 0) return 0;
+    if (D <= 0 || D > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
+    const int heads = NH + 2 * NKV;
+    dim3 grid(T, (heads + QRA_WARPS - 1) / QRA_WARPS);
+    const size_t smem = (size_t)QRA_WARPS * D * sizeof(float);
+    if (dtype == ACV_F32)
+        qk_norm_rope_append_kernel<float><<<grid, QRA_WARPS * 32, smem, stream>>>(
+            (float*)qkv, row_stride, NH, NKV, D, q_w, k_w, eps, cos_sin, rot, table_rows, positions, seq_of_token,
+            block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size, num_pages);
+    else if (dtype == ACV_BF16)
+        qk_norm_rope_append_kernel<bf16><<<grid, QRA_WARPS * 32, smem, stream>>>(
+            (bf16*)qkv, row_stride, NH, NKV, D, q_w, k_w, eps, cos_sin, rot, table_rows, positions, seq_of_token,
+            block_table, bt_stride, (bf16*)k_pages, (bf16*)v_pages, page_size, num_pages);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}

@@ -1,0 +1,275 @@
+// On-device sampling over float32 logits [rows, V]: penalties, greedy argmax,
+// temperature, top-k, min-p, top-p and the draw, one block per row.
+//
+// Order and meaning follow the reference (acvram/engine/sampler.py:195-256):
+// penalties on the raw logits; scaled = logit / max(T, 1e-5); top-k keeps the
+// values >= the k-th largest; min-p drops p < min_p * p_max; top-p drops a token
+// when the mass of the tokens before it in descending order exceeds top_p (the
+// token that crosses stays, so the set is never empty); the draw is from the
+// softmax of what is left.  A row with temperature <= 0 takes the argmax.
+//
+// Nothing is sorted: the k-th value and the top-p cut are found by bisection on
+// an order-preserving 32-bit key of the float, 32 counting passes each over the
+// row (which stays in L2).  The reference draws with torch.multinomial from a
+// global generator; here each row has a counter-based generator, Philox-4x32-10
+// keyed by the request's seed with the request's step as counter, so a draw does
+// not depend on what else is in the batch.  The draw is the inverse CDF over the
+// kept tokens in index order.
+#include "common.cuh"
+
+#define SMP_THREADS 1024
+
+__device__ __forceinline__ uint32_t order_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ float philox_uniform(uint64_t seed, uint64_t counter) {
+    const uint32_t M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+    uint32_t c0 = (uint32_t)counter, c1 = (uint32_t)(counter >> 32), c2 = 0, c3 = 0;
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+    for (int r = 0; r < 10; ++r) {
+        const uint32_t hi0 = __umulhi(M0, c0), lo0 = M0 * c0;
+        const uint32_t hi1 = __umulhi(M1, c2), lo1 = M1 * c2;
+        const uint32_t n0 = hi1 ^ c1 ^ k0, n1 = lo1, n2 = hi0 ^ c3 ^ k1, n3 = lo0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += W0; k1 += W1;
+    }
+    return ((float)c0 + 0.5f) * (1.0f / 4294967296.0f);
+}
+
+// block-wide reductions over SMP_THREADS threads; all threads get the result
+__device__ __forceinline__ float block_reduce_sum(float v, float* red) { return block_sum(v, red); }
+
+__device__ __forceinline__ float block_reduce_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = lane < nwarp ? red[lane] : -INFINITY;
+    return warp_max(t);
+}
+
+__device__ __forceinline__ int block_reduce_sum_int(int v, int* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    int t = lane < nwarp ? red[lane] : 0;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    return t;
+}
+
+// argmax with the lowest index among equal values (torch.argmax's answer)
+__device__ __forceinline__ int block_argmax(const float* row, int V, float inv_temp, float* redf, int* redi) {
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float v = row[i] * inv_temp;
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    __syncthreads();
+    if (lane == 0) { redf[warp] = best; redi[warp] = bi; }
+    __syncthreads();
+    best = lane < nwarp ? redf[lane] : -INFINITY;
+    bi = lane < nwarp ? redi[lane] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    return bi;
+}
+
+__global__ void __launch_bounds__(SMP_THREADS)
+argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+    __shared__ float redf[32];
+    __shared__ int redi[32];
+    const int bi = block_argmax(logits + (size_t)blockIdx.x * ld, V, 1.f, redf, redi);
+    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+}
+
+ACV_API int acv_argmax(const float* logits, int ld, int rows, int V, int* out, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0) return ACV_ERR_SIZE;
+    argmax_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, ld, V, out);
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- penalties
+// One thread per (row, distinct token already seen, its count).
+__global__ void penalties_kernel(float* __restrict__ logits, int ld, int V, const int* __restrict__ pen_row,
+                                 const int* __restrict__ pen_token, const int* __restrict__ pen_count, int n,
+                                 const float* __restrict__ repetition, const float* __restrict__ presence,
+                                 const float* __restrict__ frequency) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int r = pen_row[i], tok = pen_token[i];
+    if (tok < 0 || tok >= V) return;
+    float v = logits[(size_t)r * ld + tok];
+    const float rep = repetition[r];
+    if (rep != 1.f) v = v > 0.f ? v / rep : v * rep;
+    v -= presence[r];
+    v -= frequency[r] * (float)pen_count[i];
+    logits[(size_t)r * ld + tok] = v;
+}
+
+ACV_API int acv_apply_penalties(float* logits, int ld, int V, const int* pen_row, const int* pen_token,
+                                const int* pen_count, int n, const float* repetition, const float* presence,
+                                const float* frequency, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    penalties_kernel<<<(n + 255) / 256, 256, 0, stream>>>(logits, ld, V, pen_row, pen_token, pen_count, n, repetition,
+                                                          presence, frequency);
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- sample
+__global__ void __launch_bounds__(SMP_THREADS)
+sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __restrict__ temperature,
+              const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+              const unsigned long long* __restrict__ seed, const unsigned long long* __restrict__ counter,
+              int* __restrict__ out_token, float* __restrict__ out_logprob) {
+    __shared__ float redf[32];
+    __shared__ int redi[32];
+    __shared__ float scan[SMP_THREADS];
+    const int r = blockIdx.x;
+    const float* row = logits + (size_t)r * ld;
+    const float temp = temperature[r];
+
+    if (temp <= 0.f) {  // greedy row
+        const int bi = block_argmax(row, V, 1.f, redf, redi);
+        float z = 0.f;
+        if (out_logprob) {
+            const float mx = row[bi];
+            for (int i = threadIdx.x; i < V; i += blockDim.x) z += expf(row[i] - mx);
+            z = block_reduce_sum(z, redf);
+        }
+        if (threadIdx.x == 0) {
+            out_token[r] = bi;
+            if (out_logprob) out_logprob[r] = -logf(z);
+        }
+        return;
+    }
+
+    const float inv_t = 1.f / fmaxf(temp, 1e-5f);
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i] * inv_t);
+    mx = block_reduce_max(mx, redf);
+
+    uint32_t cut = 0;  // keys >= cut are kept
+    const int k = top_k[r];
+    if (k > 0 && k < V) {
+        uint32_t prefix = 0;
+        for (int b = 31; b >= 0; --b) {
+            const uint32_t cand = prefix | (1u << b);
+            int cnt = 0;
+            for (int i = threadIdx.x; i < V; i += blockDim.x) cnt += order_key(row[i] * inv_t) >= cand;
+            cnt = block_reduce_sum_int(cnt, redi);
+            if (cnt >= k) prefix = cand;
+        }
+        cut = prefix;
+    }
+    const float mp = min_p[r];
+    const bool use_minp = mp > 0.f;
+    // kept(i): key >= cut and (no min-p or exp(s - max) >= min_p)
+    const float tp = top_p[r];
+    if (tp > 0.f && tp < 1.f) {
+        float z = 0.f;
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float s = row[i] * inv_t;
+            const float e = expf(s - mx);
+            if (order_key(s) >= cut && !(use_minp && e < mp)) z += e;
+        }
+        z = block_reduce_sum(z, redf);
+        const float limit = tp * z;
+        uint32_t prefix = 0;  // the largest key value t with mass(key > t) > limit
+        for (int b = 31; b >= 0; --b) {
+            const uint32_t cand = prefix | (1u << b);
+            float mass = 0.f;
+            for (int i = threadIdx.x; i < V; i += blockDim.x) {
+                const float s = row[i] * inv_t;
+                const uint32_t key = order_key(s);
+                const float e = expf(s - mx);
+                if (key > cand && key >= cut && !(use_minp && e < mp)) mass += e;
+            }
+            mass = block_reduce_sum(mass, redf);
+            if (mass > limit) prefix = cand;
+        }
+        const uint32_t cut_p = prefix + 1u;
+        cut = cut_p > cut ? cut_p : cut;
+    }
+
+    // inverse CDF in index order: each thread owns a contiguous range of indices
+    const int chunk = (V + blockDim.x - 1) / blockDim.x;
+    const int lo = threadIdx.x * chunk, hi = min(V, lo + chunk);
+    float local = 0.f;
+    for (int i = lo; i < hi; ++i) {
+        const float s = row[i] * inv_t;
+        const float e = expf(s - mx);
+        if (order_key(s) >= cut && !(use_minp && e < mp)) local += e;
+    }
+    scan[threadIdx.x] = local;
+    __syncthreads();
+    __shared__ float total_s;
+    __shared__ int owner_s;
+    __shared__ float before_s;
+    if (threadIdx.x == 0) {
+        float run = 0.f;
+        for (int t = 0; t < (int)blockDim.x; ++t) run += scan[t];
+        const float u = philox_uniform(seed[r], counter[r]);
+        const float target = u * run;
+        float acc = 0.f;
+        int owner = -1;
+        int last_nonempty = 0;
+        for (int t = 0; t < (int)blockDim.x; ++t) {
+            if (scan[t] > 0.f) last_nonempty = t;
+            if (owner < 0 && scan[t] > 0.f && acc + scan[t] >= target) { owner = t; before_s = acc; }
+            if (owner < 0) acc += scan[t];
+        }
+        if (owner < 0) { owner = last_nonempty; before_s = acc - scan[last_nonempty]; }
+        owner_s = owner;
+        total_s = run;
+        redf[0] = target;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x == owner_s) {
+        const float target = redf[0];
+        float acc = before_s;
+        int pick = -1, last_kept = -1;
+        for (int i = lo; i < hi; ++i) {
+            const float s = row[i] * inv_t;
+            const float e = expf(s - mx);
+            if (order_key(s) >= cut && !(use_minp && e < mp)) {
+                last_kept = i;
+                acc += e;
+                if (acc >= target) { pick = i; break; }
+            }
+        }
+        if (pick < 0) pick = last_kept;
+        out_token[r] = pick;
+        if (out_logprob) out_logprob[r] = (row[pick] * inv_t - mx) - logf(total_s);
+    }
+}
+
+ACV_API int acv_sample(const float* logits, int ld, int rows, int V, const float* temperature, const int* top_k,
+                       const float* top_p, const float* min_p, const unsigned long long* seed,
+                       const unsigned long long* counter, int* out_token, float* out_logprob, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0) return ACV_ERR_SIZE;
+    sample_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p, seed, counter,
+                                                    out_token, out_logprob);
+    return acv_launch_status();
+}

@@ -1,0 +1,80 @@
+"""The step function: run a batch of (request, its next tokens) from the cache.
+
+``ModelRunner`` owns the model, the cache manager and the cache storage.  One
+call of ``step`` reserves pages for the tokens it is given, runs exactly those
+tokens as one batch through every scheduled layer (reading older keys and values
+from the pages that earlier steps left), and returns float32 logits at the wanted
+places.  Generation (the scheduler) and trace replay both go through this call.
+"""
+
+from __future__ import annotations
+
+from typing import Hashable, Sequence
+
+import torch
+
+from ..cache import CacheManager, CacheStorage
+from ..parts import Runtime
+from .batch import BatchBuilder, StepContext, StepEntry
+
+
+class ModelRunner:
+    def __init__(self, model, page_size: int, num_pages: int, max_requests: int) -> None:
+        if model.rt is None:
+            raise ValueError("the model has no weights loaded")
+        rt: Runtime = model.rt
+        self.model = model
+        self.rt = rt
+        self.manager = CacheManager(model.cache_plan(), page_size, num_pages, max_requests)
+        self.storage = CacheStorage(self.manager, rt.device, rt.dtype)
+        self.builder = BatchBuilder(self.manager, rt.device, model.plan.vocab_size, model.plan.max_positions)
+        self.steps = 0
+
+    # ------------------------------------------------------------------ requests
+    def admit(self, request: Hashable) -> None:
+        for group, slot in self.manager.admit(request).items():
+            self.storage.zero_state(group, slot)
+
+    def release(self, request: Hashable) -> None:
+        self.manager.release(request)
+
+    def length(self, request: Hashable) -> int:
+        return self.manager.lengths[request]
+
+    # ------------------------------------------------------------------ the step
+    def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
+        """Admit new requests, reserve pages for the step's tokens, build its context."""
+        m = self.manager
+        starts = []
+        grown = []
+        try:
+            for e in entries:
+                if e.request not in m.lengths:
+                    self.admit(e.request)
+                start = m.lengths[e.request]
+                m.grow(e.request, start + len(e.tokens))
+                grown.append(e.request)
+                starts.append(start)
+        except Exception:
+            # a step that cannot be held leaves the lengths as they were; pages already
+            # taken stay with their requests (they are within what those requests will need)
+            for r, s in zip(grown, starts):
+                m.lengths[r] = s
+            raise
+        return self.builder.build(entries, starts)
+
+    @torch.no_grad()
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Logits float32 [wanted, vocab] in the order of the entries and of their ``want``."""
+        if not entries:
+            return torch.empty((0, self.model.plan.vocab_size), device=self.rt.device, dtype=torch.float32)
+        ctx = self.prepare(entries)
+        if self.rt.device.type == "cuda":
+            with torch.cuda.device(self.rt.device):
+                logits = self.model.forward(ctx, self.storage)
+        else:  # only reachable with the kernels replaced by a test: the kernels themselves refuse CPU tensors
+            logits = self.model.forward(ctx, self.storage)
+        for e in entries:
+            self.manager.trim(e.request)
+        self.steps += 1
+        return logits

@@ -1,0 +1,231 @@
+"""Python faces of the CUDA kernels (ctypes over the C entry points of ``csrc/``).
+
+Each function takes torch CUDA tensors, checks what the kernel assumes (device,
+dtype, contiguity) and launches on the current stream.  There is no other
+implementation behind these names: without the compiled library, or without a
+CUDA device, the first call raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+
+import torch
+
+from .build import BuildError, library_path
+
+F32, BF16 = 0, 1
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+_ERRORS = {
+    -2: "unsupported element type",
+    -3: "a size is outside what this kernel takes",
+    -4: "a pointer or stride is not aligned as this kernel needs",
+    -5: "scratch memory is too small",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib = None
+_cudart_err = None
+
+
+def library() -> ctypes.CDLL:
+    """Load (building on first use) the kernel library; raise if it cannot be had."""
+    global _lib
+    if _lib is None:
+        try:
+            path = library_path()
+        except BuildError as exc:
+            raise KernelError(f"the CUDA kernels of acvram_b200 could not be built: {exc}") from exc
+        lib = ctypes.CDLL(path)
+        _declare(lib)
+        _lib = lib
+    return _lib
+
+
+def loaded_library_path() -> str | None:
+    return None if _lib is None else _lib._name
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    P, I, F = c_void_p, c_int, c_float
+    sig = {
+        "acv_embed": [P, P, P, I, I, I, I, P],
+        "acv_add_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
+        "acv_swiglu": [P, P, I, I, I, P],
+        "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
+        "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+        "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
+        "acv_argmax": [P, I, I, I, P, P],
+        "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
+        "acv_sample": [P, I, I, I, P, P, P, P, P, P, P, P, P],
+    }
+    for name, args in sig.items():
+        fn = getattr(lib, name)
+        fn.argtypes = args
+        fn.restype = c_int
+
+
+def _check(code: int, name: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{name}: {_ERRORS.get(code, f'refused with code {code}')}")
+    raise KernelError(f"{name}: CUDA error {code} ({torch.cuda.cudart().cudaGetErrorString(code) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else 'see cudaError_t'})")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: torch.Tensor | None):
+    return None if t is None else t.data_ptr()
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DT[dtype]
+    except KeyError:
+        raise KernelError(f"element type {dtype} is not built (float32 and bfloat16 are)") from None
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("acvram_b200 kernels run on a CUDA device only; got a CPU tensor")
+
+
+# ----------------------------------------------------------------------------- elementwise
+def embed(table: torch.Tensor, tokens: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[t] = table[tokens[t]].  table [V, H]; tokens int32 [T]; out [T, H]."""
+    _need_cuda(table, tokens, out)
+    T, H = out.shape
+    _check(library().acv_embed(_p(table), _p(tokens), _p(out), T, H, table.shape[0], dtype_code(table.dtype),
+                               _stream()), "embed")
+    return out
+
+
+def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float, out: torch.Tensor,
+                rows: torch.Tensor | None = None) -> torch.Tensor:
+    """x += delta (in place, when delta is given); out = rmsnorm(x) * weight.
+
+    With ``rows`` (int32 [R]) only those rows are normed, into out[0..R), and x is
+    left as it is.  weight is float32 [H]."""
+    _need_cuda(x, out, weight)
+    n = out.shape[0] if rows is not None else x.shape[0]
+    _check(library().acv_add_rmsnorm(_p(x), _p(delta), _p(weight), _p(out), _p(rows), n, x.shape[-1], eps,
+                                     dtype_code(x.dtype), _stream()), "add_rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:].  gate_up [T, 2I] contiguous."""
+    _need_cuda(gate_up, out)
+    T, I = out.shape
+    _check(library().acv_swiglu(_p(gate_up), _p(out), T, I, dtype_code(out.dtype), _stream()), "swiglu")
+    return out
+
+
+# ----------------------------------------------------------------------------- attention
+def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                        q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
+                        cos_sin: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
+                        block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
+                        v_pages: torch.Tensor | None) -> None:
+    """Per-head norm, rotation and cache append over the stacked projection qkv [T, (NH+2NKV)*D], in place.
+
+    cos_sin float32 [positions, R] (cos of R/2 angles, then sin); pages [NP, NKV, page, D]."""
+    _need_cuda(qkv)
+    T = qkv.shape[0]
+    rot = cos_sin.shape[1] if cos_sin is not None else 0
+    rows = cos_sin.shape[0] if cos_sin is not None else 0
+    page = k_pages.shape[2] if k_pages is not None else 1
+    n_pages = k_pages.shape[0] if k_pages is not None else 0
+    bts = block_table.stride(0) if block_table is not None else 0
+    _check(library().acv_qk_norm_rope_append(
+        _p(qkv), qkv.stride(0), T, num_heads, num_kv_heads, head_dim, _p(q_weight), _p(k_weight), eps, _p(cos_sin),
+        rot, rows, _p(positions), _p(seq_of_token), _p(block_table), bts, _p(k_pages), _p(v_pages), page, n_pages,
+        dtype_code(qkv.dtype), _stream()), "qk_norm_rope_append")
+
+
+def attention_generic(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                      positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
+                      num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+    """Paged causal attention for every token of the step.  q: rows of num_heads*head_dim (row stride free)."""
+    _need_cuda(q, out, k_pages)
+    T = q.shape[0]
+    _check(library().acv_attention_generic(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),
+        _p(block_table), block_table.stride(0), T, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
+        k_pages.shape[0], scale, window, dtype_code(q.dtype), _stream()), "attention_generic")
+    return out
+
+
+# ----------------------------------------------------------------------------- matrix products
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M,N] = a[M,K] @ w[N,K]^T with 32-bit accumulation on the CUDA cores."""
+    _need_cuda(a, w, out)
+    M, K = a.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape[0] != M or out.shape[1] != N or a.dtype != w.dtype:
+        raise KernelError(f"gemm_simt: shapes {tuple(a.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gemm_simt: innermost strides must be 1")
+    _check(library().acv_gemm_simt(_p(a), a.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
+                                   dtype_code(a.dtype), dtype_code(out.dtype), _stream()), "gemm_simt")
+    return out
+
+
+# ----------------------------------------------------------------------------- sampling
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[r] = argmax(logits[r]) (lowest index among equals).  logits float32 [R, V]; out int32 [R]."""
+    _need_cuda(logits, out)
+    R, V = logits.shape
+    _check(library().acv_argmax(_p(logits), logits.stride(0), R, V, _p(out), _stream()), "argmax")
+    return out
+
+
+def apply_penalties(logits: torch.Tensor, pen_row: torch.Tensor, pen_token: torch.Tensor, pen_count: torch.Tensor,
+                    repetition: torch.Tensor, presence: torch.Tensor, frequency: torch.Tensor) -> None:
+    _need_cuda(logits, pen_row)
+    _check(library().acv_apply_penalties(_p(logits), logits.stride(0), logits.shape[1], _p(pen_row), _p(pen_token),
+                                         _p(pen_count), pen_row.numel(), _p(repetition), _p(presence),
+                                         _p(frequency), _stream()), "apply_penalties")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           min_p: torch.Tensor, seed: torch.Tensor, counter: torch.Tensor, out_token: torch.Tensor,
+           out_logprob: torch.Tensor | None = None) -> torch.Tensor:
+    """One token per row.  seed, counter: int64 [R] (read as unsigned)."""
+    _need_cuda(logits, out_token)
+    R, V = logits.shape
+    _check(library().acv_sample(_p(logits), logits.stride(0), R, V, _p(temperature), _p(top_k), _p(top_p), _p(min_p),
+                                _p(seed), _p(counter), _p(out_token), _p(out_logprob), _stream()), "sample")
+    return out_token
+
+
+# ----------------------------------------------------------------------------- dispatch by shape
+def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
+              block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+              window: int = 0) -> torch.Tensor:
+    """Attention of every token of the step over its request's pages.
+
+    ``qkv`` is the stacked projection after norm and rotation (queries are its first
+    num_heads*head_dim columns); ``ctx`` is the step's StepContext."""
+    return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
+                             num_kv_heads, head_dim, scale, window)
+
+
+def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out = x @ w^T in bfloat16 with float accumulation."""
+    return torch.mm(x, w.t(), out=out)
+
+
+def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out (float32) = x @ w^T from bfloat16 operands, accumulated in float32."""
+    return gemm_simt(x, w, out)

@@ -1,0 +1,45 @@
+"""Position encodings."""
+
+from __future__ import annotations
+
+import torch
+
+from .base import PositionEncoding, Runtime
+from .registry import register
+
+
+@register("position", "rotary")
+class Rotary(PositionEncoding):
+    """Rotate-half rotary positions over the first ``dim`` elements of a head.
+
+    inv_freq[i] = 1 / theta^(2i/dim); angle = position * inv_freq; pairs are
+    (i, i + dim/2) (acvram/engine/layers.py:727-730, 934-936, 1006-1009).  The table
+    holds, for each position, cos of the dim/2 angles and then their sin, in
+    float32: the reference rounds its tables to the model's type
+    (acvram/engine/layers.py:829-830); here angles, cos and sin stay 32-bit in both
+    precisions.  The attention kernel reads the table itself."""
+
+    def __init__(self, hidden_size: int, dim: int, theta: float, max_positions: int) -> None:
+        if dim % 2:
+            raise ValueError(f"rotary dim {dim} must be even")
+        self.dim, self.theta, self.max_positions = int(dim), float(theta), int(max_positions)
+        self.table: torch.Tensor | None = None
+
+    def load(self, tensors, rt: Runtime) -> None:
+        inv = 1.0 / (self.theta ** (torch.arange(0, self.dim, 2, dtype=torch.float32) / self.dim))
+        ang = torch.outer(torch.arange(self.max_positions, dtype=torch.float32), inv)
+        self.table = torch.cat((ang.cos(), ang.sin()), dim=-1).contiguous().to(rt.device)
+
+    def rotary_table(self):
+        return self.table
+
+
+@register("position", "none")
+class NoPosition(PositionEncoding):
+    """No position signal (the mixer sees order through causality only)."""
+
+    def __init__(self, hidden_size: int) -> None:
+        pass
+
+    def apply(self, q, k, ctx) -> None:
+        return None
