@@ -268,12 +268,21 @@ class CacheManager:
         return slots
 
     def grow(self, request, length: int) -> None:
-        """Reserve pages so that positions [0, length) exist; all groups or none."""
+        """Reserve pages so that positions [0, length) exist; all groups or none.
+
+        Reserving does not move the request's length: ``advance`` does, once the
+        tokens have run.  Growing to a length already reserved takes nothing."""
         if not self.can_grow(request, length):
             raise OutOfPages(f"request {request!r} cannot grow to {length} tokens: free {self.free_pages()}")
         for g in self.paged_groups:
             g.grow(request, length)
-        self.lengths[request] = max(self.lengths[request], length)
+
+    def advance(self, request, length: int) -> None:
+        """The request now holds ``length`` tokens in its pages."""
+        for g in self.paged_groups:
+            if g.pages_for(length) > len(g.tables[request]):
+                raise CacheAccountingError(f"request {request!r} advanced to {length} tokens beyond its pages")
+        self.lengths[request] = length
 
     def trim(self, request) -> int:
         """After a step: release what every window has passed.  Returns pages freed."""

@@ -32,8 +32,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ requests
     def admit(self, request: Hashable) -> None:
-        for group, slot in self.manager.admit(request).items():
-            self.storage.zero_state(group, slot)
+        self.manager.admit(request)
 
     def release(self, request: Hashable) -> None:
         self.manager.release(request)
@@ -46,21 +45,16 @@ class ModelRunner:
         """Admit new requests, reserve pages for the step's tokens, build its context."""
         m = self.manager
         starts = []
-        grown = []
-        try:
-            for e in entries:
-                if e.request not in m.lengths:
-                    self.admit(e.request)
-                start = m.lengths[e.request]
-                m.grow(e.request, start + len(e.tokens))
-                grown.append(e.request)
-                starts.append(start)
-        except Exception:
-            # a step that cannot be held leaves the lengths as they were; pages already
-            # taken stay with their requests (they are within what those requests will need)
-            for r, s in zip(grown, starts):
-                m.lengths[r] = s
-            raise
+        for e in entries:
+            if e.request not in m.lengths:
+                self.admit(e.request)
+            start = m.lengths[e.request]
+            if start == 0:     # a request's first step (also after a preemption): its state starts at zero
+                for gi, g in enumerate(m.groups):
+                    if g.need.kind == "state":
+                        self.storage.zero_state(gi, g.slot_of[e.request])
+            m.grow(e.request, start + len(e.tokens))   # takes nothing if the scheduler reserved already
+            starts.append(start)
         return self.builder.build(entries, starts)
 
     @torch.no_grad()
@@ -74,7 +68,8 @@ class ModelRunner:
                 logits = self.model.forward(ctx, self.storage)
         else:  # only reachable with the kernels replaced by a test: the kernels themselves refuse CPU tensors
             logits = self.model.forward(ctx, self.storage)
-        for e in entries:
+        for e, kv in zip(entries, ctx.kv_lens):
+            self.manager.advance(e.request, kv)
             self.manager.trim(e.request)
         self.steps += 1
         return logits

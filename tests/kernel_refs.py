@@ -94,7 +94,7 @@ def attention_generic(q, out, k_pages, v_pages, positions, seq_of_token, block_t
         p = int(positions[t])
         seq = int(seq_of_token[t])
         lo = max(0, p - window + 1) if window > 0 else 0
-        js = torch.arange(lo, p + 1)
+        js = torch.arange(lo, p + 1, device=q.device)
         pages = block_table[seq].long()[js // page]
         keep = pages >= 0
         js, pages = js[keep], pages[keep]

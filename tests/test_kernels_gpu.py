@@ -1,0 +1,228 @@
+"""Each CUDA kernel alone against its plain PyTorch reference, at sizes other than the engine's."""
+
+from __future__ import annotations
+
+import pytest
+import torch
+
+import kernel_refs as ref
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == torch.float32 else dict(rtol=1.6e-2, atol=1.6e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from acvram_b200.kernels import ops
+    ops.library()
+    return ops
+
+
+def rnd(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(*shape, device="cuda", generator=g) * scale).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,V,T", [(72, 331, 9), (4096, 1000, 3), (50, 77, 1)])
+def test_embed(ops, dtype, H, V, T):
+    table = rnd(V, H, dtype=dtype)
+    tok = torch.randint(0, V, (T,), device="cuda", dtype=torch.int32)
+    out = torch.empty(T, H, device="cuda", dtype=dtype)
+    ops.embed(table, tok, out)
+    assert torch.equal(out, table[tok.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,H,eps", [(5, 72, 1e-6), (3, 4096, 1e-5), (2, 5120, 1e-6), (1, 13000, 1e-5), (17, 50, 1e-3)])
+def test_add_rmsnorm(ops, dtype, T, H, eps):
+    x = rnd(T, H, dtype=dtype, seed=1)
+    d = rnd(T, H, dtype=dtype, seed=2)
+    w = 1 + 0.1 * rnd(H, seed=3)
+    # with the residual sum
+    x1, x2 = x.clone(), x.clone()
+    o1 = ops.add_rmsnorm(x1, d, w, eps, torch.empty_like(x))
+    o2 = ref.add_rmsnorm(x2, d, w, eps, torch.empty_like(x))
+    torch.testing.assert_close(x1, x2, **tol(dtype))
+    torch.testing.assert_close(o1, o2, **tol(dtype))
+    # without, and on chosen rows only
+    rows = torch.tensor([T - 1, 0], device="cuda", dtype=torch.int32)
+    x3 = x.clone()
+    o3 = ops.add_rmsnorm(x3, d, w, eps, torch.empty(2, H, device="cuda", dtype=dtype), rows)
+    o4 = ref.add_rmsnorm(x.clone(), d, w, eps, torch.empty(2, H, device="cuda", dtype=dtype), rows)
+    assert torch.equal(x3, x), "the rows form must leave x as it is"
+    torch.testing.assert_close(o3, o4, **tol(dtype))
+    o5 = ops.add_rmsnorm(x.clone(), None, w, eps, torch.empty_like(x))
+    o6 = ref.add_rmsnorm(x.clone(), None, w, eps, torch.empty_like(x))
+    torch.testing.assert_close(o5, o6, **tol(dtype))
+
+
+def test_rmsnorm_breaking_arm(ops):
+    """The judge can see a fault: a wrong eps moves the result beyond the tolerance."""
+    x = rnd(4, 96, scale=0.01, seed=4)
+    w = torch.ones(96, device="cuda")
+    good = ops.add_rmsnorm(x.clone(), None, w, 1e-6, torch.empty_like(x))
+    bad = ref.add_rmsnorm(x.clone(), None, w, 1e-4, torch.empty_like(x))
+    assert (good - bad).abs().max() > 1e-2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,I", [(7, 176), (2, 12288), (1, 5), (33, 1000)])
+def test_swiglu(ops, dtype, T, I):
+    gu = rnd(T, 2 * I, dtype=dtype, scale=3.0, seed=5)
+    gu[0, 0] = 80.0   # extremes: exp(-g) under- and overflows
+    gu[0, 1] = -80.0
+    o1 = ops.swiglu(gu, torch.empty(T, I, device="cuda", dtype=dtype))
+    o2 = ref.swiglu(gu, torch.empty(T, I, device="cuda", dtype=dtype))
+    torch.testing.assert_close(o1, o2, **tol(dtype))
+    assert torch.isfinite(o1.float()).all()
+
+
+def _paged_setup(B, lens, NKV, D, page, dtype, n_pages, seed, shuffle=True):
+    """Random block tables over a shuffled pool; returns (k_pages, v_pages, table[B, W])."""
+    g = torch.Generator().manual_seed(seed)
+    W = max((l + page - 1) // page for l in lens)
+    perm = torch.randperm(n_pages, generator=g) if shuffle else torch.arange(n_pages)
+    table = torch.full((B, W), -1, dtype=torch.int32)
+    used = 0
+    for b, l in enumerate(lens):
+        n = (l + page - 1) // page
+        table[b, :n] = perm[used:used + n].to(torch.int32)
+        used += n
+    assert used <= n_pages
+    kp = torch.zeros(n_pages, NKV, page, D, device="cuda", dtype=dtype)
+    vp = torch.zeros_like(kp)
+    return kp, vp, table.cuda()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("NH,NKV,D,rot,page", [(5, 1, 48, 48, 16), (6, 2, 32, 32, 8), (8, 8, 64, 32, 4), (4, 2, 128, 128, 16),
+                                              (3, 3, 16, 16, 32)])
+def test_qk_norm_rope_append(ops, dtype, NH, NKV, D, rot, page):
+    lens = [19, 3, 40]
+    q_lens = [5, 3, 1]   # the last tokens of each request are this step's
+    B = len(lens)
+    kp, vp, table = _paged_setup(B, lens, NKV, D, page, dtype, 16, seed=7)
+    kp2, vp2 = kp.clone(), vp.clone()
+    pos = torch.cat([torch.arange(l - q, l) for l, q in zip(lens, q_lens)]).to(torch.int32).cuda()
+    seq = torch.cat([torch.full((q,), b) for b, q in enumerate(q_lens)]).to(torch.int32).cuda()
+    T = pos.numel()
+    qkv = rnd(T, (NH + 2 * NKV) * D, dtype=dtype, seed=8)
+    qw, kw = 1 + 0.1 * rnd(D, seed=9), 1 + 0.1 * rnd(D, seed=10)
+    inv = 1.0 / (10000.0 ** (torch.arange(0, rot, 2, dtype=torch.float32) / rot))
+    ang = torch.outer(torch.arange(64, dtype=torch.float32), inv)
+    cs = torch.cat((ang.cos(), ang.sin()), -1).cuda()
+    a, b = qkv.clone(), qkv.clone()
+    ops.qk_norm_rope_append(a, NH, NKV, D, qw, kw, 1e-6, cs, pos, seq, table, kp, vp)
+    ref.qk_norm_rope_append(b, NH, NKV, D, qw, kw, 1e-6, cs, pos, seq, table, kp2, vp2)
+    torch.testing.assert_close(a[:, :NH * D], b[:, :NH * D], **tol(dtype))
+    torch.testing.assert_close(kp, kp2, **tol(dtype))
+    torch.testing.assert_close(vp, vp2, **tol(dtype))
+    # steps alone: norm only (no table, no pages), then append only
+    c, d = qkv.clone(), qkv.clone()
+    ops.qk_norm_rope_append(c, NH, NKV, D, qw, kw, 1e-6, None, pos, seq, None, None, None)
+    ref.qk_norm_rope_append(d, NH, NKV, D, qw, kw, 1e-6, None, pos, seq, None, None, None)
+    torch.testing.assert_close(c, d, **tol(dtype))
+    kp3, vp3 = torch.zeros_like(kp), torch.zeros_like(vp)
+    ops.qk_norm_rope_append(c, NH, NKV, D, None, None, 0.0, None, pos, seq, table, kp3, vp3)
+    kp4, vp4 = torch.zeros_like(kp), torch.zeros_like(vp)
+    ref.qk_norm_rope_append(d, NH, NKV, D, None, None, 0.0, None, pos, seq, table, kp4, vp4)
+    torch.testing.assert_close(kp3, kp4, **tol(dtype))
+    torch.testing.assert_close(vp3, vp4, **tol(dtype))
+
+
+def test_append_skips_negative_page(ops):
+    """A page index < 0 writes nothing (it must not wrap to the last page)."""
+    NH, NKV, D, page = 2, 1, 16, 4
+    kp = torch.zeros(4, NKV, page, D, device="cuda")
+    vp = torch.zeros_like(kp)
+    table = torch.full((1, 2), -1, dtype=torch.int32, device="cuda")
+    qkv = rnd(1, (NH + 2 * NKV) * D, seed=11)
+    pos = torch.tensor([5], dtype=torch.int32, device="cuda")
+    seq = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.qk_norm_rope_append(qkv, NH, NKV, D, None, None, 0.0, None, pos, seq, table, kp, vp)
+    assert kp.abs().sum() == 0 and vp.abs().sum() == 0
+
+
+def _attention_case(ops, fn, dtype, NH, NKV, D, page, lens, q_lens, window, seed, spike=None):
+    B = len(lens)
+    n_pages = sum((l + page - 1) // page for l in lens) + 3
+    kp, vp, table = _paged_setup(B, lens, NKV, D, page, dtype, n_pages, seed)
+    # fill the pages of each request with random keys and values
+    g = torch.Generator(device="cuda").manual_seed(seed + 1)
+    for b, l in enumerate(lens):
+        for j in range(l):
+            pg = int(table[b, j // page])
+            kp[pg, :, j % page] = torch.randn(NKV, D, device="cuda", generator=g).to(dtype)
+            vp[pg, :, j % page] = torch.randn(NKV, D, device="cuda", generator=g).to(dtype)
+    pos = torch.cat([torch.arange(l - q, l) for l, q in zip(lens, q_lens)]).to(torch.int32).cuda()
+    seq = torch.cat([torch.full((q,), b) for b, q in enumerate(q_lens)]).to(torch.int32).cuda()
+    T = pos.numel()
+    q = rnd(T, (NH + 2 * NKV) * D, dtype=dtype, seed=seed + 2)
+    if spike is not None:
+        # make one far key dominate for the last query of request 0: a kernel that loses that
+        # key (a page's edge, a tile's edge) is far off, not a little
+        b, j = spike
+        pg = int(table[b, j // page])
+        last = sum(q_lens[:b + 1]) - 1
+        for h in range(NH):
+            kv = h // (NH // NKV)
+            q[last, h * D:(h + 1) * D] = (kp[pg, kv, j % page].float() * 4.0).to(dtype)
+    out1 = torch.zeros(T, NH * D, device="cuda", dtype=dtype)
+    out2 = torch.zeros_like(out1)
+    fn(q, out1, kp, vp, pos, seq, table, NH, NKV, D, D ** -0.5, window)
+    ref.attention_generic(q, out2, kp, vp, pos, seq, table, NH, NKV, D, D ** -0.5, window)
+    return out1, out2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("NH,NKV,D,page,window", [(5, 1, 48, 16, 0), (6, 2, 32, 8, 0), (4, 4, 16, 4, 0), (8, 2, 128, 16, 0),
+                                                 (4, 2, 64, 16, 21), (6, 3, 80, 8, 7), (2, 1, 256, 16, 0)])
+def test_attention_generic(ops, dtype, NH, NKV, D, page, window):
+    o1, o2 = _attention_case(ops, ops.attention_generic, dtype, NH, NKV, D, page, lens=[150, 33, 1, 64],
+                             q_lens=[37, 33, 1, 2], window=window, seed=20)
+    torch.testing.assert_close(o1, o2, **tol(dtype))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_generic_far_key(ops, dtype):
+    """One far key among hundreds carries the answer."""
+    for j in (0, 15, 16, 255, 256, 300):
+        o1, o2 = _attention_case(ops, ops.attention_generic, dtype, 4, 2, 64, 16, lens=[301, 40], q_lens=[1, 3],
+                                 window=0, seed=30 + j, spike=(0, j))
+        torch.testing.assert_close(o1, o2, **tol(dtype))
+
+
+@pytest.mark.parametrize("in_dtype,out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.float32),
+                                                (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("M,N,K", [(1, 331, 80), (7, 100, 72), (65, 130, 200), (3, 1000, 4096), (128, 64, 16)])
+def test_gemm_simt(ops, in_dtype, out_dtype, M, N, K):
+    a = rnd(M, K, dtype=in_dtype, seed=40)
+    w = rnd(N, K, dtype=in_dtype, scale=0.05, seed=41)
+    out = ops.gemm_simt(a, w, torch.empty(M, N, device="cuda", dtype=out_dtype))
+    want = (a.double() @ w.double().T)
+    t = dict(rtol=1e-4, atol=1e-4) if out_dtype == torch.float32 else tol(out_dtype)
+    torch.testing.assert_close(out.double(), want, **t)
+
+
+def test_gemm_simt_rows_independent(ops):
+    """A row's result does not depend on the other rows of the batch (bit for bit)."""
+    a = rnd(37, 300, seed=42)
+    w = rnd(91, 300, scale=0.05, seed=43)
+    whole = ops.gemm_simt(a, w, torch.empty(37, 91, device="cuda"))
+    one = ops.gemm_simt(a[5:6].contiguous(), w, torch.empty(1, 91, device="cuda"))
+    assert torch.equal(whole[5:6], one)
+
+
+@pytest.mark.parametrize("R,V", [(1, 331), (5, 151936), (3, 1000), (64, 4097)])
+def test_argmax(ops, R, V):
+    lg = rnd(R, V, seed=50)
+    lg[0, V - 1] = lg[0, 3] = 50.0   # equal maxima: the lowest index wins
+    out = ops.argmax(lg, torch.empty(R, device="cuda", dtype=torch.int32))
+    assert out.tolist() == lg.argmax(-1).tolist()
+    assert out[0].item() == 3
