@@ -89,6 +89,22 @@ class BatchBuilder:
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         return self._hosts[i], self._dev
 
+    def validate(self, entries: Sequence[StepEntry]) -> None:
+        """Refuse a malformed batch before anything is reserved for it."""
+        seen = set()
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request!r}: an entry without tokens")
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+            if min(e.tokens) < 0 or max(e.tokens) >= self.vocab_size:
+                raise ValueError(f"request {e.request!r}: token id outside the vocabulary of {self.vocab_size}")
+            for w in e.want:
+                if not 0 <= w < n:
+                    raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
+
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], extra_sections: dict[str, np.ndarray] | None = None) -> StepContext:
         """``starts[i]`` is the number of tokens request i held before this step; its pages
         for the new tokens are already reserved."""

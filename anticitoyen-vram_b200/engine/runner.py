@@ -44,6 +44,12 @@ class ModelRunner:
     def prepare(self, entries: Sequence[StepEntry]) -> StepContext:
         """Admit new requests, reserve pages for the step's tokens, build its context."""
         m = self.manager
+        self.builder.validate(entries)
+        for e in entries:
+            have = m.lengths.get(e.request, 0)
+            if have + len(e.tokens) > self.model.plan.max_positions:
+                raise ValueError(f"request {e.request!r} would reach {have + len(e.tokens)} tokens; the model has "
+                                 f"{self.model.plan.max_positions} positions")
         starts = []
         for e in entries:
             if e.request not in m.lengths:

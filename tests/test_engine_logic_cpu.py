@@ -1,0 +1,148 @@
+"""The step function, the batch builder and the cache on the CPU, with each kernel replaced by its
+plain PyTorch reference (tests/kernel_refs.py): only the logic is under test here; the kernels
+themselves are tested on the GPU."""
+
+from __future__ import annotations
+
+import dataclasses
+
+import pytest
+import torch
+
+import kernel_refs
+import plain_qwen3
+from acvram_b200.engine.batch import StepEntry
+from acvram_b200.engine.runner import ModelRunner
+from acvram_b200.models import DecoderModel, plan_of_folder
+from acvram_b200.parts import Runtime, ScheduleEntry
+from acvram_b200.weights import load_tensors
+from conftest import TINY_PAGE, random_ids
+
+
+@pytest.fixture(autouse=True)
+def references_in_place_of_kernels(monkeypatch):
+    kernel_refs.patch_ops(monkeypatch)
+
+
+def build(folder, change_plan=None):
+    _, plan = plan_of_folder(folder)
+    if change_plan:
+        plan = change_plan(plan)
+    model = DecoderModel(plan)
+    model.load(load_tensors(folder, model.tensor_needs()), Runtime(torch.device("cpu"), torch.float32))
+    return model
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_portions_and_mixing_equal_whole(name, tiny_folders, plain_models):
+    cfg, t = plain_models[name]
+    model = build(tiny_folders[name])
+    ids_a = random_ids(cfg["vocab_size"], 45, 1)
+    ids_b = random_ids(cfg["vocab_size"], 23, 2)
+    ref_a = plain_qwen3.forward_logits(cfg, t, ids_a)
+    ref_b = plain_qwen3.forward_logits(cfg, t, ids_b)
+    r = ModelRunner(model, TINY_PAGE[name], 10, 4)
+    got_a, got_b = [], []
+    got_a.append(r.step([StepEntry("a", ids_a[:19], range(19))]))
+    lg = r.step([StepEntry("a", ids_a[19:21], range(2)), StepEntry("b", ids_b[:20], range(20))])
+    got_a.append(lg[:2]); got_b.append(lg[2:])
+    pa, pb = 21, 20
+    while pa < 45 or pb < 23:
+        entries = []
+        if pb < 23:
+            entries.append(StepEntry("b", ids_b[pb:pb + 1], [0]))
+        if pa < 45:
+            n = min(5, 45 - pa)
+            entries.append(StepEntry("a", ids_a[pa:pa + n], range(n)))
+        lg = r.step(entries)
+        if pb < 23:
+            got_b.append(lg[:1]); lg = lg[1:]; pb += 1
+        if pa < 45:
+            got_a.append(lg); pa += n
+    assert (torch.cat(got_a) - ref_a).abs().max() < 2e-6
+    assert (torch.cat(got_b) - ref_b).abs().max() < 2e-6
+    r.release("a"); r.release("b")
+    r.manager.check()
+    assert r.manager.free_pages() == [10]
+
+
+def test_wanted_rows_only(tiny_folders, plain_models):
+    cfg, t = plain_models["A"]
+    model = build(tiny_folders["A"])
+    ids = random_ids(cfg["vocab_size"], 12, 3)
+    ref = plain_qwen3.forward_logits(cfg, t, ids)
+    r = ModelRunner(model, 16, 4, 2)
+    assert r.step([StepEntry("a", ids[:5], ())]).shape == (0, cfg["vocab_size"])
+    lg = r.step([StepEntry("a", ids[5:], (6, 0))])
+    assert (lg[0] - ref[11]).abs().max() < 2e-6 and (lg[1] - ref[5]).abs().max() < 2e-6
+
+
+def test_a_layer_twice_and_a_shared_cache(tiny_folders, plain_models):
+    """The order of layers is data: layer 1 runs twice (each run with a cache slot of its own)."""
+    cfg, t = plain_models["B"]
+    sched = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(1, 2), ScheduleEntry(2, 3))
+    model = build(tiny_folders["B"], lambda p: dataclasses.replace(p, schedule=sched))
+    ids = random_ids(cfg["vocab_size"], 30, 4)
+    ref = plain_qwen3.forward_logits(cfg, t, ids, schedule=[0, 1, 1, 2])
+    r = ModelRunner(model, 8, 8, 2)
+    got = torch.cat([r.step([StepEntry("a", ids[:17], range(17))]), r.step([StepEntry("a", ids[17:], range(13))])])
+    assert (got - ref).abs().max() < 2e-6
+    assert model.cache_plan().slots_per_group == [4]
+
+
+def test_reading_another_layers_cache(tiny_folders, plain_models):
+    """Layer 2 reads the keys and values that layer 1 wrote (it appends nothing of its own)."""
+    cfg, t = plain_models["B"]
+    sched = (ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(2, 1, writes=False))
+    model = build(tiny_folders["B"], lambda p: dataclasses.replace(p, schedule=sched))
+    assert model.cache_plan().slots_per_group == [2]
+    ids = random_ids(cfg["vocab_size"], 21, 5)
+    r = ModelRunner(model, 8, 8, 2)
+    whole = r.step([StepEntry("w", ids, range(21))])
+    r.release("w")
+    parts = torch.cat([r.step([StepEntry("p", ids[:9], range(9))]), r.step([StepEntry("p", ids[9:], range(12))])])
+    assert (whole - parts).abs().max() < 2e-6, "portions equal whole for a layer that shares a cache"
+    base = plain_qwen3.forward_logits(cfg, t, ids)
+    assert (whole - base).abs().max() > 1e-4, "and sharing the cache does change the model"
+
+
+def test_window_layers_get_their_own_group_and_free_pages(tiny_folders, plain_models):
+    """A window on some layers: another cache group, pages returned as the window passes."""
+    cfg, t = plain_models["A"]
+
+    def windowed(plan):
+        layers = list(plan.layers)
+        layers[1] = dataclasses.replace(layers[1], mixer=layers[1].mixer.with_params(window=16))
+        return dataclasses.replace(plan, layers=tuple(layers))
+
+    model = build(tiny_folders["A"], windowed)
+    assert len(model.cache_plan().groups) == 2
+    ids = random_ids(cfg["vocab_size"], 80, 6)
+    r = ModelRunner(model, 8, 12, 2)
+    got = []
+    pos = 0
+    for n in (30, 2, 17, 1, 1, 1, 28):
+        got.append(r.step([StepEntry("a", ids[pos:pos + n], range(n))]))
+        pos += n
+    got = torch.cat(got)
+    full_pages, window_pages = r.manager.free_pages()
+    assert full_pages == 12 - 10 and window_pages == 12 - 2, "the windowed group holds only the window's pages"
+    # plain: layer 0 full, layer 1 windowed
+    s = plain_qwen3.sizes(cfg)
+    x = plain_qwen3.embed(t["model.embed_tokens.weight"], torch.tensor(ids), torch.float32)
+    positions = torch.arange(80)
+    x = plain_qwen3.decoder_layer(x, t, 0, s, positions, 0)
+    x = plain_qwen3.decoder_layer(x, t, 1, s, positions, 16)
+    ref = plain_qwen3.output_logits(x, t, s)
+    assert (got - ref).abs().max() < 2e-6
+
+
+def test_bad_inputs_are_refused(tiny_folders):
+    model = build(tiny_folders["A"])
+    r = ModelRunner(model, 16, 4, 2)
+    with pytest.raises(ValueError):
+        r.step([StepEntry("a", [1, 2, 999], ())])
+    with pytest.raises(ValueError):
+        r.step([StepEntry("b", [1, 2], (5,))])
+    with pytest.raises(ValueError):
+        r.step([StepEntry("c", [], ())])

@@ -1,0 +1,152 @@
+"""Generation through the Python entry point and the command line, against the plain implementation."""
+
+from __future__ import annotations
+
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_qwen3
+from conftest import ROOT, TINY_PAGE, random_ids
+
+pytestmark = pytest.mark.gpu
+
+
+def engine_for(folder, dtype="float32", **kw):
+    from acvram_b200 import Engine
+    args = dict(max_batch_size=4, max_model_len=256, page_size=16, num_pages=64, token_budget=64)
+    args.update(kw)
+    return Engine(folder, dtype, **args)
+
+
+def test_greedy_three_requests_tiny_a(tiny_folders, plain_models):
+    """Tiny A's workload: prompts of 5/17/33 tokens, 16 greedy tokens each, generated together."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["A"]
+    prompts = [random_ids(cfg["vocab_size"], n, 200 + n) for n in (5, 17, 33)]
+    eng = engine_for(tiny_folders["A"], page_size=TINY_PAGE["A"])
+    got = eng.generate_batch(prompts, SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True))
+    for p, g in zip(prompts, got):
+        assert g == plain_qwen3.greedy_generate(cfg, t, p, 16)
+    assert eng.runner.manager.free_pages() == [64] and eng.idle
+    assert eng.stats.decode_tokens == 3 * 15 and eng.stats.prefill_tokens == 55
+
+
+def test_generate_iterator_and_stats(tiny_folders, plain_models):
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["B"]
+    prompt = random_ids(cfg["vocab_size"], 9, 3)
+    eng = engine_for(tiny_folders["B"], page_size=8)
+    outs = list(eng.generate(prompt, SamplingParams(temperature=0.0, max_tokens=5, ignore_eos=True)))
+    toks = [x for o in outs for x in o.token_ids]
+    assert toks == plain_qwen3.greedy_generate(cfg, t, prompt, 5)
+    assert outs[-1].finished and outs[-1].finish_reason == "length" and outs[-1].completion_tokens == 5
+    assert outs[0].prompt_tokens == 9 and not outs[0].finished
+
+
+def test_long_greedy_decoding(tiny_folders, plain_models):
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["A"]
+    prompt = random_ids(cfg["vocab_size"], 7, 5)
+    eng = engine_for(tiny_folders["A"])
+    got = eng.generate_batch([prompt], SamplingParams(temperature=0.0, max_tokens=200, ignore_eos=True))[0]
+    assert got == plain_qwen3.greedy_generate(cfg, t, prompt, 200)
+
+
+def test_temperature_sampling_tiny_b_portions_mixed_with_decoding(tiny_folders, plain_models):
+    """Tiny B's workload: prompts of 1/9/40/130 tokens in portions of 32 beside decoding, temperature 0.7, fixed
+    seeds.  Each sampled token must be the plain sampler's choice on the plain logits with the same uniform."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["B"]
+    prompts = [random_ids(cfg["vocab_size"], n, 300 + n) for n in (1, 9, 40, 130)]
+    eng = engine_for(tiny_folders["B"], page_size=8, num_pages=128, token_budget=32)
+    params = [SamplingParams(temperature=0.7, top_k=50, top_p=0.9, max_tokens=12, seed=1000 + i, ignore_eos=True)
+              for i in range(4)]
+    got = eng.generate_batch(prompts, params)
+    for i, (p, g) in enumerate(zip(prompts, got)):
+        assert len(g) == 12
+        logits = plain_qwen3.forward_logits(cfg, t, p + g)
+        for n, tok in enumerate(g):
+            row = logits[len(p) - 1 + n]
+            scaled = plain_qwen3.filtered_distribution(row, 0.7, 50, 0.0, 0.9)
+            want = plain_qwen3.draw(scaled, plain_qwen3.philox_uniform(1000 + i, n))
+            assert tok == want, f"request {i} token {n}: engine {tok}, plain sampler {want}"
+
+
+def test_a_requests_tokens_do_not_depend_on_the_batch(tiny_folders, plain_models):
+    from acvram_b200 import SamplingParams
+    cfg, _ = plain_models["B"]
+    prompts = [random_ids(cfg["vocab_size"], n, 400 + n) for n in (12, 30, 5)]
+    sp = lambda i: SamplingParams(temperature=0.9, top_p=0.95, max_tokens=10, seed=77 + i, ignore_eos=True)
+    eng = engine_for(tiny_folders["B"], page_size=8)
+    together = eng.generate_batch(prompts, [sp(i) for i in range(3)])
+    alone = [eng.generate_batch([p], sp(i))[0] for i, p in enumerate(prompts)]
+    assert together == alone
+
+
+def test_preemption_changes_no_token(tiny_folders, plain_models):
+    """With so few pages that running requests are preempted and recomputed, greedy tokens stay the same."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["A"]
+    prompts = [random_ids(cfg["vocab_size"], n, 500 + n) for n in (20, 25, 18)]
+    sp = SamplingParams(temperature=0.0, max_tokens=30, ignore_eos=True)
+    small = engine_for(tiny_folders["A"], num_pages=7, token_budget=16)
+    got = small.generate_batch(prompts, sp)
+    assert small.stats.preempted > 0, "the pool was meant to be too small"
+    for p, g in zip(prompts, got):
+        assert g == plain_qwen3.greedy_generate(cfg, t, p, 30)
+    small.runner.manager.check()
+    assert small.runner.manager.free_pages() == [7]
+
+
+def test_refusal_and_stop_tokens(tiny_folders, plain_models):
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["A"]
+    eng = engine_for(tiny_folders["A"], num_pages=2)
+    outs = list(eng.generate(random_ids(cfg["vocab_size"], 40, 1), SamplingParams(temperature=0.0, max_tokens=4)))
+    assert outs[-1].finished and outs[-1].finish_reason == "refused" and outs[-1].token_ids == []
+    eng = engine_for(tiny_folders["A"])
+    prompt = random_ids(cfg["vocab_size"], 10, 2)
+    free = plain_qwen3.greedy_generate(cfg, t, prompt, 6)
+    outs = list(eng.generate(prompt, SamplingParams(temperature=0.0, max_tokens=6, stop_token_ids=[free[2]])))
+    toks = [x for o in outs for x in o.token_ids]
+    assert toks == free[:free.index(free[2]) + 1] and outs[-1].finish_reason == "stop"
+
+
+def test_bfloat16_generation_follows_the_plain_logits(tiny_folders, plain_models):
+    """bfloat16 greedy tokens: at every step the engine's choice is within the plain float32 logits' near-ties."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["B"]
+    prompt = random_ids(cfg["vocab_size"], 33, 9)
+    eng = engine_for(tiny_folders["B"], "bfloat16", page_size=8)
+    got = eng.generate_batch([prompt], SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))[0]
+    logits = plain_qwen3.forward_logits(cfg, t, prompt + got)
+    ref16 = plain_qwen3.forward_logits(cfg, t, prompt + got, torch.bfloat16)
+    yard = float((logits - ref16).abs().max())
+    for n, tok in enumerate(got):
+        row = logits[len(prompt) - 1 + n]
+        assert float(row.max() - row[tok]) <= 3 * yard, f"token {n} is not a near-best choice"
+
+
+def test_command_line_generate_and_random_model(tiny_folders, plain_models, tmp_path):
+    cfg, t = plain_models["A"]
+    prompt = random_ids(cfg["vocab_size"], 11, 4)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "acvram"), "generate", tiny_folders["A"],
+                          "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "5",
+                          "--temperature", "0", "--ignore-eos", "--max-model-len", "128", "--num-pages", "16",
+                          "--json"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    res = json.loads(out.stdout.strip().splitlines()[-1])
+    assert res["outputs"][0] == plain_qwen3.greedy_generate(cfg, t, prompt, 5)
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "acvram"), "random-model",
+                          os.path.join(tiny_folders["B"], "config.json"), str(tmp_path / "m"), "--seed", "1"],
+                         capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    from safetensors.torch import load_file
+    a = load_file(os.path.join(tiny_folders["B"], "model.safetensors"))
+    b = load_file(str(tmp_path / "m" / "model.safetensors"))
+    assert all(torch.equal(a[k], b[k]) for k in a)

@@ -1,0 +1,187 @@
+"""The scheduler's decisions, with a fake model: admission, portions under a token budget, decoding,
+finishing and freeing, and what happens when pages run out."""
+
+from __future__ import annotations
+
+import random
+
+import pytest
+
+from acvram_b200.cache import CacheManager, CachePlan, PagedNeed
+from acvram_b200.engine.scheduler import Request, Scheduler
+from acvram_b200.sampling import SamplingParams
+
+
+def make(num_pages=16, page=4, max_batch=4, budget=16, max_len=256):
+    m = CacheManager(CachePlan([PagedNeed(1, 8, 0)] * 2), page, num_pages, max_batch)
+    return m, Scheduler(m, max_batch, budget, max_len)
+
+
+def req(i, n, max_tokens=4, **kw):
+    return Request(f"r{i}", list(range(1, n + 1)), SamplingParams(temperature=0.0, max_tokens=max_tokens, **kw), seed=i)
+
+
+def run_step(m, s, token=7, eos=()):
+    """Schedule, 'run' (advance the cache manager as the runner does) and commit."""
+    plan = s.schedule()
+    for e in plan.entries:
+        m.advance(e.request.request_id, e.start + e.count)
+    s.commit(plan, [token] * sum(e.samples for e in plan.entries), eos)
+    m.check()
+    return plan
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    m, s = make(budget=16, num_pages=32)
+    s.add(req(0, 40))
+    sizes = []
+    while not s.idle:
+        plan = run_step(m, s)
+        sizes.append([(e.request.request_id, e.start, e.count, e.samples) for e in plan.entries])
+    assert sizes[0] == [("r0", 0, 16, False)] and sizes[1] == [("r0", 16, 16, False)]
+    assert sizes[2] == [("r0", 32, 8, True)]
+    assert sizes[3] == [("r0", 40, 1, True)], "after the prompt, one token per step"
+    assert len(sizes) == 3 + 3 and m.free_pages() == [32]
+
+
+def test_decode_tokens_come_first_and_portions_share_the_rest():
+    m, s = make(budget=10, num_pages=64)
+    s.add(req(0, 6, max_tokens=10))
+    run_step(m, s)                       # r0 whole prompt, first token
+    s.add(req(1, 30))
+    s.add(req(2, 5))
+    plan = run_step(m, s)
+    got = [(e.request.request_id, e.count, e.samples) for e in plan.entries]
+    assert got == [("r0", 1, True), ("r1", 9, False)], "1 decode token, then 9 of the budget for the oldest prompt"
+    plan = run_step(m, s)
+    got = [(e.request.request_id, e.count) for e in plan.entries]
+    assert got == [("r0", 1), ("r1", 9)]
+    plan = run_step(m, s)
+    plan = run_step(m, s)                # r1 has 3 left: r2 gets a portion in the same step
+    got = [(e.request.request_id, e.count, e.samples) for e in plan.entries]
+    assert got == [("r0", 1, True), ("r1", 3, True), ("r2", 5, True)]
+
+
+def test_finish_reasons():
+    m, s = make()
+    s.add(req(0, 3, max_tokens=2, ignore_eos=True))
+    s.add(req(1, 3, max_tokens=5))
+    s.add(req(2, 3, max_tokens=5, ignore_eos=True))
+    s.add(req(3, 3, max_tokens=5, stop_token_ids=[7]))
+    reqs = list(s.waiting)
+    run_step(m, s, token=9, eos=(9,))
+    assert reqs[1].finish_reason == "stop" and reqs[1].output == [9]
+    assert not reqs[2].finished
+    run_step(m, s, token=7, eos=(9,))
+    assert reqs[0].finish_reason == "length" and reqs[0].output == [9, 7]
+    assert reqs[3].finish_reason == "stop"
+    assert not reqs[2].finished
+    while not s.idle:
+        run_step(m, s, token=9, eos=(9,))
+    assert reqs[2].finish_reason == "length" and len(reqs[2].output) == 5
+    assert m.free_pages() == [16] and not m.live()
+
+
+def test_max_tokens_zero_delivers_nothing():
+    m, s = make()
+    s.add(req(0, 3, max_tokens=0))
+    r = s.waiting[0]
+    run_step(m, s)
+    assert r.finished and r.finish_reason == "length" and r.output == []
+
+
+def test_request_that_can_never_fit_is_refused():
+    m, s = make(num_pages=4, page=4)     # 16 tokens in all
+    s.add(req(0, 20))
+    s.add(req(1, 5))
+    plan = s.schedule()
+    assert [r.request_id for r in plan.refused] == ["r0"] and plan.refused[0].finish_reason == "refused"
+    assert [e.request.request_id for e in plan.entries] == ["r1"]
+    assert s.counters["refused"] == 1
+
+
+def test_waiting_request_waits_for_pages():
+    m, s = make(num_pages=6, page=4, budget=64)
+    s.add(req(0, 15, max_tokens=3))
+    s.add(req(1, 12, max_tokens=3))
+    plan = run_step(m, s)
+    assert [e.request.request_id for e in plan.entries] == ["r0"], "r1 needs 3 pages, 2 are free: it waits"
+    assert len(s.waiting) == 1
+    while s.running:
+        run_step(m, s)
+    plan = run_step(m, s)
+    assert [e.request.request_id for e in plan.entries] == ["r1"]
+
+
+def test_pages_run_out_while_decoding_preempts_the_latest():
+    """Two requests fill the pool; when the older one needs a page the later one is preempted,
+    requeued at the head, and recomputed with its tokens so far."""
+    m, s = make(num_pages=4, page=4, budget=64)
+    s.add(req(0, 7, max_tokens=8))
+    s.add(req(1, 6, max_tokens=8))
+    r0, r1 = list(s.waiting)
+    run_step(m, s)                         # both prompts: 2 + 2 pages
+    assert m.free_pages() == [0]
+    plan = run_step(m, s)                  # r0: 8 tokens, fits; r1: 7 tokens, fits
+    assert not plan.preempted
+    plan = run_step(m, s)                  # r0 needs a third page -> r1 (admitted last) gives way
+    assert [r.request_id for r in plan.preempted] == ["r1"]
+    assert [e.request.request_id for e in plan.entries] == ["r0"]
+    assert r1.computed == 0 and r1.preemptions == 1 and s.waiting[0] is r1 and len(r1.output) == 2
+    assert s.counters["preempted"] == 1
+    while not s.idle:
+        run_step(m, s)
+    assert len(r0.output) == 8 and len(r1.output) == 8, "the preempted request still gets all its tokens"
+    assert m.free_pages() == [4]
+
+
+def test_request_alone_that_cannot_grow_is_cut_and_delivered():
+    m, s = make(num_pages=2, page=4, budget=64)
+    s.add(req(0, 6, max_tokens=20))
+    r = s.waiting[0]
+    plans = []
+    while not s.idle:
+        plans.append(run_step(m, s))
+    assert r.finish_reason == "length" and len(r.prompt) + len(r.output) == 9
+    assert plans[-1].truncated == [r] and s.counters["truncated"] == 1
+    assert m.free_pages() == [2]
+
+
+def test_abort_frees_pages():
+    m, s = make(budget=32)
+    s.add(req(0, 9))
+    s.add(req(1, 9))
+    run_step(m, s)
+    s.abort("r0")
+    m.check()
+    assert len(s.running) == 1 and m.free_pages() == [16 - 3]
+    s.abort("r1")
+    assert s.idle and m.free_pages() == [16]
+
+
+def test_too_long_prompt_is_an_error():
+    m, s = make(max_len=10)
+    with pytest.raises(ValueError):
+        s.add(req(0, 10))
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_traffic_ends_with_every_page_free(seed):
+    rng = random.Random(seed)
+    m, s = make(num_pages=rng.choice([6, 9, 20]), page=4, max_batch=rng.choice([2, 4]), budget=rng.choice([3, 8, 32]))
+    reqs = [req(i, rng.randint(1, 18), max_tokens=rng.randint(1, 12)) for i in range(12)]
+    pending = list(reqs)
+    steps = 0
+    while pending or not s.idle:
+        if pending and rng.random() < 0.5:
+            s.add(pending.pop(0))
+        plan = run_step(m, s, token=rng.randint(1, 50))
+        assert plan.num_tokens <= s.token_budget
+        assert len(s.running) <= s.max_batch_size
+        steps += 1
+        assert steps < 3000
+    for r in reqs:
+        assert r.finished
+        if r.finish_reason == "length" and len(r.prompt) + len(r.output) < 24:
+            assert len(r.output) == r.params.max_tokens or m.paged_groups[0].pool.num_pages * 4 <= len(r.prompt) + len(r.output) + 4
+    assert m.free_pages() == [m.paged_groups[0].pool.num_pages] and not m.live()

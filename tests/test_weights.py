@@ -1,0 +1,109 @@
+"""Weights by name: one clear error for everything that does not fit; seeded random models."""
+
+from __future__ import annotations
+
+import json
+import os
+
+import pytest
+import torch
+from safetensors.torch import load_file, save_file
+
+from acvram_b200.models import needs_of_plan, plan_of_folder
+from acvram_b200.weights import WeightError, load_tensors, write_random_model
+from conftest import tiny_config
+
+
+def test_random_model_round_trip(tmp_path):
+    cfg = tiny_config("B")
+    write_random_model(cfg, tmp_path, seed=5)
+    config, plan = plan_of_folder(tmp_path)
+    assert config == cfg
+    tensors = load_tensors(tmp_path, needs_of_plan(plan))
+    assert tensors["model.layers.2.self_attn.q_proj.weight"].shape == (192, 96)
+    assert tensors["lm_head.weight"].dtype == torch.bfloat16
+    # matrices are N(0, 0.02), every norm weight is 1 + N(0, 0.1)
+    w = tensors["model.layers.0.mlp.gate_proj.weight"].float()
+    assert abs(w.std().item() - 0.02) < 2e-3 and abs(w.mean().item()) < 2e-3
+    for name in ("model.norm.weight", "model.layers.1.input_layernorm.weight", "model.layers.1.self_attn.k_norm.weight"):
+        n = tensors[name].float()
+        assert abs(n.mean().item() - 1) < 0.08 and 0.03 < n.std().item() < 0.2
+
+
+def test_seed_and_name_decide_a_tensor(tmp_path):
+    a, b, c = tmp_path / "a", tmp_path / "b", tmp_path / "c"
+    write_random_model(tiny_config("A"), a, seed=1)
+    write_random_model(tiny_config("A"), b, seed=1)
+    write_random_model(tiny_config("A"), c, seed=2)
+    ta, tb, tc = (load_file(str(p / "model.safetensors")) for p in (a, b, c))
+    assert all(torch.equal(ta[k], tb[k]) for k in ta)
+    assert not torch.equal(ta["model.norm.weight"], tc["model.norm.weight"])
+    assert "lm_head.weight" not in ta, "a tied model stores no head"
+
+
+def test_stored_precision_is_kept(tmp_path):
+    write_random_model(tiny_config("A"), tmp_path, seed=1, dtype=torch.float32)
+    _, plan = plan_of_folder(tmp_path)
+    t = load_tensors(tmp_path, needs_of_plan(plan))
+    assert all(v.dtype == torch.float32 for v in t.values()), "a tensor stored in 32-bit stays so"
+    # and its values are the bfloat16-rounded ones, so both run precisions read the same numbers
+    assert torch.equal(t["model.norm.weight"], t["model.norm.weight"].bfloat16().float())
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
+    write_random_model(tiny_config("B"), tmp_path, seed=0)
+    path = os.path.join(tmp_path, "model.safetensors")
+    t = load_file(path)
+    del t["model.layers.1.mlp.up_proj.weight"]
+    del t["model.norm.weight"]
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(16)
+    t["model.layers.2.self_attn.k_proj.weight"] = torch.zeros(32, 96, dtype=torch.bfloat16)
+    save_file(t, path)
+    _, plan = plan_of_folder(tmp_path)
+    with pytest.raises(WeightError) as err:
+        load_tensors(tmp_path, needs_of_plan(plan))
+    e = err.value
+    assert sorted(e.missing) == ["model.layers.1.mlp.up_proj.weight", "model.norm.weight"]
+    assert e.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert e.wrong_shape == [("model.layers.2.self_attn.k_proj.weight", (32, 96), (64, 96))]
+    msg = str(e)
+    for word in ("missing (2)", "unexpected (1)", "wrong shape", "[64, 96]"):
+        assert word in msg
+
+
+def test_untied_model_needs_its_head(tmp_path):
+    write_random_model(tiny_config("B"), tmp_path, seed=0)
+    path = os.path.join(tmp_path, "model.safetensors")
+    t = load_file(path)
+    del t["lm_head.weight"]
+    save_file(t, path)
+    _, plan = plan_of_folder(tmp_path)
+    with pytest.raises(WeightError) as err:
+        load_tensors(tmp_path, needs_of_plan(plan))
+    assert err.value.missing == ["lm_head.weight"]
+
+
+def test_sharded_folder(tmp_path):
+    write_random_model(tiny_config("A"), tmp_path, seed=3)
+    path = os.path.join(tmp_path, "model.safetensors")
+    t = load_file(path)
+    names = sorted(t)
+    half = len(names) // 2
+    shards = {"model-00001-of-00002.safetensors": names[:half], "model-00002-of-00002.safetensors": names[half:]}
+    weight_map = {}
+    for shard, ns in shards.items():
+        save_file({n: t[n] for n in ns}, os.path.join(tmp_path, shard))
+        weight_map.update({n: shard for n in ns})
+    os.remove(path)
+    with open(os.path.join(tmp_path, "model.safetensors.index.json"), "w") as fh:
+        json.dump({"weight_map": weight_map}, fh)
+    _, plan = plan_of_folder(tmp_path)
+    got = load_tensors(tmp_path, needs_of_plan(plan))
+    assert all(torch.equal(got[n], t[n]) for n in names)
+
+
+def test_integer_tables_become_int32(tmp_path):
+    from acvram_b200.weights import TensorNeed
+    save_file({"table": torch.arange(6, dtype=torch.int64).view(2, 3)}, os.path.join(tmp_path, "model.safetensors"))
+    got = load_tensors(tmp_path, {"table": TensorNeed((2, 3), "table")})
+    assert got["table"].dtype == torch.int32
