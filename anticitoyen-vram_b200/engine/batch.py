@@ -73,6 +73,7 @@ class BatchBuilder:
         self._hosts: list[torch.Tensor | None] = [None, None]
         self._events: list[torch.cuda.Event | None] = [None, None]
         self._turn = 0
+        self.last_h2d_bytes = 0
         self._dev: torch.Tensor | None = None
 
     def _buffers(self, n: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -162,6 +163,7 @@ class BatchBuilder:
             offsets[name] = (off, arr.size)
             off += _round4(arr.size)
         dev[:total].copy_(host[:total], non_blocking=True)
+        self.last_h2d_bytes = total * 4
         if self.device.type == "cuda":
             if self._events[self._turn] is None:
                 self._events[self._turn] = torch.cuda.Event()

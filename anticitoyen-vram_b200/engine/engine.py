@@ -75,7 +75,9 @@ class Engine:
         run_dtype = _DTYPES[dtype]
         if not torch.cuda.is_available():
             raise RuntimeError("acvram_b200 needs a CUDA device: its kernels have no CPU path")
-        if random_weights:
+        if hasattr(model, "plan") and hasattr(model, "forward"):     # a model already built and loaded
+            self.model, self.config = model, None
+        elif random_weights:
             config = load_config(model) if isinstance(model, (str, bytes)) or hasattr(model, "__fspath__") else model
             self.model = build_random(config, seed, run_dtype, device)
             self.config = config

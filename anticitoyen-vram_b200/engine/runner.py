@@ -64,11 +64,16 @@ class ModelRunner:
         return self.builder.build(entries, starts)
 
     @torch.no_grad()
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
-        """Logits float32 [wanted, vocab] in the order of the entries and of their ``want``."""
+    def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
+        """Logits float32 [wanted, vocab] in the order of the entries and of their ``want``.
+
+        ``device_tokens`` (int32 [T] on the device) replaces the entries' token ids, for a caller that
+        keeps the sampled tokens on the device between steps; the entries then only say how many."""
         if not entries:
             return torch.empty((0, self.model.plan.vocab_size), device=self.rt.device, dtype=torch.float32)
         ctx = self.prepare(entries)
+        if device_tokens is not None:
+            ctx.tokens.copy_(device_tokens)
         if self.rt.device.type == "cuda":
             with torch.cuda.device(self.rt.device):
                 logits = self.model.forward(ctx, self.storage)

@@ -71,8 +71,13 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.restype = c_int
 
 
+LAUNCHES = 0   # kernels of this package launched so far (library matrix products are not counted)
+
+
 def _check(code: int, name: str) -> None:
+    global LAUNCHES
     if code == 0:
+        LAUNCHES += 1
         return
     if code < 0:
         raise KernelError(f"{name}: {_ERRORS.get(code, f'refused with code {code}')}")
