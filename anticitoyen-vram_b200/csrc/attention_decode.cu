@@ -1,0 +1,299 @@
+// Split-KV paged decode attention, bfloat16, grouped by kv-head.
+//
+// One CTA per (decoding request, kv-head, split of the context).  All query heads
+// that share the kv-head (NH/NKV of them, at most 16) form the 16 rows of one
+// tensor-core tile, so each key and value is read from memory once for the whole
+// group.  The reference has such a kernel for int8 pages only and, for bf16
+// pages, gathers the whole context into a dense copy before calling SDPA
+// (acvram/engine/attention.py:651-654, acvram/memory/kvcache.py:735-768); its int8
+// kernels have the same shape of work: partial (m, l, acc) per chunk, then a merge
+// (acvram/kernels/acvram_kernels.cu:955-1361), and its Triton form lets the block
+// that arrives last do the merge (acvram/kernels/attn_paginee.py:176-259), which
+// is what happens here: no block ever waits for another.
+//
+// Keys and values stream through shared memory in tiles of 64 keys with 16-byte
+// asynchronous copies, two tiles in flight; each of the four warps takes 16 keys
+// of a tile (QK^T and PV on mma.sync m16n8k16, softmax state in float) and the
+// warps merge at the end.  Rows of a tile are addressed through the block table
+// one by one, so any page size works.
+#include "mma_tiles.cuh"
+
+#define AD_THREADS 128
+#define AD_TILE 64
+#define AD_LOG2E 1.4426950408889634f
+
+template <int D>
+__global__ void __launch_bounds__(AD_THREADS)
+attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
+                   const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                   const int* __restrict__ dec_tokens, const int* __restrict__ dec_seqs,
+                   const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride, int NH, int NKV,
+                   int page_size, int num_pages, float scale, int window, int n_splits, float* __restrict__ part_acc,
+                   float* __restrict__ part_ml, int* __restrict__ counters) {
+    constexpr int CH = D / 8;                 // 16-byte chunks per row
+    constexpr int TILE_BYTES = AD_TILE * D * 2;
+    extern __shared__ __align__(128) unsigned char smem[];
+    unsigned char* q_s = smem;                                   // [16][D]
+    unsigned char* k_s = smem + 16 * D * 2;                      // [2][64][D]
+    unsigned char* v_s = k_s + 2 * TILE_BYTES;                   // [2][64][D]
+    __shared__ int is_last_s;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int tok = dec_tokens[item], seq = dec_seqs[item];
+    const int n_rep = NH / NKV;
+    const int* bt = block_table + (size_t)seq * bt_stride;
+    const int p = kv_len[seq] - 1;
+    const int lo = window > 0 ? max(0, p - window + 1) : 0;
+    const int n_keys = p + 1 - lo;
+    const int chunk = (((n_keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
+    const int beg = lo + split * chunk;
+    const int end = min(beg + chunk, p + 1);
+    const int n_tiles = beg < end ? (end - beg + AD_TILE - 1) / AD_TILE : 0;
+
+    // ---- queries of the group into shared memory (rows >= n_rep are zero)
+    for (int id = tid; id < 16 * CH; id += AD_THREADS) {
+        const int r = id / CH, c = id % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * n_rep + r) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+    }
+
+    auto load_tile = [&](int t, int stage) {
+        const int j0 = beg + t * AD_TILE;
+        for (int id = tid; id < AD_TILE * CH; id += AD_THREADS) {
+            const int r = id / CH, c = id % CH;
+            const int j = j0 + r;
+            const bf16* kr = nullptr;
+            const bf16* vr = nullptr;
+            if (j < end) {
+                kr = paged_row(k_pages, bt, j, kvh, NKV, page_size, num_pages, D);
+                vr = kr ? v_pages + (kr - k_pages) : nullptr;
+            }
+            const int off = stage * TILE_BYTES + tile_off<D>(r, c);
+            cp_async16(smem_u32(k_s + off), kr ? (const void*)(kr + c * 8) : (const void*)k_pages, kr != nullptr);
+            cp_async16(smem_u32(v_s + off), vr ? (const void*)(vr + c * 8) : (const void*)v_pages, vr != nullptr);
+        }
+    };
+
+    if (n_tiles > 0) load_tile(0, 0);
+    cp_async_commit();
+    __syncthreads();
+
+    // ---- query fragments (A operand), kept in registers for the whole kernel
+    uint32_t qf[D / 16][4];
+    {
+        const int mi = lane >> 3, r = lane & 7;
+#pragma unroll
+        for (int kd = 0; kd < D / 16; ++kd)
+            ldmatrix_x4(qf[kd], smem_u32(q_s + tile_off<D>((mi & 1) * 8 + r, kd * 2 + (mi >> 1))));
+    }
+
+    float acc[D / 8][4];
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][e] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    const float scale_log2 = scale * AD_LOG2E;
+    const int mi = lane >> 3, lr = lane & 7;
+
+    for (int t = 0; t < n_tiles; ++t) {
+        const int stage = t & 1;
+        if (t + 1 < n_tiles) load_tile(t + 1, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const uint32_t kb = smem_u32(k_s + stage * TILE_BYTES), vb = smem_u32(v_s + stage * TILE_BYTES);
+        const int jw = beg + t * AD_TILE + warp * 16;   // first key of this warp's 16
+        if (jw < end) {
+            float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+            for (int kd = 0; kd < D / 16; ++kd) {
+                uint32_t b[4];
+                ldmatrix_x4(b, kb + tile_off<D>(warp * 16 + (mi >> 1) * 8 + lr, kd * 2 + (mi & 1)));
+                mma_bf16(s[0], qf[kd], b[0], b[1]);
+                mma_bf16(s[1], qf[kd], b[2], b[3]);
+            }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int j = jw + nt * 8 + (lane & 3) * 2 + (e & 1);
+                    const float v = j < end ? s[nt][e] * scale_log2 : -INFINITY;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+            float alpha[2], m_use[2];
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m_run[h], mx[h]);
+                m_use[h] = m_new == -INFINITY ? 0.f : m_new;
+                alpha[h] = exp2f(m_run[h] - m_use[h]);
+                m_run[h] = m_new;
+                l_run[h] *= alpha[h];
+            }
+            uint32_t pa[4];
+            float pv[2][4];
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    pv[nt][e] = exp2f(s[nt][e] - m_use[e >> 1]);
+                    l_run[e >> 1] += pv[nt][e];
+                }
+            pa[0] = pack_bf16(pv[0][0], pv[0][1]);
+            pa[1] = pack_bf16(pv[0][2], pv[0][3]);
+            pa[2] = pack_bf16(pv[1][0], pv[1][1]);
+            pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+#pragma unroll
+            for (int i = 0; i < D / 8; ++i) {
+                acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
+                acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+            }
+#pragma unroll
+            for (int nd = 0; nd < D / 16; ++nd) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, vb + tile_off<D>(warp * 16 + (mi & 1) * 8 + lr, nd * 2 + (mi >> 1)));
+                mma_bf16(acc[2 * nd], pa, b[0], b[1]);
+                mma_bf16(acc[2 * nd + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+    __syncthreads();
+
+    // ---- merge the four warps through shared memory (the tiles are no longer needed)
+    float* wm = reinterpret_cast<float*>(k_s);            // [4][16]
+    float* wl = wm + 64;                                  // [4][16]
+    float* wacc = wl + 64;                                // [4][16][D]
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+        if ((lane & 3) == 0) {
+            wm[warp * 16 + r0] = m_run[0]; wm[warp * 16 + r0 + 8] = m_run[1];
+            wl[warp * 16 + r0] = l_run[0]; wl[warp * 16 + r0 + 8] = l_run[1];
+        }
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+            float* a0 = wacc + ((warp * 16 + r0) * D) + i * 8 + c0;
+            float* a1 = wacc + ((warp * 16 + r0 + 8) * D) + i * 8 + c0;
+            a0[0] = acc[i][0]; a0[1] = acc[i][1];
+            a1[0] = acc[i][2]; a1[1] = acc[i][3];
+        }
+    }
+    __syncthreads();
+
+    const size_t part = ((size_t)item * NKV + kvh) * n_splits + split;
+    for (int idx = tid; idx < n_rep * D; idx += AD_THREADS) {
+        const int r = idx / D, d = idx % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w * 16 + r]);
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float f = exp2f(wm[w * 16 + r] - M);
+                L += wl[w * 16 + r] * f;
+                O += wacc[(w * 16 + r) * D + d] * f;
+            }
+        }
+        if (n_splits == 1) {
+            out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            part_acc[(part * n_rep + r) * D + d] = O;
+            if (d == 0) {
+                part_ml[(part * n_rep + r) * 2] = M;
+                part_ml[(part * n_rep + r) * 2 + 1] = L;
+            }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // ---- the block that arrives last merges the splits, in split order
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int old = atomicAdd(&counters[item * NKV + kvh], 1);
+        is_last_s = old == n_splits - 1;
+    }
+    __syncthreads();
+    if (!is_last_s) return;
+    __threadfence();
+    const size_t base = ((size_t)item * NKV + kvh) * n_splits;
+    for (int idx = tid; idx < n_rep * D; idx += AD_THREADS) {
+        const int r = idx / D, d = idx % D;
+        float M = -INFINITY;
+        for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(&part_ml[((base + sp) * n_rep + r) * 2]));
+        float L = 0.f, O = 0.f;
+        if (M != -INFINITY) {
+            for (int sp = 0; sp < n_splits; ++sp) {
+                const float f = exp2f(__ldcg(&part_ml[((base + sp) * n_rep + r) * 2]) - M);
+                L += __ldcg(&part_ml[((base + sp) * n_rep + r) * 2 + 1]) * f;
+                O += __ldcg(&part_acc[((base + sp) * n_rep + r) * D + d]) * f;
+            }
+        }
+        out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+    if (tid == 0) counters[item * NKV + kvh] = 0;   // ready for the next launch
+}
+
+template <int D>
+static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                         const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
+                         const int* block_table, int bt_stride, int NH, int NKV, int page_size, int num_pages,
+                         float scale, int window, int n_splits, float* part_acc, float* part_ml, int* counters,
+                         cudaStream_t stream) {
+    const int smem = 16 * D * 2 + 4 * AD_TILE * D * 2;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(n_dec, NKV, n_splits);
+    attn_decode_kernel<D><<<grid, AD_THREADS, smem, stream>>>(
+        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
+        dec_seqs, kv_len, block_table, bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc,
+        part_ml, counters);
+    return acv_launch_status();
+}
+
+// Scratch, given by the caller: part_acc holds n_dec*NKV*n_splits*(NH/NKV)*D floats, part_ml
+// n_dec*NKV*n_splits*(NH/NKV)*2 floats, counters n_dec*NKV ints that are zero before the first call
+// (the kernel leaves them zero).  scratch_floats / scratch_counters say how much the caller gave.
+ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                 const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec,
+                                 const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int D,
+                                 int page_size, int num_pages, float scale, int window, int n_splits, float* part_acc,
+                                 float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
+                                 long long scratch_counters, cudaStream_t stream) {
+    if (n_dec <= 0) return 0;
+    if (NKV <= 0 || NH % NKV || NH / NKV > 16 || n_splits < 1 || n_splits > 65535 || NKV > 65535) return ACV_ERR_SIZE;
+    if (((uintptr_t)q & 15) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
+        return ACV_ERR_ALIGN;
+    const long long n_rep = NH / NKV;
+    if (n_splits > 1) {
+        const long long parts = (long long)n_dec * NKV * n_splits;
+        if (parts * n_rep * D > scratch_floats || parts * n_rep * 2 > scratch_ml_floats ||
+            (long long)n_dec * NKV > scratch_counters)
+            return ACV_ERR_SCRATCH;
+    }
+#define AD_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
+                bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, stream
+    switch (D) {
+        case 64: return launch_decode<64>(AD_ARGS);
+        case 128: return launch_decode<128>(AD_ARGS);
+        default: return ACV_ERR_SIZE;
+    }
+#undef AD_ARGS
+}

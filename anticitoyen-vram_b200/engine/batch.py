@@ -55,6 +55,9 @@ class StepContext:
         return max(self.q_lens, default=0)
 
 
+QUERY_TILE = 64   # query tokens per tile of the portion-attention kernel
+
+
 def _round4(n: int) -> int:
     return (n + 3) & ~3
 
@@ -150,6 +153,19 @@ class BatchBuilder:
                 shapes[f"bt{gi}"] = (B, W)
             else:
                 sections.append((f"st{gi}", np.asarray([g.slot_of[e.request] for e in entries], dtype=np.int32)))
+        # work lists of the attention kernels: requests with one token (decoding) and tiles of
+        # QUERY_TILE tokens of the requests with more (portions of prompts)
+        ql = np.asarray(q_lens, dtype=np.int32)
+        dec = np.nonzero(ql == 1)[0].astype(np.int32)
+        tile_seq, tile_q0 = [], []
+        for i in np.nonzero(ql > 1)[0]:
+            starts_i = np.arange(0, q_lens[i], QUERY_TILE, dtype=np.int32)
+            tile_seq.append(np.full(starts_i.size, i, dtype=np.int32))
+            tile_q0.append(starts_i)
+        work_counts = {"dec": int(dec.size), "tiles": int(sum(t.size for t in tile_seq))}
+        sections += [("dec_tokens", cu[:-1][dec]), ("dec_seqs", dec),
+                     ("tile_seq", np.concatenate(tile_seq) if tile_seq else np.zeros(0, np.int32)),
+                     ("tile_q0", np.concatenate(tile_q0) if tile_q0 else np.zeros(0, np.int32))]
         for name, arr in (extra_sections or {}).items():
             sections.append((name, np.ascontiguousarray(arr, dtype=np.int32).reshape(-1)))
 
@@ -182,6 +198,9 @@ class BatchBuilder:
                 ctx.block_tables[gi] = view(f"bt{gi}").view(shapes[f"bt{gi}"])
             else:
                 ctx.state_slots[gi] = view(f"st{gi}")
-        for name in (extra_sections or {}):
+        for name in ("dec_tokens", "dec_seqs", "tile_seq", "tile_q0", *(extra_sections or {})):
             ctx.work[name] = view(name)
+        ctx.work["n_dec"] = work_counts["dec"]
+        ctx.work["n_tiles"] = work_counts["tiles"]
+        ctx.work["max_dec_kv"] = max((k for k, q in zip(kv_lens, q_lens) if q == 1), default=0)
         return ctx

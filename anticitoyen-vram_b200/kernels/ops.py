@@ -53,7 +53,7 @@ def loaded_library_path() -> str | None:
 
 
 def _declare(lib: ctypes.CDLL) -> None:
-    P, I, F = c_void_p, c_int, c_float
+    P, I, F, LL = c_void_p, c_int, c_float, ctypes.c_longlong
     sig = {
         "acv_embed": [P, P, P, I, I, I, I, P],
         "acv_add_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
@@ -61,6 +61,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, P],
+        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
         "acv_sample": [P, I, I, I, P, P, P, P, P, P, P, P, P],
@@ -214,6 +216,67 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     return out_token
 
 
+# ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
+_SM_COUNT = 148
+_scratch: dict = {}
+
+
+def _decode_scratch(device, floats: int, ml_floats: int, counters: int):
+    """Scratch of the split-KV kernel, kept between calls and only ever grown (addresses that a
+    captured graph holds stay valid as long as a warm-up call of the same shape came first)."""
+    key = str(device)
+    have = _scratch.get(key)
+    if have is None or have[0].numel() < floats or have[1].numel() < ml_floats or have[2].numel() < counters:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("attention_decode: scratch would grow during a graph capture; run the shape once first")
+        grow = lambda n, old: max(n, 2 * old)
+        o = have or (torch.empty(0), torch.empty(0), torch.empty(0))
+        have = (torch.empty(grow(floats, o[0].numel()), device=device, dtype=torch.float32),
+                torch.empty(grow(ml_floats, o[1].numel()), device=device, dtype=torch.float32),
+                torch.zeros(grow(counters, o[2].numel()), device=device, dtype=torch.int32))
+        _scratch[key] = have
+    return have
+
+
+def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
+    """How many splits of the context fill the GPU: about two CTAs per SM, no split under 128 keys."""
+    pairs = max(1, n_dec * num_kv_heads)
+    want = -(-2 * _SM_COUNT // pairs)
+    return max(1, min(want, -(-max_kv // 128)))
+
+
+def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                     dec_tokens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, kv_len: torch.Tensor,
+                     block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                     window: int, n_splits: int) -> torch.Tensor:
+    """Attention of requests that bring one token each, over their pages, split over the context."""
+    n_rep = num_heads // num_kv_heads
+    parts = n_dec * num_kv_heads * n_splits if n_splits > 1 else 0
+    acc, ml, cnt = _decode_scratch(q.device, parts * n_rep * head_dim, parts * n_rep * 2, n_dec * num_kv_heads)
+    _check(library().acv_attention_decode(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(dec_tokens), _p(dec_seqs), n_dec,
+        _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim, k_pages.shape[2],
+        k_pages.shape[0], scale, window, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
+        _stream()), "attention_decode")
+    return out
+
+
+def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                    tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
+                    kv_len: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                    scale: float, window: int) -> torch.Tensor:
+    """Causal attention of portions of prompts (tiles of 64 query tokens) over their requests' pages."""
+    _check(library().acv_attention_chunk(
+        _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0), n_tiles,
+        _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim,
+        k_pages.shape[2], k_pages.shape[0], scale, window, _stream()), "attention_chunk")
+    return out
+
+
+def tensor_core_attention_takes(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and num_heads // num_kv_heads <= 16
+
+
 # ----------------------------------------------------------------------------- dispatch by shape
 def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
@@ -221,9 +284,22 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     """Attention of every token of the step over its request's pages.
 
     ``qkv`` is the stacked projection after norm and rotation (queries are its first
-    num_heads*head_dim columns); ``ctx`` is the step's StepContext."""
-    return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
-                             num_kv_heads, head_dim, scale, window)
+    num_heads*head_dim columns); ``ctx`` is the step's StepContext.  bfloat16 with a head
+    size of 64 or 128 goes to the tensor-core kernels, requests with one token to the
+    split-KV kernel and portions to the tiled one; everything else to the generic kernel."""
+    if not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim):
+        return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
+                                 num_kv_heads, head_dim, scale, window)
+    w = ctx.work
+    if w["n_dec"]:
+        kv = min(w["max_dec_kv"], window) if window > 0 else w["max_dec_kv"]
+        attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
+                         block_table, num_heads, num_kv_heads, head_dim, scale, window,
+                         w.get("n_splits") or decode_splits(w["n_dec"], num_kv_heads, kv))
+    if w["n_tiles"]:
+        attention_chunk(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
+                        block_table, num_heads, num_kv_heads, head_dim, scale, window)
+    return out
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

@@ -44,11 +44,15 @@ def tiny_config(which: str):
         return Qwen3Config(vocab_size=331, hidden_size=80, intermediate_size=176, num_hidden_layers=2,
                            num_attention_heads=5, num_key_value_heads=1, head_dim=48, rms_norm_eps=1e-6,
                            rope_theta=50000.0, max_position_embeddings=1024, tie_word_embeddings=False)
+    if which == "D":  # head size 64: the bfloat16 runs of this one go through the tensor-core attention kernels
+        return Qwen3Config(vocab_size=300, hidden_size=128, intermediate_size=160, num_hidden_layers=2,
+                           num_attention_heads=6, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6,
+                           rope_theta=1000000.0, max_position_embeddings=512, tie_word_embeddings=False)
     raise KeyError(which)
 
 
-TINY_SEEDS = {"A": 0, "B": 1, "C": 2}
-TINY_PAGE = {"A": 16, "B": 8, "C": 16}
+TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
+TINY_PAGE = {"A": 16, "B": 8, "C": 16, "D": 16}
 
 
 @pytest.fixture(scope="session")
@@ -56,7 +60,7 @@ def tiny_folders(tmp_path_factory):
     """{name: folder} of the tiny models, written once per session into a temporary folder."""
     from acvram_b200.weights import write_random_model
     out = {}
-    for name in ("A", "B", "C"):
+    for name in ("A", "B", "C", "D"):
         folder = tmp_path_factory.mktemp(f"tiny_{name}")
         write_random_model(tiny_config(name), folder, TINY_SEEDS[name])
         out[name] = str(folder)

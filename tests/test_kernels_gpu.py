@@ -226,3 +226,88 @@ def test_argmax(ops, R, V):
     out = ops.argmax(lg, torch.empty(R, device="cuda", dtype=torch.int32))
     assert out.tolist() == lg.argmax(-1).tolist()
     assert out[0].item() == 3
+
+
+# ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
+class _Ctx:
+    pass
+
+
+def _tc_case(ops, NH, NKV, D, page, lens, q_lens, window, seed, n_splits=None, spike=None):
+    """A mixed batch through ops.attention (decode kernel for one-token requests, tile kernel for portions)."""
+    dtype = torch.bfloat16
+    B = len(lens)
+    n_pages = sum((l + page - 1) // page for l in lens) + 3
+    kp, vp, table = _paged_setup(B, lens, NKV, D, page, dtype, n_pages, seed)
+    g = torch.Generator(device="cuda").manual_seed(seed + 1)
+    for b, l in enumerate(lens):
+        for j in range(l):
+            pg = int(table[b, j // page])
+            kp[pg, :, j % page] = torch.randn(NKV, D, device="cuda", generator=g).to(dtype)
+            vp[pg, :, j % page] = torch.randn(NKV, D, device="cuda", generator=g).to(dtype)
+    ctx = _Ctx()
+    ctx.positions = torch.cat([torch.arange(l - q, l) for l, q in zip(lens, q_lens)]).to(torch.int32).cuda()
+    ctx.seq_of_token = torch.cat([torch.full((q,), b) for b, q in enumerate(q_lens)]).to(torch.int32).cuda()
+    cu = [0]
+    for q in q_lens:
+        cu.append(cu[-1] + q)
+    ctx.cu_q = torch.tensor(cu, dtype=torch.int32).cuda()
+    ctx.kv_len = torch.tensor(lens, dtype=torch.int32).cuda()
+    dec = [b for b, q in enumerate(q_lens) if q == 1]
+    tiles = [(b, s) for b, q in enumerate(q_lens) if q > 1 for s in range(0, q, 64)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    ctx.work = {"dec_tokens": i32([cu[b] for b in dec]), "dec_seqs": i32(dec), "n_dec": len(dec),
+                "tile_seq": i32([t[0] for t in tiles]), "tile_q0": i32([t[1] for t in tiles]), "n_tiles": len(tiles),
+                "max_dec_kv": max([lens[b] for b in dec], default=0), "n_splits": n_splits}
+    T = cu[-1]
+    q = rnd(T, (NH + 2 * NKV) * D, dtype=dtype, seed=seed + 2)
+    if spike is not None:
+        b, j = spike
+        pg = int(table[b, j // page])
+        last = cu[b + 1] - 1
+        for h in range(NH):
+            q[last, h * D:(h + 1) * D] = (kp[pg, h // (NH // NKV), j % page].float() * 3.0).to(dtype)
+    out1 = torch.full((T, NH * D), 7.0, device="cuda", dtype=dtype)
+    out2 = torch.zeros_like(out1)
+    assert ops.tensor_core_attention_takes(dtype, NH, NKV, D)
+    ops.attention(q, out1, kp, vp, ctx, table, NH, NKV, D, D ** -0.5, window)
+    ref.attention_generic(q, out2, kp, vp, ctx.positions, ctx.seq_of_token, table, NH, NKV, D, D ** -0.5, window)
+    return out1, out2
+
+
+@pytest.mark.parametrize("NH,NKV,D,page", [(8, 2, 128, 16), (6, 2, 64, 8), (5, 1, 64, 16), (16, 1, 128, 32), (4, 4, 128, 4),
+                                          (3, 3, 64, 16)])
+@pytest.mark.parametrize("n_splits", [1, 2, 5, None])
+def test_attention_decode_kernel(ops, NH, NKV, D, page, n_splits):
+    o1, o2 = _tc_case(ops, NH, NKV, D, page, lens=[1, 77, 300, 64, 65, 513], q_lens=[1] * 6, window=0, seed=60,
+                      n_splits=n_splits)
+    torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("NH,NKV,D,page", [(8, 2, 128, 16), (6, 2, 64, 8), (5, 1, 64, 16), (4, 4, 128, 4)])
+def test_attention_chunk_kernel(ops, NH, NKV, D, page):
+    # whole prompts, portions after a cached prefix, a portion of two tokens, tiles that end mid-way
+    o1, o2 = _tc_case(ops, NH, NKV, D, page, lens=[150, 33, 200, 64, 130, 2], q_lens=[150, 2, 71, 64, 65, 2], window=0,
+                      seed=61)
+    torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("window", [1, 7, 64, 100])
+def test_tensor_core_attention_window_and_mixed_batch(ops, window):
+    o1, o2 = _tc_case(ops, 8, 2, 128, 16, lens=[150, 90, 300, 17, 64], q_lens=[150, 1, 70, 1, 2], window=window, seed=62)
+    torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+def test_tensor_core_attention_far_key(ops):
+    """One far key among hundreds carries the answer: at a page's edge, a tile's edge, a split's edge."""
+    for j in (0, 15, 16, 63, 64, 127, 128, 447, 448, 600):
+        for q_lens in ([1, 1], [5, 3]):
+            o1, o2 = _tc_case(ops, 4, 2, 128, 16, lens=[601, 40], q_lens=q_lens, window=0, seed=70 + j, spike=(0, j))
+            torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+def test_decode_kernel_twice_leaves_its_counters_clean(ops):
+    """The split counters go back to zero, so a second call with other shapes is right too."""
+    for seed, lens in ((80, [500, 300]), (81, [129, 700, 90])):
+        o1, o2 = _tc_case(ops, 8, 2, 128, 16, lens=lens, q_lens=[1] * len(lens), window=0, seed=seed, n_splits=4)
+        torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
