@@ -1,0 +1,410 @@
+// C[M,N] = X[M,K] . W[N,K]^T in bfloat16 on the fifth-generation tensor cores:
+// tcgen05.mma with both operands in shared memory (staged by TMA, 128-byte
+// swizzle) and the accumulator in tensor memory, read back with tcgen05.ld.
+//
+// One kernel serves prefill and decode.  An MMA tile is 128 rows of the "A
+// operand" by BN rows of the "B operand", both K-major, which is how x [M,K] and
+// a weight [N,K] both lie in memory.  With many tokens the tokens are the A
+// operand (128 tokens x BN features per tile); with few tokens (decode) the roles
+// are swapped: 128 output features x BN tokens per tile, so that every weight is
+// streamed from memory once whatever the batch and the tensor core's M = 128 is
+// filled by the weight rows.  The K range may be split over several CTAs (decode
+// has too few tiles to fill 148 SMs otherwise); partial tiles go to a float
+// workspace and the CTA that arrives last at a tile adds them in split order, so
+// the sum does not depend on timing.  The reference hands these products to cuBLAS
+// (acvram/kernels/__init__.py:1896-1899).
+//
+// Warp roles in a CTA of 192 threads: warp 0 issues the TMA loads, warp 1
+// allocates tensor memory and issues the MMAs (one thread each), warps 2..5 are
+// the epilogue (each owns the 32 accumulator lanes its rank modulo 4 may read).
+// A CTA walks its work items with a fixed stride, two accumulator buffers in
+// tensor memory let the epilogue of one item overlap the main loop of the next.
+// Every wait on an mbarrier is bounded: when a wait runs out, the kernel records
+// where in `status`, all roles leave their loops, tensor memory is freed and the
+// kernel returns.
+#include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+#define GT_THREADS 192
+#define GT_BM 128            // rows of the A operand per tile = UMMA M
+#define GT_BK 64             // K elements per stage = one 128-byte swizzle row
+#define GT_WAIT_LIMIT (1u << 22)
+
+// ----------------------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ uint32_t gt_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.b32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait: false when the limit ran out (the caller records it and leaves)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < GT_WAIT_LIMIT; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 255) == 255 && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ uint32_t pack2(uint32_t lo_bits, uint32_t hi_bits) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(__uint_as_float(lo_bits), __uint_as_float(hi_bits));
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// K-major operand tile in shared memory, rows of 128 bytes, 128-byte swizzle over groups of 8 rows
+// (1024 bytes apart); tile base aligned to 1024 bytes.  Bits: start address >> 4 [0,14), leading byte
+// offset >> 4 [16,30) (unused for swizzled K-major, 1), stride byte offset >> 4 [32,46) = 64, descriptor
+// version 1 [46,48), layout 2 = SWIZZLE_128B [61,64).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// instruction descriptor of kind::f16: float accumulator [4,6)=1, A and B bfloat16 [7,10)=1 [10,13)=1,
+// both K-major (bits 15, 16 = 0), N >> 3 at [17,23), M >> 4 at [24,29)
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(GT_BM >> 4) << 24);
+}
+
+struct GemmParams {
+    int RA, RB, K;          // rows of the A operand, rows of the B operand, reduction length
+    int M, N;               // output is C[M, N]
+    int ldc;
+    int swap;               // 0: A = x (rows = tokens), 1: A = weight (rows = features)
+    int out_f32;
+    int tiles_a, tiles_b, splits, kb_per_split, n_kb;
+    void* C;
+    float* workspace;       // [tiles][splits][BN][128] floats when splits > 1
+    int* counters;          // [tiles], zero before and after
+    int* status;            // 0, or the code of the wait that ran out
+};
+
+template <int BN>
+struct GemmShape {
+    static constexpr int STAGE_BYTES = (GT_BM + BN) * GT_BK * 2;
+    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;     // two accumulator buffers; a power of two
+    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(GT_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+    using S = GemmShape<BN>;
+    extern __shared__ unsigned char smem_raw[];
+    // operand tiles start on a 1024-byte boundary of the shared window (the swizzle pattern is anchored there)
+    unsigned char* tiles = smem_raw + ((1024u - (gt_smem(smem_raw) & 1023u)) & 1023u);
+    uint64_t* bars = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES);
+    // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
+    const uint32_t full0 = gt_smem(bars), empty0 = full0 + 8 * S::STAGES;
+    const uint32_t tfull0 = empty0 + 8 * S::STAGES, tempty0 = tfull0 + 16;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+    __shared__ int last_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < S::STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gt_smem(&tmem_base_s)), "r"(S::TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+
+    const int n_items = p.tiles_a * p.tiles_b * p.splits;
+    const uint32_t tiles_addr = gt_smem(tiles);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x) {
+                const int split = item % p.splits, tile = item / p.splits;
+                const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+                const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % S::STAGES;
+                    const uint32_t ph = (it / S::STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 1); break; }
+                    mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+                    const uint32_t a_dst = tiles_addr + s * S::STAGE_BYTES;
+                    tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * GT_BK, ta * GT_BM);
+                    tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * s, kb * GT_BK, tb * BN);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(BN);
+            uint32_t it = 0, local = 0;
+            for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
+                const int split = item % p.splits;
+                const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
+                const uint32_t buf = local & 1, use = local >> 1;
+                if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 2); break; }
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * BN;
+                bool failed = false;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % S::STAGES;
+                    const uint32_t ph = (it / S::STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, ph, &abort_s)) { abort_s = 1; atomicExch(p.status, 3); failed = true; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = tiles_addr + s * S::STAGE_BYTES, b_addr = a_addr + GT_BM * GT_BK * 2;
+#pragma unroll
+                    for (int k = 0; k < GT_BK / 16; ++k)
+                        tc_mma_bf16(d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc_commit(empty0 + 8 * s);      // frees the stage when these MMAs have read it
+                }
+                if (failed) break;
+                tc_commit(tfull0 + 8 * buf);        // the accumulator is complete
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int wq = warp & 3;                    // the 32 tensor-memory lanes this warp may read
+        const int et = threadIdx.x - 64;            // 0..127 among the epilogue threads
+        uint32_t local = 0;
+        for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
+            const int split = item % p.splits, tile = item / p.splits;
+            const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+            const uint32_t buf = local & 1, use = local >> 1;
+            if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 4); break; }
+            tc_fence_after();
+            const int row_a = ta * GT_BM + wq * 32 + lane;          // row of the A operand this thread holds
+            const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(wq * 32) << 16);
+            if (p.splits == 1) {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    uint32_t r[16];
+                    tc_ld16(taddr + c0, r);
+                    if (p.swap) {
+                        // C[token = tb*BN + c][feature = row_a]: lanes write neighbouring features
+                        if (row_a < p.N) {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) {
+                                const int m = tb * BN + c0 + c;
+                                if (m < p.M) {
+                                    if (p.out_f32) ((float*)p.C)[(size_t)m * p.ldc + row_a] = __uint_as_float(r[c]);
+                                    else ((bf16*)p.C)[(size_t)m * p.ldc + row_a] = __float2bfloat16_rn(__uint_as_float(r[c]));
+                                }
+                            }
+                        }
+                    } else if (row_a < p.M) {
+                        const int n0 = tb * BN + c0;
+                        if (p.out_f32) {
+                            float* dst = (float*)p.C + (size_t)row_a * p.ldc + n0;
+#pragma unroll
+                            for (int c = 0; c < 16; ++c)
+                                if (n0 + c < p.N) dst[c] = __uint_as_float(r[c]);
+                        } else {
+                            bf16* dst = (bf16*)p.C + (size_t)row_a * p.ldc + n0;
+                            if (n0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0) {
+                                uint4 v0, v1;
+                                v0.x = pack2(r[0], r[1]); v0.y = pack2(r[2], r[3]); v0.z = pack2(r[4], r[5]); v0.w = pack2(r[6], r[7]);
+                                v1.x = pack2(r[8], r[9]); v1.y = pack2(r[10], r[11]); v1.z = pack2(r[12], r[13]); v1.w = pack2(r[14], r[15]);
+                                ((uint4*)dst)[0] = v0;
+                                ((uint4*)dst)[1] = v1;
+                            } else {
+#pragma unroll
+                                for (int c = 0; c < 16; ++c)
+                                    if (n0 + c < p.N) dst[c] = __float2bfloat16_rn(__uint_as_float(r[c]));
+                            }
+                        }
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+                continue;
+            }
+            // ---- split K: partial tile to the workspace, the CTA that arrives last sums in split order
+            float* ws = p.workspace + ((size_t)tile * p.splits + split) * (BN * GT_BM);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                uint32_t r[16];
+                tc_ld16(taddr + c0, r);
+#pragma unroll
+                for (int c = 0; c < 16; ++c) ws[(c0 + c) * GT_BM + wq * 32 + lane] = __uint_as_float(r[c]);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (et == 0) last_s = atomicAdd(&p.counters[tile], 1) == p.splits - 1;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (last_s) {
+                __threadfence();
+                const float* wt = p.workspace + (size_t)tile * p.splits * (BN * GT_BM);
+                const int rows_b = min(BN, p.RB - tb * BN);
+                for (int c0 = 0; c0 < rows_b; c0 += 16) {
+                    // sixteen columns at a time: all loads of a split are issued before any store
+                    float sum[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) sum[c] = 0.f;
+                    for (int sp = 0; sp < p.splits; ++sp) {
+                        float v[16];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) v[c] = __ldcg(&wt[((size_t)sp * BN + c0 + c) * GT_BM + wq * 32 + lane]);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) sum[c] += v[c];
+                    }
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        const int m = p.swap ? tb * BN + c0 + c : row_a;
+                        const int n = p.swap ? row_a : tb * BN + c0 + c;
+                        if (c0 + c < rows_b && m < p.M && n < p.N) {
+                            if (p.out_f32) ((float*)p.C)[(size_t)m * p.ldc + n] = sum[c];
+                            else ((bf16*)p.C)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum[c]);
+                        }
+                    }
+                }
+                if (et == 0) p.counters[tile] = 0;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(S::TMEM_COLS));
+    }
+}
+
+// ----------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    });
+    return fn;
+}
+
+// tensor map of a row-major bf16 matrix [rows, K] with row stride ld (elements): box = 64 x box_rows, 128-byte swizzle
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return ACV_ERR_SIZE;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {GT_BK, (cuuint32_t)box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : ACV_ERR_ALIGN;
+}
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t stream) {
+    using S = GemmShape<BN>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    gemm_tc_kernel<BN><<<grid, GT_THREADS, S::SMEM, stream>>>(ma, mb, p);
+    return acv_launch_status();
+}
+
+// x [M,K] (row stride ldx), w [N,K] (row stride ldw), C [M,N] (row stride ldc) bf16 or float.
+// bn: rows of the B operand per tile (16, 32, 64, 128 or 256); swap: the weight is the A operand.
+// splits > 1 needs workspace of tiles*splits*bn*128 floats and `tiles` zeroed counters.
+// status: one int, 0 unless a bounded wait inside the kernel ran out.
+ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
+                        int out_f32, int swap, int bn, int splits, float* workspace, long long workspace_floats,
+                        int* counters, long long n_counters, int* status, int sm_count, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACV_ERR_ALIGN;
+    GemmParams p;
+    const void* a_ptr = swap ? w : x;
+    const void* b_ptr = swap ? x : w;
+    p.RA = swap ? N : M;
+    p.RB = swap ? M : N;
+    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32;
+    p.tiles_a = (p.RA + GT_BM - 1) / GT_BM;
+    p.tiles_b = (p.RB + bn - 1) / bn;
+    p.n_kb = (K + GT_BK - 1) / GT_BK;
+    if (splits < 1) splits = 1;
+    if (splits > p.n_kb) splits = p.n_kb;
+    p.kb_per_split = (p.n_kb + splits - 1) / splits;
+    p.splits = (p.n_kb + p.kb_per_split - 1) / p.kb_per_split;
+    p.C = C; p.workspace = workspace; p.counters = counters; p.status = status;
+    const long long tiles = (long long)p.tiles_a * p.tiles_b;
+    if (p.splits > 1 && (tiles * p.splits * bn * GT_BM > workspace_floats || tiles > n_counters)) return ACV_ERR_SCRATCH;
+    if (tiles * p.splits > 0x7fffffff) return ACV_ERR_SIZE;
+    CUtensorMap ma, mb;
+    int rc = make_map(&ma, a_ptr, p.RA, K, swap ? ldw : ldx, GT_BM);
+    if (rc) return rc;
+    rc = make_map(&mb, b_ptr, p.RB, K, swap ? ldx : ldw, bn);
+    if (rc) return rc;
+    const int items = (int)(tiles * p.splits);
+    const int grid = items < sm_count ? items : sm_count;
+    switch (bn) {
+        case 16: return launch_gemm<16>(ma, mb, p, grid, stream);
+        case 32: return launch_gemm<32>(ma, mb, p, grid, stream);
+        case 64: return launch_gemm<64>(ma, mb, p, grid, stream);
+        case 128: return launch_gemm<128>(ma, mb, p, grid, stream);
+        case 256: return launch_gemm<256>(ma, mb, p, grid, stream);
+        default: return ACV_ERR_SIZE;
+    }
+}

@@ -61,6 +61,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
+        "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
         "acv_argmax": [P, I, I, I, P, P],
@@ -188,6 +189,82 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tens
     return out
 
 
+# ----------------------------------------------------------------------------- tensor-core matrix product (bfloat16)
+_gemm_scratch: dict = {}
+
+
+def _gemm_buffers(device, ws_floats: int, n_counters: int):
+    key = str(device)
+    have = _gemm_scratch.get(key)
+    if have is None or have[0].numel() < ws_floats or have[1].numel() < n_counters:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("gemm_tc: workspace would grow during a graph capture; run the shape once first")
+        old = have or (torch.empty(0), torch.empty(0), None)
+        ws = torch.empty(max(ws_floats, 2 * old[0].numel(), 1 << 20), device=device, dtype=torch.float32)
+        cnt = torch.zeros(max(n_counters, 2 * old[1].numel(), 4096), device=device, dtype=torch.int32)
+        status = old[2] if old[2] is not None else torch.zeros(1, device=device, dtype=torch.int32)
+        have = (ws, cnt, status)
+        _gemm_scratch[key] = have
+    return have
+
+
+def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int]:
+    """(swap, bn, splits) for x[M,K] @ w[N,K]^T.
+
+    Up to 128 tokens the weight rows fill the tensor core's M = 128 and the tokens are the narrow
+    side (weights stream once whatever the batch); above, tokens are the M side with 256 features
+    per tile.  Splits of K are chosen so that the work items fill whole waves of the SMs."""
+    n_kb = -(-K // 64)
+    if M <= 128:
+        bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
+        tiles = -(-N // 128) * -(-M // bn)
+        if tiles >= 2 * _SM_COUNT:
+            return 1, bn, 1
+        best, best_score = 1, -1.0
+        for s in range(1, 9):
+            if s > 1 and n_kb // s < 8:
+                break
+            items = tiles * s
+            score = items / (-(-items // _SM_COUNT) * _SM_COUNT) - 0.02 * (s - 1)
+            if score > best_score:
+                best, best_score = s, score
+        return 1, bn, best
+    bn = 256 if N >= 256 else 128 if N > 64 else 64
+    return 0, bn, 1
+
+
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple[int, int, int] | None = None) -> torch.Tensor:
+    """out[M,N] = x[M,K] @ w[N,K]^T on tcgen05; x, w bfloat16, out bfloat16 or float32."""
+    _need_cuda(x, w, out)
+    M, K = x.shape
+    N = w.shape[0]
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError("gemm_tc: operands must be bfloat16 and the output bfloat16 or float32")
+    if w.shape[1] != K or out.shape != (M, N) or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError(f"gemm_tc: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
+    swap, bn, splits = plan or gemm_tc_plan(M, N, K)
+    tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
+    ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
+    _check(library().acv_gemm_tc(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
+                                 1 if out.dtype == torch.float32 else 0, swap, bn, splits, _p(ws), ws.numel(), _p(cnt),
+                                 cnt.numel(), _p(status), _SM_COUNT, _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """The tensor-core kernel needs 16-byte aligned rows: K and the row strides multiples of 8."""
+    return (x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(1) == 1)
+
+
+def gemm_status(device=None) -> int:
+    """0, or the code a bounded wait inside a tensor-core product left when it ran out (synchronises)."""
+    worst = 0
+    for key, (_, _, status) in _gemm_scratch.items():
+        worst = max(worst, int(status.item()))
+    return worst
+
+
 # ----------------------------------------------------------------------------- sampling
 def argmax(logits: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out[r] = argmax(logits[r]) (lowest index among equals).  logits float32 [R, V]; out int32 [R]."""
@@ -303,10 +380,15 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """out = x @ w^T in bfloat16 with float accumulation."""
+    """out = x @ w^T in bfloat16 with float accumulation: the tcgen05 kernel; rows that are not 16-byte
+    aligned (K or a stride no multiple of 8) go to the library product, as all do in the reference."""
+    if gemm_tc_takes(x, w):
+        return gemm_tc(x, w, out)
     return torch.mm(x, w.t(), out=out)
 
 
 def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out (float32) = x @ w^T from bfloat16 operands, accumulated in float32."""
+    if gemm_tc_takes(x, w):
+        return gemm_tc(x, w, out)
     return gemm_simt(x, w, out)

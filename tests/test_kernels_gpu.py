@@ -311,3 +311,61 @@ def test_decode_kernel_twice_leaves_its_counters_clean(ops):
     for seed, lens in ((80, [500, 300]), (81, [129, 700, 90])):
         o1, o2 = _tc_case(ops, 8, 2, 128, 16, lens=lens, q_lens=[1] * len(lens), window=0, seed=seed, n_splits=4)
         torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+# ----------------------------------------------------------------------------- tcgen05 matrix product
+GEMM_SHAPES = [
+    # (M, N, K): decode-like (swapped roles) and prefill-like, with edges that fill no tile
+    (1, 256, 128), (8, 6144, 4096), (5, 331, 72), (16, 128, 64), (17, 200, 264), (64, 1000, 512), (100, 384, 200),
+    (128, 256, 4096), (129, 256, 128), (300, 520, 136), (2048, 512, 1024), (515, 4096, 256),
+]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tc(ops, M, N, K, out_dtype):
+    x = rnd(M, K, dtype=torch.bfloat16, seed=90)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=91)
+    out = torch.full((M, N), 3.0, device="cuda", dtype=out_dtype)
+    ops.gemm_tc(x, w, out)
+    want = x.double() @ w.double().T
+    assert ops.gemm_status() == 0
+    t = dict(rtol=1e-4, atol=1e-4) if out_dtype == torch.float32 else tol(torch.bfloat16)
+    torch.testing.assert_close(out.double(), want, **t)
+
+
+@pytest.mark.parametrize("plan", [(1, 16, 1), (1, 16, 4), (1, 32, 3), (1, 64, 2), (1, 128, 5), (0, 64, 1), (0, 128, 2),
+                                  (0, 256, 1), (0, 256, 3)])
+def test_gemm_tc_every_tile_shape_and_split(ops, plan):
+    M, N, K = (50 if plan[0] else 300), 700, 1160
+    if plan[0] and M > plan[1]:
+        M = plan[1] - 3
+    x = rnd(M, K, dtype=torch.bfloat16, seed=92)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=93)
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.zeros(M, N, device="cuda", dtype=out_dtype)
+        ops.gemm_tc(x, w, out, plan)
+        assert ops.gemm_status() == 0
+        t = dict(rtol=1e-4, atol=1e-4) if out_dtype == torch.float32 else tol(torch.bfloat16)
+        torch.testing.assert_close(out.double(), x.double() @ w.double().T, **t)
+
+
+def test_gemm_tc_strided_rows_and_repeat(ops):
+    """x as a column slice of a wider matrix (row stride > K), twice in a row (split counters return to zero)."""
+    big = rnd(40, 1024, dtype=torch.bfloat16, seed=94)
+    x = big[:, 256:768]
+    w = rnd(384, 512, dtype=torch.bfloat16, scale=0.05, seed=95)
+    for _ in range(2):
+        out = torch.zeros(40, 384, device="cuda", dtype=torch.float32)
+        ops.gemm_tc(x, w, out, (1, 64, 4))
+        torch.testing.assert_close(out.double(), x.double() @ w.double().T, rtol=1e-4, atol=1e-4)
+    assert ops.gemm_status() == 0
+
+
+def test_gemm_tc_rows_do_not_depend_on_the_batch(ops):
+    """The same token gives the same output row alone and among others (same tile shape and split)."""
+    x = rnd(16, 512, dtype=torch.bfloat16, seed=96)
+    w = rnd(640, 512, dtype=torch.bfloat16, scale=0.05, seed=97)
+    whole = ops.gemm_tc(x, w, torch.zeros(16, 640, device="cuda", dtype=torch.float32), (1, 16, 2))
+    one = ops.gemm_tc(x[3:4], w, torch.zeros(1, 640, device="cuda", dtype=torch.float32), (1, 16, 2))
+    assert torch.equal(whole[3:4], one)
