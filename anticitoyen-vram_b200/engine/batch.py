@@ -109,6 +109,71 @@ class BatchBuilder:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
 
+    # ------------------------------------------------------------------ fixed-shape decode batches
+    @staticmethod
+    def decode_layout(padded: int, width: int, n_paged: int) -> tuple[dict[str, tuple[int, int]], int]:
+        """Offsets of the sections of a decode batch padded to ``padded`` rows with block tables
+        ``width`` wide: the same for every step of that shape, so a captured graph can hold them."""
+        off, out = 0, {}
+        for name, n in [("tokens", padded), ("positions", padded), ("seq_of_token", padded), ("cu_q", padded + 1),
+                        ("kv_len", padded), ("logit_rows", padded), ("dec_tokens", padded), ("dec_seqs", padded),
+                        *[(f"bt{g}", padded * width) for g in range(n_paged)]]:
+            out[name] = (off, n)
+            off += _round4(n)
+        return out, off
+
+    def build_decode(self, entries: Sequence[StepEntry], starts: Sequence[int], padded: int, width: int,
+                     dev: torch.Tensor) -> StepContext:
+        """One token for each request, padded to ``padded`` rows (padding rows hold nothing: context
+        length 0 and a block table of -1, so they read and write no page), into the buffer ``dev``."""
+        m = self.manager
+        B = len(entries)
+        paged = [(gi, g) for gi, g in enumerate(m.groups) if isinstance(g, PagedGroup)]
+        layout, total = self.decode_layout(padded, width, len(paged))
+        host, _ = self._buffers(total)
+        h = host.numpy()
+        ar = np.arange(padded + 1, dtype=np.int32)
+
+        def put(name, values, fill=0):
+            o, n = layout[name]
+            h[o:o + n] = fill
+            h[o:o + len(values)] = values
+
+        put("tokens", [e.tokens[0] for e in entries])
+        put("positions", list(starts))
+        put("seq_of_token", ar[:padded])
+        put("cu_q", ar)
+        put("kv_len", [s + 1 for s in starts])
+        put("logit_rows", ar[:padded])
+        put("dec_tokens", ar[:padded])
+        put("dec_seqs", ar[:padded])
+        for k, (gi, g) in enumerate(paged):
+            o, n = layout[f"bt{k}"]
+            table = h[o:o + n].reshape(padded, width)
+            table[:] = -1
+            for i, e in enumerate(entries):
+                t = g.tables[e.request]
+                table[i, :len(t)] = t
+        dev[:total].copy_(host[:total], non_blocking=True)
+        self.last_h2d_bytes = total * 4
+        if self.device.type == "cuda":
+            if self._events[self._turn] is None:
+                self._events[self._turn] = torch.cuda.Event()
+            self._events[self._turn].record()
+        view = lambda name: dev[layout[name][0]:layout[name][0] + layout[name][1]]
+        kv_lens = [s + 1 for s in starts]
+        ctx = StepContext(
+            num_tokens=padded, num_seqs=padded, num_logit_rows=padded, tokens=view("tokens"),
+            positions=view("positions"), seq_of_token=view("seq_of_token"), cu_q=view("cu_q"), kv_len=view("kv_len"),
+            logit_rows=view("logit_rows"), requests=[e.request for e in entries], q_lens=[1] * padded,
+            kv_lens=kv_lens + [0] * (padded - B))
+        for k, (gi, g) in enumerate(paged):
+            ctx.block_tables[gi] = view(f"bt{k}").view(padded, width)
+        ctx.work = {"dec_tokens": view("dec_tokens"), "dec_seqs": view("dec_seqs"), "n_dec": padded, "n_tiles": 0,
+                    "tile_seq": view("dec_seqs")[:0], "tile_q0": view("dec_seqs")[:0],
+                    "max_dec_kv": width * m.page_size}
+        return ctx
+
     def build(self, entries: Sequence[StepEntry], starts: Sequence[int], extra_sections: dict[str, np.ndarray] | None = None) -> StepContext:
         """``starts[i]`` is the number of tokens request i held before this step; its pages
         for the new tokens are already reserved."""

@@ -95,6 +95,8 @@ class Engine:
         self.seed = seed
         self.stats = EngineStats()
         self.enable_cuda_graphs = enable_cuda_graphs and run_dtype == torch.bfloat16
+        if self.enable_cuda_graphs:
+            self.runner.enable_graphs()
         self._ids = itertools.count()
         self._requests: dict[Hashable, Request] = {}
         self._seq_ids: dict[Hashable, int] = {}

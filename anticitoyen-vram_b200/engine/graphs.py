@@ -1,0 +1,97 @@
+"""CUDA-graph replay of the decode step.
+
+A step in which every request brings one token has the same launches whatever the
+requests are, once the batch is padded to a bucket and the block tables to a
+bucket width; the whole model step is then captured once per (batch bucket, table
+width) and replayed, which removes the per-launch cost of some three hundred
+launches a step.  The idea, buckets and padding rows follow the reference's
+``GraphRunner`` (acvram/engine/graphs.py:8-22, 49-72; padding rows carry a context
+length of 0 and write nothing, acvram/engine/graphs.py:14-17).  Each graph owns a
+static metadata buffer; a step only copies its packed metadata there and replays.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from .batch import BatchBuilder
+
+BATCH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+MIN_TABLE_WIDTH = 8
+MAX_GRAPHS = 64   # the reference keeps at most 64 as well
+
+
+def batch_bucket(n: int) -> int:
+    for b in BATCH_BUCKETS:
+        if n <= b:
+            return b
+    return 0
+
+
+def width_bucket(pages: int) -> int:
+    w = MIN_TABLE_WIDTH
+    while w < pages:
+        w *= 2
+    return w
+
+
+class DecodeGraphs:
+    def __init__(self, runner) -> None:
+        self.runner = runner
+        self.graphs: dict[tuple[int, int], dict] = {}
+        self.replays = 0
+        self.launches = 0       # kernels of this package run through replays
+        self.disabled_reason: str | None = None
+        if runner.manager.state_groups:
+            self.disabled_reason = "the model keeps per-request state of fixed size"
+
+    def usable(self, entries) -> bool:
+        return (self.disabled_reason is None and all(len(e.tokens) == 1 for e in entries)
+                and batch_bucket(len(entries)) > 0)
+
+    def run(self, entries, starts, device_tokens=None) -> torch.Tensor:
+        """Logits [len(entries), vocab] of a decode step, through a captured graph."""
+        r = self.runner
+        m = r.manager
+        padded = batch_bucket(len(entries))
+        pages = max(g.pages_for(s + 1) for g in m.paged_groups for s in starts)
+        width = width_bucket(pages)
+        key = (padded, width)
+        slot = self.graphs.get(key)
+        if slot is None:
+            if len(self.graphs) >= MAX_GRAPHS:
+                return None
+            slot = self._capture(key, entries, starts, device_tokens)
+        else:
+            ctx = r.builder.build_decode(entries, starts, padded, width, slot["dev"])
+            if device_tokens is not None:
+                ctx.tokens[:len(entries)].copy_(device_tokens)
+            slot["graph"].replay()
+        self.replays += 1
+        self.launches += slot["kernels"]
+        return slot["logits"][:len(entries)]
+
+    def _capture(self, key, entries, starts, device_tokens):
+        r = self.runner
+        padded, width = key
+        paged = len(r.manager.paged_groups)
+        _, total = BatchBuilder.decode_layout(padded, width, paged)
+        dev = torch.empty(total, dtype=torch.int32, device=r.rt.device)
+        ctx = r.builder.build_decode(entries, starts, padded, width, dev)
+        if device_tokens is not None:
+            ctx.tokens[:len(entries)].copy_(device_tokens)
+        # the split of the context is part of the launch shape: fix it for the whole bucket
+        kv_heads = max((g.need.num_kv_heads for g in r.manager.paged_groups), default=1)
+        ctx.work["n_splits"] = ops.decode_splits(padded, kv_heads, width * r.manager.page_size)
+        r.model.forward(ctx, r.storage)             # eager once: scratch buffers reach their size
+        torch.cuda.synchronize(r.rt.device)
+        graph = torch.cuda.CUDAGraph()
+        before = ops.LAUNCHES
+        with torch.cuda.graph(graph):
+            logits = r.model.forward(ctx, r.storage)
+        kernels = ops.LAUNCHES - before
+        graph.replay()
+        slot = {"graph": graph, "dev": dev, "ctx": ctx, "logits": logits, "kernels": kernels}
+        self.graphs[key] = slot
+        return slot

@@ -42,6 +42,8 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
     # multiple of the page, so max_tokens / page_size pages always hold the live requests
     num_pages = (max_tokens + page_size - 1) // page_size
     runner = ModelRunner(model, page_size, num_pages, MAX_LIVE_REQUESTS)
+    if run_dtype == torch.bfloat16:
+        runner.enable_graphs()      # as serving does: steps of single tokens replay a captured graph
     for line in lines:
         line = line.strip()
         if not line:

@@ -29,6 +29,17 @@ class ModelRunner:
         self.storage = CacheStorage(self.manager, rt.device, rt.dtype)
         self.builder = BatchBuilder(self.manager, rt.device, model.plan.vocab_size, model.plan.max_positions)
         self.steps = 0
+        self.graphs = None          # DecodeGraphs when graph replay of decode steps is on
+
+    def enable_graphs(self) -> None:
+        """Replay decode steps (one token per request) from captured CUDA graphs."""
+        from .graphs import DecodeGraphs
+        if self.rt.device.type == "cuda":
+            self.graphs = DecodeGraphs(self)
+
+    @property
+    def graph_launches(self) -> int:
+        return self.graphs.launches if self.graphs is not None else 0
 
     # ------------------------------------------------------------------ requests
     def admit(self, request: Hashable) -> None:
@@ -63,6 +74,31 @@ class ModelRunner:
             starts.append(start)
         return self.builder.build(entries, starts)
 
+    def _graph_step(self, entries, device_tokens):
+        m = self.manager
+        self.builder.validate(entries)
+        starts = []
+        for e in entries:
+            if e.request not in m.lengths:
+                self.admit(e.request)
+            start = m.lengths[e.request]
+            if start + 1 > self.model.plan.max_positions:
+                raise ValueError(f"request {e.request!r} would pass the model's {self.model.plan.max_positions} positions")
+            m.grow(e.request, start + 1)
+            starts.append(start)
+        with torch.cuda.device(self.rt.device):
+            logits = self.graphs.run(entries, starts, device_tokens)
+        if logits is None:
+            return None
+        if any(e.want != (0,) and list(e.want) != [0] for e in entries):
+            rows = [i for i, e in enumerate(entries) if len(e.want)]
+            logits = logits[rows] if len(rows) != len(entries) else logits
+        for e, s in zip(entries, starts):
+            m.advance(e.request, s + 1)
+            m.trim(e.request)
+        self.steps += 1
+        return logits
+
     @torch.no_grad()
     def step(self, entries: Sequence[StepEntry], device_tokens: torch.Tensor | None = None) -> torch.Tensor:
         """Logits float32 [wanted, vocab] in the order of the entries and of their ``want``.
@@ -71,6 +107,10 @@ class ModelRunner:
         keeps the sampled tokens on the device between steps; the entries then only say how many."""
         if not entries:
             return torch.empty((0, self.model.plan.vocab_size), device=self.rt.device, dtype=torch.float32)
+        if self.graphs is not None and self.graphs.usable(entries):
+            logits = self._graph_step(entries, device_tokens)
+            if logits is not None:
+                return logits
         ctx = self.prepare(entries)
         if device_tokens is not None:
             ctx.tokens.copy_(device_tokens)

@@ -203,6 +203,8 @@ def _gemm_buffers(device, ws_floats: int, n_counters: int):
         ws = torch.empty(max(ws_floats, 2 * old[0].numel(), 1 << 20), device=device, dtype=torch.float32)
         cnt = torch.zeros(max(n_counters, 2 * old[1].numel(), 4096), device=device, dtype=torch.int32)
         status = old[2] if old[2] is not None else torch.zeros(1, device=device, dtype=torch.int32)
+        if key in _gemm_scratch:
+            _retired.append(_gemm_scratch[key])
         have = (ws, cnt, status)
         _gemm_scratch[key] = have
     return have
@@ -296,6 +298,7 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 # ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
 _SM_COUNT = 148
 _scratch: dict = {}
+_retired: list = []     # outgrown scratch buffers, never freed (graphs captured earlier point into them)
 
 
 def _decode_scratch(device, floats: int, ml_floats: int, counters: int):
@@ -311,6 +314,8 @@ def _decode_scratch(device, floats: int, ml_floats: int, counters: int):
         have = (torch.empty(grow(floats, o[0].numel()), device=device, dtype=torch.float32),
                 torch.empty(grow(ml_floats, o[1].numel()), device=device, dtype=torch.float32),
                 torch.zeros(grow(counters, o[2].numel()), device=device, dtype=torch.int32))
+        if key in _scratch:
+            _retired.append(_scratch[key])   # a captured graph may still hold these addresses: keep them alive
         _scratch[key] = have
     return have
 
