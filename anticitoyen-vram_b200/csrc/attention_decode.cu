@@ -28,14 +28,15 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    const int* __restrict__ dec_tokens, const int* __restrict__ dec_seqs,
                    const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride, int NH, int NKV,
-                   int page_size, int num_pages, float scale, int window, int n_splits, float* __restrict__ part_acc,
-                   float* __restrict__ part_ml, int* __restrict__ counters) {
+                   int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
+                   float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
     constexpr int TILE_BYTES = AD_TILE * D * 2;
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                                   // [16][D]
     unsigned char* k_s = smem + 16 * D * 2;                      // [2][64][D]
     unsigned char* v_s = k_s + 2 * TILE_BYTES;                   // [2][64][D]
+    int* pg_s = reinterpret_cast<int*>(v_s + 2 * TILE_BYTES);    // [pg_cap] pages of this CTA's key range
     __shared__ int is_last_s;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -59,20 +60,31 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
     }
 
+    // the block-table entries of this CTA's keys, read once (a tile's copies then wait for no lookup)
+    const int first_pg = page_shift >= 0 ? beg >> page_shift : beg / page_size;
+    const int n_pg = n_tiles > 0 ? (page_shift >= 0 ? (end - 1) >> page_shift : (end - 1) / page_size) - first_pg + 1 : 0;
+    const bool pg_cached = n_pg <= pg_cap;
+    if (pg_cached)
+        for (int i = tid; i < n_pg; i += AD_THREADS) pg_s[i] = bt[first_pg + i];
+    __syncthreads();
+
     auto load_tile = [&](int t, int stage) {
         const int j0 = beg + t * AD_TILE;
         for (int id = tid; id < AD_TILE * CH; id += AD_THREADS) {
             const int r = id / CH, c = id % CH;
             const int j = j0 + r;
-            const bf16* kr = nullptr;
-            const bf16* vr = nullptr;
-            if (j < end) {
-                kr = paged_row(k_pages, bt, j, kvh, NKV, page_size, num_pages, D);
-                vr = kr ? v_pages + (kr - k_pages) : nullptr;
+            bool ok = j < end;
+            size_t row_off = 0;
+            if (ok) {
+                const int pi = page_shift >= 0 ? j >> page_shift : j / page_size;
+                const int in_pg = page_shift >= 0 ? j & (page_size - 1) : j - pi * page_size;
+                const int pg = pg_cached ? pg_s[pi - first_pg] : bt[pi];
+                ok = pg >= 0 && pg < num_pages;
+                row_off = (((size_t)pg * NKV + kvh) * page_size + in_pg) * D + c * 8;
             }
             const int off = stage * TILE_BYTES + tile_off<D>(r, c);
-            cp_async16(smem_u32(k_s + off), kr ? (const void*)(kr + c * 8) : (const void*)k_pages, kr != nullptr);
-            cp_async16(smem_u32(v_s + off), vr ? (const void*)(vr + c * 8) : (const void*)v_pages, vr != nullptr);
+            cp_async16(smem_u32(k_s + off), ok ? (const void*)(k_pages + row_off) : (const void*)k_pages, ok);
+            cp_async16(smem_u32(v_s + off), ok ? (const void*)(v_pages + row_off) : (const void*)v_pages, ok);
         }
     };
 
@@ -252,19 +264,26 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
                          const int* block_table, int bt_stride, int NH, int NKV, int page_size, int num_pages,
                          float scale, int window, int n_splits, float* part_acc, float* part_ml, int* counters,
-                         cudaStream_t stream) {
-    const int smem = 16 * D * 2 + 4 * AD_TILE * D * 2;
-    static bool configured = false;
-    if (!configured) {
+                         int max_kv, cudaStream_t stream) {
+    int page_shift = -1;
+    for (int b = 0; b < 31; ++b)
+        if ((1 << b) == page_size) page_shift = b;
+    const int keys = window > 0 && window < max_kv ? window : max_kv;
+    const int chunk = (((keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
+    int pg_cap = chunk / page_size + 2;
+    if (pg_cap > 8192) pg_cap = 8192;
+    const int smem = 16 * D * 2 + 4 * AD_TILE * D * 2 + pg_cap * 4;
+    static int configured = 0;
+    if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
     dim3 grid(n_dec, NKV, n_splits);
     attn_decode_kernel<D><<<grid, AD_THREADS, smem, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
-        dec_seqs, kv_len, block_table, bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc,
-        part_ml, counters);
+        dec_seqs, kv_len, block_table, bt_stride, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
+        n_splits, part_acc, part_ml, counters);
     return acv_launch_status();
 }
 
@@ -276,7 +295,7 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
                                  const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int D,
                                  int page_size, int num_pages, float scale, int window, int n_splits, float* part_acc,
                                  float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
-                                 long long scratch_counters, cudaStream_t stream) {
+                                 long long scratch_counters, int max_kv, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH / NKV > 16 || n_splits < 1 || n_splits > 65535 || NKV > 65535) return ACV_ERR_SIZE;
     if (((uintptr_t)q & 15) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
@@ -289,7 +308,7 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
             return ACV_ERR_SCRATCH;
     }
 #define AD_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
-                bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, stream
+                bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, max_kv, stream
     switch (D) {
         case 64: return launch_decode<64>(AD_ARGS);
         case 128: return launch_decode<128>(AD_ARGS);

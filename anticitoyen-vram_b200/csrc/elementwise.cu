@@ -69,9 +69,90 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delt
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<T>(round_to<T>(row[i] * rs) * w[i]);
 }
 
+// Vector form: the row is read once with 16-byte loads and stays in registers (up to VCH chunks of
+// 16 bytes per thread).  Same arithmetic and the same rounding points as the kernel above.
+template <typename T, int VCH>
+__global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ delta, const float* __restrict__ w,
+                                       T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
+    constexpr int E = 16 / sizeof(T);          // elements per 16-byte chunk
+    __shared__ float red[32];
+    const int r_out = blockIdx.x;
+    const int r_in = rows ? rows[r_out] : r_out;
+    const int n_chunks = H / E;
+    uint4* xr = reinterpret_cast<uint4*>(x + (size_t)r_in * H);
+    const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + (size_t)r_in * H) : nullptr;
+    float v[VCH][E];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VCH; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n_chunks) {
+            uint4 xa = xr[c];
+            const T* xe = reinterpret_cast<const T*>(&xa);
+            if (dr) {
+                uint4 da = dr[c];
+                const T* de = reinterpret_cast<const T*>(&da);
+                T summed[E];
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    summed[e] = from_f32<T>(to_f32(xe[e]) + to_f32(de[e]));
+                    v[i][e] = to_f32(summed[e]);
+                }
+                if (!rows) xr[c] = *reinterpret_cast<const uint4*>(summed);
+            } else {
+#pragma unroll
+                for (int e = 0; e < E; ++e) v[i][e] = to_f32(xe[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) ss += v[i][e] * v[i][e];
+        }
+    }
+    ss = block_sum(ss, red);
+    const float rs = rsqrtf(ss / (float)H + eps);
+    uint4* o = reinterpret_cast<uint4*>(out + (size_t)r_out * H);
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+#pragma unroll
+    for (int i = 0; i < VCH; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+        if (c < n_chunks) {
+            T res[E];
+#pragma unroll
+            for (int e4 = 0; e4 < E / 4; ++e4) {
+                const float4 ww = w4[c * (E / 4) + e4];
+                res[e4 * 4 + 0] = from_f32<T>(round_to<T>(v[i][e4 * 4 + 0] * rs) * ww.x);
+                res[e4 * 4 + 1] = from_f32<T>(round_to<T>(v[i][e4 * 4 + 1] * rs) * ww.y);
+                res[e4 * 4 + 2] = from_f32<T>(round_to<T>(v[i][e4 * 4 + 2] * rs) * ww.z);
+                res[e4 * 4 + 3] = from_f32<T>(round_to<T>(v[i][e4 * 4 + 3] * rs) * ww.w);
+            }
+            o[c] = *reinterpret_cast<const uint4*>(res);
+        }
+    }
+}
+
 template <typename T>
 static int launch_add_rmsnorm(void* x, const void* delta, const float* w, void* out, const int* rows, int n_rows,
                               int H, float eps, cudaStream_t stream) {
+    constexpr int E = 16 / sizeof(T);
+    const bool aligned = H % E == 0 && !((uintptr_t)x & 15) && !((uintptr_t)out & 15) && !((uintptr_t)w & 15) &&
+                         (!delta || !((uintptr_t)delta & 15));
+    if (aligned) {
+        const int n_chunks = H / E;
+        int threads = 128;
+        while (threads < 1024 && threads < n_chunks) threads *= 2;
+        const int per = (n_chunks + threads - 1) / threads;
+        if (per <= 1) {
+            add_rmsnorm_vec_kernel<T, 1><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
+            return acv_launch_status();
+        }
+        if (per <= 2) {
+            add_rmsnorm_vec_kernel<T, 2><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
+            return acv_launch_status();
+        }
+        if (per <= 4) {
+            add_rmsnorm_vec_kernel<T, 4><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
+            return acv_launch_status();
+        }
+    }
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return ACV_ERR_SIZE;
     if (smem > 48 * 1024) {

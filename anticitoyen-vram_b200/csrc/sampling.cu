@@ -102,9 +102,77 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
     if (threadIdx.x == 0) out[blockIdx.x] = bi;
 }
 
+// Wide rows: each row is cut into ARG_PARTS slices, one block per slice leaves (value, index) in
+// scratch, and the block that arrives last at a row picks among the slices in slice order (lowest
+// index among equal values, as above).  No block waits for another.
+#define ARG_PARTS 16
+#define ARG_MAX_ROWS 4096
+static __device__ float arg_part_val[ARG_MAX_ROWS * ARG_PARTS];
+static __device__ int arg_part_idx[ARG_MAX_ROWS * ARG_PARTS];
+static __device__ int arg_counter[ARG_MAX_ROWS];
+
+__global__ void __launch_bounds__(256)
+argmax_split_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__ out) {
+    __shared__ float redf[32];
+    __shared__ int redi[32];
+    __shared__ int last_s;
+    const int row = blockIdx.x, part = blockIdx.y;
+    const int span = ((V + ARG_PARTS - 1) / ARG_PARTS + 3) & ~3;
+    const int lo = part * span, hi = min(V, lo + span);
+    const float* r = logits + (size_t)row * ld;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+        const float v = r[i];
+        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    if (lane == 0) { redf[warp] = best; redi[warp] = bi; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < nwarp ? redf[lane] : -INFINITY;
+        bi = lane < nwarp ? redi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (lane == 0) {
+            arg_part_val[row * ARG_PARTS + part] = best;
+            arg_part_idx[row * ARG_PARTS + part] = bi;
+            __threadfence();
+            last_s = atomicAdd(&arg_counter[row], 1) == ARG_PARTS - 1;
+        }
+    }
+    __syncthreads();
+    if (last_s && threadIdx.x == 0) {
+        __threadfence();
+        float b = -INFINITY;
+        int idx = 0x7fffffff;
+        for (int q = 0; q < ARG_PARTS; ++q) {
+            const float v = __ldcg(&arg_part_val[row * ARG_PARTS + q]);
+            const int i = __ldcg(&arg_part_idx[row * ARG_PARTS + q]);
+            if (v > b || (v == b && i < idx)) { b = v; idx = i; }
+        }
+        out[row] = idx == 0x7fffffff ? 0 : idx;
+        arg_counter[row] = 0;
+    }
+}
+
 ACV_API int acv_argmax(const float* logits, int ld, int rows, int V, int* out, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (V <= 0) return ACV_ERR_SIZE;
+    if (V >= 16384 && rows <= ARG_MAX_ROWS) {
+        argmax_split_kernel<<<dim3(rows, ARG_PARTS), 256, 0, stream>>>(logits, ld, V, out);
+        return acv_launch_status();
+    }
     argmax_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, ld, V, out);
     return acv_launch_status();
 }

@@ -62,7 +62,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, P],
-        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
@@ -330,7 +330,7 @@ def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                      dec_tokens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, kv_len: torch.Tensor,
                      block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                     window: int, n_splits: int) -> torch.Tensor:
+                     window: int, n_splits: int, max_kv: int = 0) -> torch.Tensor:
     """Attention of requests that bring one token each, over their pages, split over the context."""
     n_rep = num_heads // num_kv_heads
     parts = n_dec * num_kv_heads * n_splits if n_splits > 1 else 0
@@ -339,7 +339,7 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(dec_tokens), _p(dec_seqs), n_dec,
         _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim, k_pages.shape[2],
         k_pages.shape[0], scale, window, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
-        _stream()), "attention_decode")
+        max_kv or block_table.shape[1] * k_pages.shape[2], _stream()), "attention_decode")
     return out
 
 
@@ -377,7 +377,7 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
         kv = min(w["max_dec_kv"], window) if window > 0 else w["max_dec_kv"]
         attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
                          block_table, num_heads, num_kv_heads, head_dim, scale, window,
-                         w.get("n_splits") or decode_splits(w["n_dec"], num_kv_heads, kv))
+                         w.get("n_splits") or decode_splits(w["n_dec"], num_kv_heads, kv), w["max_dec_kv"])
     if w["n_tiles"]:
         attention_chunk(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
                         block_table, num_heads, num_kv_heads, head_dim, scale, window)
