@@ -316,3 +316,65 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
     }
 #undef AD_ARGS
 }
+
+// ----------------------------------------------------------------------------- entry point without allocation
+// See no_alloc.h.  The split-KV kernel needs scratch for the partial results of the splits; here it
+// lives in a file-scope device array of fixed size instead of memory the caller allocates.
+#include "no_alloc.h"
+
+#define AD_STATIC_FLOATS (1 << 20)   /* 4 MiB on every GPU that loads this library, until the process exits */
+static __device__ __align__(256) float ad_static_scratch[AD_STATIC_FLOATS];
+
+// In host code `ad_static_scratch` is only a handle for the runtime; the device address has to be
+// asked for, once per device, with that device current.
+static float* ad_static_address(int* error) {
+    static float* address[64] = {nullptr};
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess || device < 0 || device >= 64) {
+        *error = e != cudaSuccess ? (int)e : ACV_ERR_SIZE;
+        return nullptr;
+    }
+    if (!address[device]) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, ad_static_scratch);
+        if (e != cudaSuccess) {
+            *error = (int)e;
+            return nullptr;
+        }
+        address[device] = (float*)p;
+    }
+    *error = 0;
+    return address[device];
+}
+
+ACV_API long long acv_attention_decode_static_capacity(void) { return AD_STATIC_FLOATS; }
+
+ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                                        const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec,
+                                        const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV,
+                                        int D, int page_size, int num_pages, float scale, int window, int n_splits,
+                                        int max_kv, cudaStream_t stream) {
+    if (n_dec <= 0) return 0;
+    if (NKV <= 0 || NH % NKV || n_splits < 1) return ACV_ERR_SIZE;
+    const long long n_rep = NH / NKV;
+    const long long parts = n_splits > 1 ? (long long)n_dec * NKV * n_splits : 0;
+    const long long acc_floats = parts * n_rep * D;
+    const long long ml_floats = parts * n_rep * 2;
+    const long long counters = (long long)n_dec * NKV;
+    // layout inside the array: [partial accumulators | partial (max, sum) | one counter per (request, kv-head)]
+    if (acc_floats + ml_floats + counters > AD_STATIC_FLOATS) return ACV_ERR_SCRATCH;
+    int error = 0;
+    float* base = ad_static_address(&error);
+    if (!base) return error;
+    float* part_acc = base;
+    float* part_ml = base + acc_floats;
+    int* cnt = reinterpret_cast<int*>(base + acc_floats + ml_floats);
+    // the array keeps what the last call left, and a call with another shape puts its counters
+    // elsewhere: the counters of this call are cleared on the stream before the kernel runs
+    cudaError_t e = cudaMemsetAsync(cnt, 0, (size_t)counters * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+    return acv_attention_decode(q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len,
+                                block_table, bt_stride, NH, NKV, D, page_size, num_pages, scale, window, n_splits,
+                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, stream);
+}
