@@ -24,14 +24,15 @@ __global__ void __launch_bounds__(AC_THREADS)
 attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                   const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
-                  const int* __restrict__ block_table, int bt_stride, int NH, int NKV, int page_size, int num_pages,
-                  float scale, int window) {
+                  const int* __restrict__ block_table, int bt_stride, int NH, int NKV, int page_size, int page_shift,
+                  int pg_cap, int num_pages, float scale, int window) {
     constexpr int CH = D / 8;
     constexpr int TILE_BYTES = AC_BN * D * 2;
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                       // [64][D]
     unsigned char* k_s = smem + AC_BM * D * 2;       // [2][64][D]
     unsigned char* v_s = k_s + 2 * TILE_BYTES;       // [2][64][D]
+    int* pg_s = reinterpret_cast<int*>(v_s + 2 * TILE_BYTES);   // [pg_cap] pages of the keys this tile reads
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
@@ -54,20 +55,31 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
     }
 
+    // the block-table entries of the keys this tile reads, looked up once
+    const int first_pg = page_shift >= 0 ? j_first >> page_shift : j_first / page_size;
+    const int n_pg = (page_shift >= 0 ? hi >> page_shift : hi / page_size) - first_pg + 1;
+    const bool pg_cached = n_pg <= pg_cap;
+    if (pg_cached)
+        for (int i = tid; i < n_pg; i += AC_THREADS) pg_s[i] = bt[first_pg + i];
+    __syncthreads();
+
     auto load_tile = [&](int t, int stage) {
         const int j0 = j_first + t * AC_BN;
         for (int id = tid; id < AC_BN * CH; id += AC_THREADS) {
             const int r = id / CH, c = id % CH;
             const int j = j0 + r;
-            const bf16* kr = nullptr;
-            const bf16* vr = nullptr;
-            if (j <= hi && j >= lo) {
-                kr = paged_row(k_pages, bt, j, kvh, NKV, page_size, num_pages, D);
-                vr = kr ? v_pages + (kr - k_pages) : nullptr;
+            bool ok = j <= hi && j >= lo;
+            size_t row_off = 0;
+            if (ok) {
+                const int pi = page_shift >= 0 ? j >> page_shift : j / page_size;
+                const int in_pg = page_shift >= 0 ? j & (page_size - 1) : j - pi * page_size;
+                const int pg = pg_cached ? pg_s[pi - first_pg] : bt[pi];
+                ok = pg >= 0 && pg < num_pages;
+                row_off = (((size_t)pg * NKV + kvh) * page_size + in_pg) * D + c * 8;
             }
             const int off = stage * TILE_BYTES + tile_off<D>(r, c);
-            cp_async16(smem_u32(k_s + off), kr ? (const void*)(kr + c * 8) : (const void*)k_pages, kr != nullptr);
-            cp_async16(smem_u32(v_s + off), vr ? (const void*)(vr + c * 8) : (const void*)v_pages, vr != nullptr);
+            cp_async16(smem_u32(k_s + off), ok ? (const void*)(k_pages + row_off) : (const void*)k_pages, ok);
+            cp_async16(smem_u32(v_s + off), ok ? (const void*)(v_pages + row_off) : (const void*)v_pages, ok);
         }
     };
 
@@ -198,18 +210,23 @@ template <int D>
 static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                         const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
                         const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int page_size,
-                        int num_pages, float scale, int window, cudaStream_t stream) {
-    const int smem = AC_BM * D * 2 + 4 * AC_BN * D * 2;
-    static bool configured = false;
-    if (!configured) {
+                        int num_pages, float scale, int window, int max_kv, cudaStream_t stream) {
+    int page_shift = -1;
+    for (int b = 0; b < 31; ++b)
+        if ((1 << b) == page_size) page_shift = b;
+    int pg_cap = max_kv / page_size + 2;
+    if (pg_cap > 16384) pg_cap = 16384;
+    const int smem = AC_BM * D * 2 + 4 * AC_BN * D * 2 + pg_cap * 4;
+    static int configured = 0;
+    if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_chunk_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
     dim3 grid(n_tiles, NH);
     attn_chunk_kernel<D><<<grid, AC_THREADS, smem, stream>>>(
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, tile_seq,
-        tile_q0, cu_q, kv_len, block_table, bt_stride, NH, NKV, page_size, num_pages, scale, window);
+        tile_q0, cu_q, kv_len, block_table, bt_stride, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window);
     return acv_launch_status();
 }
 
@@ -218,7 +235,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
 ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                 const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles,
                                 const int* cu_q, const int* kv_len, const int* block_table, int bt_stride, int NH,
-                                int NKV, int D, int page_size, int num_pages, float scale, int window,
+                                int NKV, int D, int page_size, int num_pages, float scale, int window, int max_kv,
                                 cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535) return ACV_ERR_SIZE;
@@ -226,7 +243,7 @@ ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_
         ((uintptr_t)out & 3) || (out_stride & 1))
         return ACV_ERR_ALIGN;
 #define AC_ARGS q, q_stride, out, out_stride, k_pages, v_pages, tile_seq, tile_q0, n_tiles, cu_q, kv_len, block_table, \
-                bt_stride, NH, NKV, page_size, num_pages, scale, window, stream
+                bt_stride, NH, NKV, page_size, num_pages, scale, window, max_kv, stream
     switch (D) {
         case 64: return launch_chunk<64>(AC_ARGS);
         case 128: return launch_chunk<128>(AC_ARGS);

@@ -186,9 +186,44 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
     }
 }
 
+// 16 bytes of gate and of up per thread (I a multiple of the vector width, pointers aligned)
+template <typename T>
+__global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total_chunks) {
+    constexpr int E = 16 / sizeof(T);
+    const int chunks_per_row = I / E;
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_chunks;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = idx / chunks_per_row;
+        const int c = (int)(idx - t * chunks_per_row);
+        const uint4 ga = *reinterpret_cast<const uint4*>(gu + t * 2 * I + (size_t)c * E);
+        const uint4 ua = *reinterpret_cast<const uint4*>(gu + t * 2 * I + I + (size_t)c * E);
+        const T* g = reinterpret_cast<const T*>(&ga);
+        const T* u = reinterpret_cast<const T*>(&ua);
+        T res[E];
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float gv = to_f32(g[e]);
+            res[e] = from_f32<T>(round_to<T>(gv / (1.f + expf(-gv))) * to_f32(u[e]));
+        }
+        *reinterpret_cast<uint4*>(out + t * I + (size_t)c * E) = *reinterpret_cast<const uint4*>(res);
+    }
+}
+
 ACV_API int acv_swiglu(const void* gu, void* out, int T, int I, int dtype, cudaStream_t stream) {
     const size_t total = (size_t)T * I;
     if (total == 0) return 0;
+    {
+        const int E = dtype == ACV_F32 ? 4 : 8;
+        if ((dtype == ACV_F32 || dtype == ACV_BF16) && I % E == 0 && !((uintptr_t)gu & 15) && !((uintptr_t)out & 15)) {
+            const size_t chunks = total / E;
+            const int blocks = (int)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
+            if (dtype == ACV_F32)
+                swiglu_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, chunks);
+            else
+                swiglu_vec_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, I, chunks);
+            return acv_launch_status();
+        }
+    }
     const int threads = 256;
     const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
     if (dtype == ACV_F32)

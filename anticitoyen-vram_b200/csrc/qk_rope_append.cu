@@ -84,6 +84,88 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, int row_stride, 
     }
 }
 
+// Vector form for head sizes 32, 64, 128, 256 with the whole head rotated (or no rotation): a lane holds
+// D/32 neighbouring elements, loaded and stored as one vector; its rotation partner (i +- D/2) sits in
+// lane ^ 16, so the exchange is one shuffle per element and no shared memory is used.
+template <typename T, int VEC>
+__global__ void qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, int row_stride, int NH, int NKV,
+                                               const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
+                                               const float* __restrict__ cos_sin, int table_rows,
+                                               const int* __restrict__ positions, const int* __restrict__ seq_of_token,
+                                               const int* __restrict__ block_table, int bt_stride,
+                                               T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size,
+                                               int num_pages) {
+    constexpr int D = VEC * 32;
+    struct __align__(sizeof(T) * VEC) Vec { T e[VEC]; };
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * QRA_WARPS + warp;
+    const int t = blockIdx.x;
+    if (head >= NH + 2 * NKV) return;
+    T* src = qkv + (size_t)t * row_stride + (size_t)head * D;
+    const bool is_q = head < NH;
+    const bool is_k = !is_q && head < NH + NKV;
+    const bool is_v = !is_q && !is_k;
+    const float* w = is_q ? q_w : (is_k ? k_w : nullptr);
+    const int pos = positions[t];
+
+    T* dst = nullptr;
+    if (is_q) {
+        dst = src;
+    } else if (k_pages) {
+        const int seq = seq_of_token[t];
+        const int pg = block_table[(size_t)seq * bt_stride + pos / page_size];
+        if (pg >= 0 && pg < num_pages) {
+            const int kvh = is_k ? head - NH : head - NH - NKV;
+            dst = (is_k ? k_pages : v_pages) + (((size_t)pg * NKV + kvh) * page_size + (pos % page_size)) * D;
+        }
+    } else if (is_k) {
+        dst = src;
+    }
+    if (!dst) return;
+
+    const Vec in = *reinterpret_cast<const Vec*>(src + lane * VEC);
+    float a[VEC];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC; ++i) {
+        a[i] = to_f32(in.e[i]);
+        ss += a[i] * a[i];
+    }
+    if (w) {
+        ss = warp_sum(ss);
+        const float inv = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) a[i] = a[i] * inv * w[lane * VEC + i];
+    }
+    const bool rotate = cos_sin && !is_v && pos >= 0 && pos < table_rows;
+    Vec res;
+    if (cos_sin && !is_v) {    // warp-uniform: the shuffles are executed by all lanes
+        const float* cs = cos_sin + (size_t)(rotate ? pos : 0) * D;
+        const int i0 = (lane & 15) * VEC;           // index of this lane's first angle
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            const float partner = __shfl_xor_sync(0xffffffffu, a[i], 16);
+            const float c = cs[i0 + i], sn = cs[D / 2 + i0 + i];
+            const float o = lane < 16 ? a[i] * c - partner * sn : a[i] * c + partner * sn;
+            res.e[i] = from_f32<T>(rotate ? o : a[i]);
+        }
+    } else {
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) res.e[i] = from_f32<T>(a[i]);
+    }
+    *reinterpret_cast<Vec*>(dst + lane * VEC) = res;
+}
+
+template <typename T, int VEC>
+static void launch_qra_vec(dim3 grid, cudaStream_t stream, void* qkv, int row_stride, int NH, int NKV, const float* q_w,
+                           const float* k_w, float eps, const float* cos_sin, int table_rows, const int* positions,
+                           const int* seq_of_token, const int* block_table, int bt_stride, void* k_pages, void* v_pages,
+                           int page_size, int num_pages) {
+    qk_norm_rope_append_vec_kernel<T, VEC><<<grid, QRA_WARPS * 32, 0, stream>>>(
+        (T*)qkv, row_stride, NH, NKV, q_w, k_w, eps, cos_sin, table_rows, positions, seq_of_token, block_table,
+        bt_stride, (T*)k_pages, (T*)v_pages, page_size, num_pages);
+}
+
 ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, int NKV, int D, const float* q_w,
                                     const float* k_w, float eps, const float* cos_sin, int rot, int table_rows,
                                     const int* positions, const int* seq_of_token, const int* block_table,
@@ -93,6 +175,27 @@ ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, in
     if (D <= 0 || D > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
     const int heads = NH + 2 * NKV;
     dim3 grid(T, (heads + QRA_WARPS - 1) / QRA_WARPS);
+    if (dtype != ACV_F32 && dtype != ACV_BF16) return ACV_ERR_DTYPE;
+    // vector form when a lane's elements make an aligned vector and the whole head rotates
+    const int vec = D / 32;
+    const size_t esz = dtype == ACV_F32 ? 4 : 2;
+    const bool vec_ok = D % 32 == 0 && (vec == 1 || vec == 2 || vec == 4 || vec == 8) && (!cos_sin || rot == D) &&
+                        vec * esz <= 16 && !((uintptr_t)qkv % (vec * esz)) && !((row_stride * esz) % (vec * esz)) &&
+                        (!k_pages || (!((uintptr_t)k_pages % (vec * esz)) && !((uintptr_t)v_pages % (vec * esz))));
+    if (vec_ok) {
+#define QRA_VEC(TT, VV)                                                                                                 \
+    launch_qra_vec<TT, VV>(grid, stream, qkv, row_stride, NH, NKV, q_w, k_w, eps, cos_sin, table_rows, positions,       \
+                           seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size, num_pages)
+        if (dtype == ACV_F32) {
+            if (vec == 1) QRA_VEC(float, 1); else if (vec == 2) QRA_VEC(float, 2); else if (vec == 4) QRA_VEC(float, 4);
+            else return ACV_ERR_SIZE;
+        } else {
+            if (vec == 1) QRA_VEC(bf16, 1); else if (vec == 2) QRA_VEC(bf16, 2); else if (vec == 4) QRA_VEC(bf16, 4);
+            else QRA_VEC(bf16, 8);
+        }
+#undef QRA_VEC
+        return acv_launch_status();
+    }
     const size_t smem = (size_t)QRA_WARPS * D * sizeof(float);
     if (dtype == ACV_F32)
         qk_norm_rope_append_kernel<float><<<grid, QRA_WARPS * 32, smem, stream>>>(

@@ -63,7 +63,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, P],
-        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P],
+        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
         "acv_sample": [P, I, I, I, P, P, P, P, P, P, P, P, P],
@@ -351,7 +351,8 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
     _check(library().acv_attention_chunk(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0), n_tiles,
         _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim,
-        k_pages.shape[2], k_pages.shape[0], scale, window, _stream()), "attention_chunk")
+        k_pages.shape[2], k_pages.shape[0], scale, window, block_table.shape[1] * k_pages.shape[2], _stream()),
+        "attention_chunk")
     return out
 
 
