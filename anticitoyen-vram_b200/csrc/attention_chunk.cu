@@ -34,6 +34,8 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     unsigned char* v_s = k_s + 2 * TILE_BYTES;       // [2][64][D]
     int* pg_s = reinterpret_cast<int*>(v_s + 2 * TILE_BYTES);   // [pg_cap] pages of the keys this tile reads
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int seq = tile_seq[blockIdx.x], q0 = tile_q0[blockIdx.x];
     const int h = blockIdx.y;
@@ -224,7 +226,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
         configured = smem;
     }
     dim3 grid(n_tiles, NH);
-    attn_chunk_kernel<D><<<grid, AC_THREADS, smem, stream>>>(
+    acv_launch(PDL_MISC, attn_chunk_kernel<D>, grid, AC_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, tile_seq,
         tile_q0, cu_q, kv_len, block_table, bt_stride, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window);
     return acv_launch_status();

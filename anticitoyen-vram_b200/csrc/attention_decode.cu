@@ -39,6 +39,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     int* pg_s = reinterpret_cast<int*>(v_s + 2 * TILE_BYTES);    // [pg_cap] pages of this CTA's key range
     __shared__ int is_last_s;
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tok = dec_tokens[item], seq = dec_seqs[item];
@@ -280,7 +282,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
         configured = smem;
     }
     dim3 grid(n_dec, NKV, n_splits);
-    attn_decode_kernel<D><<<grid, AD_THREADS, smem, stream>>>(
+    acv_launch(PDL_ATTN, attn_decode_kernel<D>, grid, AD_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
         dec_seqs, kv_len, block_table, bt_stride, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
         n_splits, part_acc, part_ml, counters);

@@ -13,6 +13,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, T* __restrict__ out,
                              int H, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     int tok = tokens[t];
     tok = tok < 0 ? 0 : (tok >= V ? V - 1 : tok);  // the host validates ids; never a bad address
@@ -32,9 +34,9 @@ ACV_API int acv_embed(const void* table, const int* tokens, void* out, int T, in
                       cudaStream_t stream) {
     if (T <= 0) return 0;
     if (dtype == ACV_F32)
-        embed_kernel<float><<<T, 128, 0, stream>>>((const float*)table, tokens, (float*)out, H, V);
+        acv_launch(PDL_MISC, embed_kernel<float>, T, 128, 0, stream, (const float*)table, tokens, (float*)out, H, V);
     else if (dtype == ACV_BF16)
-        embed_kernel<bf16><<<T, 128, 0, stream>>>((const bf16*)table, tokens, (bf16*)out, H, V);
+        acv_launch(PDL_MISC, embed_kernel<bf16>, T, 128, 0, stream, (const bf16*)table, tokens, (bf16*)out, H, V);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();
@@ -76,6 +78,8 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ 
                                        T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
     constexpr int E = 16 / sizeof(T);          // elements per 16-byte chunk
     __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r_out = blockIdx.x;
     const int r_in = rows ? rows[r_out] : r_out;
     const int n_chunks = H / E;
@@ -141,15 +145,15 @@ static int launch_add_rmsnorm(void* x, const void* delta, const float* w, void* 
         while (threads < 1024 && threads < n_chunks) threads *= 2;
         const int per = (n_chunks + threads - 1) / threads;
         if (per <= 1) {
-            add_rmsnorm_vec_kernel<T, 1><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
+            acv_launch(PDL_NORM, add_rmsnorm_vec_kernel<T, 1>, n_rows, threads, 0, stream, (T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
             return acv_launch_status();
         }
         if (per <= 2) {
-            add_rmsnorm_vec_kernel<T, 2><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
+            acv_launch(PDL_NORM, add_rmsnorm_vec_kernel<T, 2>, n_rows, threads, 0, stream, (T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
             return acv_launch_status();
         }
         if (per <= 4) {
-            add_rmsnorm_vec_kernel<T, 4><<<n_rows, threads, 0, stream>>>((T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
+            acv_launch(PDL_NORM, add_rmsnorm_vec_kernel<T, 4>, n_rows, threads, 0, stream, (T*)x, (const T*)delta, w, (T*)out, rows, H, eps);
             return acv_launch_status();
         }
     }
@@ -191,6 +195,8 @@ template <typename T>
 __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out, int I, size_t total_chunks) {
     constexpr int E = 16 / sizeof(T);
     const int chunks_per_row = I / E;
+    pdl_launch_dependents();
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total_chunks;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t t = idx / chunks_per_row;
@@ -218,9 +224,9 @@ ACV_API int acv_swiglu(const void* gu, void* out, int T, int I, int dtype, cudaS
             const size_t chunks = total / E;
             const int blocks = (int)((chunks + 255) / 256 < 148 * 16 ? (chunks + 255) / 256 : 148 * 16);
             if (dtype == ACV_F32)
-                swiglu_vec_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gu, (float*)out, I, chunks);
+                acv_launch(PDL_ACT, swiglu_vec_kernel<float>, blocks, 256, 0, stream, (const float*)gu, (float*)out, I, chunks);
             else
-                swiglu_vec_kernel<bf16><<<blocks, 256, 0, stream>>>((const bf16*)gu, (bf16*)out, I, chunks);
+                acv_launch(PDL_ACT, swiglu_vec_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)gu, (bf16*)out, I, chunks);
             return acv_launch_status();
         }
     }
@@ -234,3 +240,6 @@ ACV_API int acv_swiglu(const void* gu, void* out, int T, int I, int dtype, cudaS
         return ACV_ERR_DTYPE;
     return acv_launch_status();
 }
+
+// Bit set of the kernel classes (PDL_* in common.cuh) launched with programmatic stream serialization; 0: none.
+ACV_API void acv_set_pdl(int classes) { acv_pdl_flag = classes; }

@@ -112,6 +112,7 @@ struct GemmParams {
     int swap;               // 0: A = x (rows = tokens), 1: A = weight (rows = features)
     int out_f32;
     int tiles_a, tiles_b, splits, kb_per_split, n_kb;
+    int stages;             // pipeline depth (2..8); shared memory = stages * (128 + BN) * 128 bytes
     void* C;
     float* workspace;       // [tiles][splits][BN][128] floats when splits > 1
     int* counters;          // [tiles], zero before and after
@@ -121,9 +122,9 @@ struct GemmParams {
 template <int BN>
 struct GemmShape {
     static constexpr int STAGE_BYTES = (GT_BM + BN) * GT_BK * 2;
-    static constexpr int STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
+    static constexpr int MAX_STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;     // two accumulator buffers; a power of two
-    static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/; }
 };
 
 template <int BN>
@@ -133,18 +134,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     extern __shared__ unsigned char smem_raw[];
     // operand tiles start on a 1024-byte boundary of the shared window (the swizzle pattern is anchored there)
     unsigned char* tiles = smem_raw + ((1024u - (gt_smem(smem_raw) & 1023u)) & 1023u);
-    uint64_t* bars = (uint64_t*)(tiles + S::STAGES * S::STAGE_BYTES);
+    const int STAGES = p.stages;
+    uint64_t* bars = (uint64_t*)(tiles + STAGES * S::STAGE_BYTES);
     // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
-    const uint32_t full0 = gt_smem(bars), empty0 = full0 + 8 * S::STAGES;
-    const uint32_t tfull0 = empty0 + 8 * S::STAGES, tempty0 = tfull0 + 16;
+    const uint32_t full0 = gt_smem(bars), empty0 = full0 + 8 * STAGES;
+    const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
     __shared__ int last_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         abort_s = 0;
-        for (int s = 0; s < S::STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -163,14 +166,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            uint32_t it = 0;
+            pdl_wait();             // the activations are the predecessor's output
+            int s = 0;              // stage of the current k-block, and the parity its "empty" barrier is awaited with
+            uint32_t ph = 0;
             for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x) {
                 const int split = item % p.splits, tile = item / p.splits;
                 const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % S::STAGES;
-                    const uint32_t ph = (it / S::STAGES) & 1;
+                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 1); break; }
                     mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
                     const uint32_t a_dst = tiles_addr + s * S::STAGE_BYTES;
@@ -183,7 +186,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(BN);
-            uint32_t it = 0, local = 0;
+            uint32_t local = 0, ph = 0;
+            int s = 0;
             for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
                 const int split = item % p.splits;
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
@@ -192,9 +196,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BN;
                 bool failed = false;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % S::STAGES;
-                    const uint32_t ph = (it / S::STAGES) & 1;
+                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     if (!mbar_wait(full0 + 8 * s, ph, &abort_s)) { abort_s = 1; atomicExch(p.status, 3); failed = true; break; }
                     tc_fence_after();
                     const uint32_t a_addr = tiles_addr + s * S::STAGE_BYTES, b_addr = a_addr + GT_BM * GT_BK * 2;
@@ -211,6 +213,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         // ------------------------------------------------------------------ epilogue (warps 2..5)
         const int wq = warp & 3;                    // the 32 tensor-memory lanes this warp may read
         const int et = threadIdx.x - 64;            // 0..127 among the epilogue threads
+        pdl_wait();                                 // results, workspace and counters are shared with earlier kernels
         uint32_t local = 0;
         for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
             const int split = item % p.splits, tile = item / p.splits;
@@ -354,15 +357,28 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld,
 }
 
 template <int BN>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int sm_count, int stages,
+                       cudaStream_t stream) {
     using S = GemmShape<BN>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SMEM);
+    if (stages < 2) stages = 2;
+    if (stages > S::MAX_STAGES) stages = S::MAX_STAGES;
+    p.stages = stages;
+    const int smem = S::smem_bytes(stages);
+    static int configured = 0;
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured = smem;
     }
-    gemm_tc_kernel<BN><<<grid, GT_THREADS, S::SMEM, stream>>>(ma, mb, p);
+    // CTAs that fit one SM: by shared memory and by tensor-memory columns (512 in all)
+    int per_sm = (227 * 1024) / (smem + 1024);
+    if (per_sm > 512 / S::TMEM_COLS) per_sm = 512 / S::TMEM_COLS;
+    if (per_sm < 1) per_sm = 1;
+    if (per_sm > 4) per_sm = 4;
+    const long long items = (long long)p.tiles_a * p.tiles_b * p.splits;
+    const long long cap = (long long)sm_count * per_sm;
+    const int grid = (int)(items < cap ? items : cap);
+    acv_launch(PDL_GEMM, gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
     return acv_launch_status();
 }
 
@@ -372,7 +388,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, const GemmP
 // status: one int, 0 unless a bounded wait inside the kernel ran out.
 ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
                         int out_f32, int swap, int bn, int splits, float* workspace, long long workspace_floats,
-                        int* counters, long long n_counters, int* status, int sm_count, cudaStream_t stream) {
+                        int* counters, long long n_counters, int* status, int sm_count, int stages,
+                        cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACV_ERR_ALIGN;
     GemmParams p;
@@ -397,14 +414,12 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
     if (rc) return rc;
     rc = make_map(&mb, b_ptr, p.RB, K, swap ? ldx : ldw, bn);
     if (rc) return rc;
-    const int items = (int)(tiles * p.splits);
-    const int grid = items < sm_count ? items : sm_count;
     switch (bn) {
-        case 16: return launch_gemm<16>(ma, mb, p, grid, stream);
-        case 32: return launch_gemm<32>(ma, mb, p, grid, stream);
-        case 64: return launch_gemm<64>(ma, mb, p, grid, stream);
-        case 128: return launch_gemm<128>(ma, mb, p, grid, stream);
-        case 256: return launch_gemm<256>(ma, mb, p, grid, stream);
+        case 16: return launch_gemm<16>(ma, mb, p, sm_count, stages, stream);
+        case 32: return launch_gemm<32>(ma, mb, p, sm_count, stages, stream);
+        case 64: return launch_gemm<64>(ma, mb, p, sm_count, stages, stream);
+        case 128: return launch_gemm<128>(ma, mb, p, sm_count, stages, stream);
+        case 256: return launch_gemm<256>(ma, mb, p, sm_count, stages, stream);
         default: return ACV_ERR_SIZE;
     }
 }

@@ -97,6 +97,8 @@ __global__ void qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, int row_stri
                                                int num_pages) {
     constexpr int D = VEC * 32;
     struct __align__(sizeof(T) * VEC) Vec { T e[VEC]; };
+    pdl_launch_dependents();
+    pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int head = blockIdx.y * QRA_WARPS + warp;
     const int t = blockIdx.x;
@@ -161,7 +163,7 @@ static void launch_qra_vec(dim3 grid, cudaStream_t stream, void* qkv, int row_st
                            const float* k_w, float eps, const float* cos_sin, int table_rows, const int* positions,
                            const int* seq_of_token, const int* block_table, int bt_stride, void* k_pages, void* v_pages,
                            int page_size, int num_pages) {
-    qk_norm_rope_append_vec_kernel<T, VEC><<<grid, QRA_WARPS * 32, 0, stream>>>(
+    acv_launch(PDL_ROPE, qk_norm_rope_append_vec_kernel<T, VEC>, grid, QRA_WARPS * 32, 0, stream,
         (T*)qkv, row_stride, NH, NKV, q_w, k_w, eps, cos_sin, table_rows, positions, seq_of_token, block_table,
         bt_stride, (T*)k_pages, (T*)v_pages, page_size, num_pages);
 }

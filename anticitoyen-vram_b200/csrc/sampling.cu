@@ -116,6 +116,8 @@ argmax_split_kernel(const float* __restrict__ logits, int ld, int V, int* __rest
     __shared__ float redf[32];
     __shared__ int redi[32];
     __shared__ int last_s;
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, part = blockIdx.y;
     const int span = ((V + ARG_PARTS - 1) / ARG_PARTS + 3) & ~3;
     const int lo = part * span, hi = min(V, lo + span);
@@ -170,7 +172,7 @@ ACV_API int acv_argmax(const float* logits, int ld, int rows, int V, int* out, c
     if (rows <= 0) return 0;
     if (V <= 0) return ACV_ERR_SIZE;
     if (V >= 16384 && rows <= ARG_MAX_ROWS) {
-        argmax_split_kernel<<<dim3(rows, ARG_PARTS), 256, 0, stream>>>(logits, ld, V, out);
+        acv_launch(PDL_MISC, argmax_split_kernel, dim3(rows, ARG_PARTS), 256, 0, stream, logits, ld, V, out);
         return acv_launch_status();
     }
     argmax_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, ld, V, out);

@@ -132,6 +132,12 @@ def _compile(bdir: str, lib: str, tag: str, verbose: bool) -> None:
         if proc.returncode != 0:
             raise BuildError(f"linking {lib} failed:\n{proc.stdout}")
         os.replace(tmp, lib)
+        for name in os.listdir(bdir):       # libraries of earlier source states are never loaded again
+            if name.startswith("libacvram_b200_") and name.endswith(".so") and os.path.join(bdir, name) != lib:
+                try:
+                    os.remove(os.path.join(bdir, name))
+                except OSError:
+                    pass
         for obj in objs:
             try:
                 os.remove(obj)

@@ -9,6 +9,7 @@ CUDA device, the first call raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -44,8 +45,19 @@ def library() -> ctypes.CDLL:
             raise KernelError(f"the CUDA kernels of acvram_b200 could not be built: {exc}") from exc
         lib = ctypes.CDLL(path)
         _declare(lib)
+        if os.environ.get("ACVRAM_B200_PDL"):
+            lib.acv_set_pdl(int(os.environ["ACVRAM_B200_PDL"], 0))
         _lib = lib
     return _lib
+
+
+def set_programmatic_launch(classes: int | bool) -> None:
+    """Which kernel classes are launched so that they may begin while their predecessor finishes
+    (bit set: 1 matrix product, 2 norm, 4 rope/append, 8 decode attention, 16 SwiGLU, 32 the rest;
+    True = the default set, False = none)."""
+    if classes is True:
+        classes = 0x3
+    library().acv_set_pdl(int(classes))
 
 
 def loaded_library_path() -> str | None:
@@ -61,7 +73,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
-        "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, P],
+        "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "acv_argmax": [P, I, I, I, P, P],
@@ -72,6 +84,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn = getattr(lib, name)
         fn.argtypes = args
         fn.restype = c_int
+    lib.acv_set_pdl.argtypes = [c_int]
+    lib.acv_set_pdl.restype = None
 
 
 LAUNCHES = 0   # kernels of this package launched so far (library matrix products are not counted)
@@ -244,12 +258,14 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple[int
         raise KernelError("gemm_tc: operands must be bfloat16 and the output bfloat16 or float32")
     if w.shape[1] != K or out.shape != (M, N) or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError(f"gemm_tc: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
-    swap, bn, splits = plan or gemm_tc_plan(M, N, K)
+    plan = plan or gemm_tc_plan(M, N, K)
+    swap, bn, splits = plan[:3]
+    stages = plan[3] if len(plan) > 3 else 8
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     _check(library().acv_gemm_tc(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
                                  1 if out.dtype == torch.float32 else 0, swap, bn, splits, _p(ws), ws.numel(), _p(cnt),
-                                 cnt.numel(), _p(status), _SM_COUNT, _stream()), "gemm_tc")
+                                 cnt.numel(), _p(status), _SM_COUNT, stages, _stream()), "gemm_tc")
     return out
 
 
