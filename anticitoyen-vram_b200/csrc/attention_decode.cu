@@ -11,15 +11,17 @@
 // that arrives last do the merge (acvram/kernels/attn_paginee.py:176-259), which
 // is what happens here: no block ever waits for another.
 //
-// Keys and values stream through shared memory in tiles of 64 keys with 16-byte
-// asynchronous copies, two tiles in flight; each of the four warps takes 16 keys
-// of a tile (QK^T and PV on mma.sync m16n8k16, softmax state in float) and the
-// warps merge at the end.  Rows of a tile are addressed through the block table
-// one by one, so any page size works.
+// Keys and values stream through shared memory with 16-byte asynchronous copies.
+// Each of the four warps takes every fourth tile of 16 keys of the CTA's range
+// through a ring of buffers of its own (QK^T and PV on mma.sync m16n8k16, softmax
+// state in float), so that several tiles are in flight for every warp and no warp
+// waits for another; the warps merge at the end.  Rows of a tile are addressed
+// through the block table one by one, so any page size works.
 #include "mma_tiles.cuh"
 
 #define AD_THREADS 128
-#define AD_TILE 64
+#define AD_TILE 64          // split boundaries fall on multiples of this many keys
+#define AD_STAGES 3         // buffers in each warp's ring
 #define AD_LOG2E 1.4426950408889634f
 
 template <int D>
@@ -31,12 +33,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
                    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
-    constexpr int TILE_BYTES = AD_TILE * D * 2;
+    constexpr int WT_BYTES = 16 * D * 2;                         // 16 keys (or values) of one kv-head
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                                   // [16][D]
-    unsigned char* k_s = smem + 16 * D * 2;                      // [2][64][D]
-    unsigned char* v_s = k_s + 2 * TILE_BYTES;                   // [2][64][D]
-    int* pg_s = reinterpret_cast<int*>(v_s + 2 * TILE_BYTES);    // [pg_cap] pages of this CTA's key range
+    unsigned char* ring = smem + 16 * D * 2;                     // [4 warps][AD_STAGES][K, V][16][D]
+    int* pg_s = reinterpret_cast<int*>(ring + 4 * AD_STAGES * 2 * WT_BYTES);   // [pg_cap] pages of this CTA's keys
     __shared__ int is_last_s;
 
     pdl_launch_dependents();
@@ -52,7 +53,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     const int chunk = (((n_keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
     const int beg = lo + split * chunk;
     const int end = min(beg + chunk, p + 1);
-    const int n_tiles = beg < end ? (end - beg + AD_TILE - 1) / AD_TILE : 0;
+    const int n_tiles = beg < end ? (end - beg + AD_TILE - 1) / AD_TILE : 0;   // > 0: this split has keys
 
     // ---- queries of the group into shared memory (rows >= n_rep are zero)
     for (int id = tid; id < 16 * CH; id += AD_THREADS) {
@@ -70,9 +71,43 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         for (int i = tid; i < n_pg; i += AD_THREADS) pg_s[i] = bt[first_pg + i];
     __syncthreads();
 
-    auto load_tile = [&](int t, int stage) {
-        const int j0 = beg + t * AD_TILE;
-        for (int id = tid; id < AD_TILE * CH; id += AD_THREADS) {
+    // Each warp streams its own keys: the CTA's range is cut into tiles of 16 keys, warp w takes the
+    // tiles w, w+4, w+8 ... through a ring of AD_STAGES buffers of its own, so that several tiles
+    // are in flight for every warp and no warp waits for another inside the loop.
+    const int n_wt = beg < end ? (end - beg + 15) / 16 : 0;
+    const int my_n = n_wt > warp ? (n_wt - warp + 3) / 4 : 0;
+    unsigned char* my_ring = ring + warp * (AD_STAGES * 2 * WT_BYTES);
+
+    // With pages of 16 keys or a multiple, and a range that starts on a multiple of 16, a tile lies
+    // in one page and its 16 rows are one contiguous run of 16*D elements: one table lookup per
+    // tile, and every lane copies fixed offsets of that run.
+    const bool contiguous = page_shift >= 4 && (beg & 15) == 0 && pg_cached;
+    const int lane_row = lane / CH, lane_c = lane % CH;       // this lane's first row and its chunk in the row
+    constexpr int ROWS_PER_IT = 32 / CH;                      // rows a warp covers with one copy instruction
+
+    auto load_wt = [&](int i, int stage) {
+        const int j0 = beg + (warp + 4 * i) * 16;
+        unsigned char* kdst = my_ring + stage * 2 * WT_BYTES;
+        unsigned char* vdst = kdst + WT_BYTES;
+        if (contiguous) {
+            const int pg = pg_s[(j0 >> page_shift) - first_pg];
+            const bool pg_ok = pg >= 0 && pg < num_pages;
+            const size_t base = (((size_t)(pg_ok ? pg : 0) * NKV + kvh) * page_size + (j0 & (page_size - 1))) * D;
+            const bf16* ksrc = k_pages + base + lane * 8;
+            const bf16* vsrc = v_pages + base + lane * 8;
+            const int rows_left = end - j0;                   // rows >= rows_left are beyond the range: zero
+#pragma unroll
+            for (int it = 0; it < 16 / ROWS_PER_IT; ++it) {
+                const int r = lane_row + it * ROWS_PER_IT;
+                const bool ok = pg_ok && r < rows_left;
+                const int off = tile_off<D>(r, lane_c);
+                cp_async16(smem_u32(kdst + off), ok ? (const void*)(ksrc + it * 256) : (const void*)k_pages, ok);
+                cp_async16(smem_u32(vdst + off), ok ? (const void*)(vsrc + it * 256) : (const void*)v_pages, ok);
+            }
+            return;
+        }
+#pragma unroll
+        for (int id = lane; id < 16 * CH; id += 32) {
             const int r = id / CH, c = id % CH;
             const int j = j0 + r;
             bool ok = j < end;
@@ -84,15 +119,17 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                 ok = pg >= 0 && pg < num_pages;
                 row_off = (((size_t)pg * NKV + kvh) * page_size + in_pg) * D + c * 8;
             }
-            const int off = stage * TILE_BYTES + tile_off<D>(r, c);
-            cp_async16(smem_u32(k_s + off), ok ? (const void*)(k_pages + row_off) : (const void*)k_pages, ok);
-            cp_async16(smem_u32(v_s + off), ok ? (const void*)(v_pages + row_off) : (const void*)v_pages, ok);
+            const int off = tile_off<D>(r, c);
+            cp_async16(smem_u32(kdst + off), ok ? (const void*)(k_pages + row_off) : (const void*)k_pages, ok);
+            cp_async16(smem_u32(vdst + off), ok ? (const void*)(v_pages + row_off) : (const void*)v_pages, ok);
         }
     };
 
-    if (n_tiles > 0) load_tile(0, 0);
-    cp_async_commit();
-    __syncthreads();
+#pragma unroll
+    for (int st = 0; st < AD_STAGES - 1; ++st) {
+        if (st < my_n) load_wt(st, st);
+        cp_async_commit();
+    }
 
     // ---- query fragments (A operand), kept in registers for the whole kernel
     uint32_t qf[D / 16][4];
@@ -112,20 +149,25 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     const float scale_log2 = scale * AD_LOG2E;
     const int mi = lane >> 3, lr = lane & 7;
 
-    for (int t = 0; t < n_tiles; ++t) {
-        const int stage = t & 1;
-        if (t + 1 < n_tiles) load_tile(t + 1, stage ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        const uint32_t kb = smem_u32(k_s + stage * TILE_BYTES), vb = smem_u32(v_s + stage * TILE_BYTES);
-        const int jw = beg + t * AD_TILE + warp * 16;   // first key of this warp's 16
-        if (jw < end) {
+    int stage = 0;
+    for (int i = 0; i < my_n; ++i) {
+        {
+            const int nxt = i + AD_STAGES - 1;
+            int nxt_stage = stage + AD_STAGES - 1;
+            if (nxt_stage >= AD_STAGES) nxt_stage -= AD_STAGES;
+            if (nxt < my_n) load_wt(nxt, nxt_stage);
+            cp_async_commit();
+        }
+        cp_async_wait<AD_STAGES - 1>();
+        __syncwarp();
+        const uint32_t kb = smem_u32(my_ring + stage * 2 * WT_BYTES), vb = kb + WT_BYTES;
+        const int jw = beg + (warp + 4 * i) * 16;       // first key of this tile
+        {
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
             for (int kd = 0; kd < D / 16; ++kd) {
                 uint32_t b[4];
-                ldmatrix_x4(b, kb + tile_off<D>(warp * 16 + (mi >> 1) * 8 + lr, kd * 2 + (mi & 1)));
+                ldmatrix_x4(b, kb + tile_off<D>((mi >> 1) * 8 + lr, kd * 2 + (mi & 1)));
                 mma_bf16(s[0], qf[kd], b[0], b[1]);
                 mma_bf16(s[1], qf[kd], b[2], b[3]);
             }
@@ -163,26 +205,29 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
             pa[1] = pack_bf16(pv[0][2], pv[0][3]);
             pa[2] = pack_bf16(pv[1][0], pv[1][1]);
             pa[3] = pack_bf16(pv[1][2], pv[1][3]);
+            if (alpha[0] != 1.f || alpha[1] != 1.f) {       // the running maximum moved: rescale what is summed so far
 #pragma unroll
-            for (int i = 0; i < D / 8; ++i) {
-                acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
-                acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+                for (int ii = 0; ii < D / 8; ++ii) {
+                    acc[ii][0] *= alpha[0]; acc[ii][1] *= alpha[0];
+                    acc[ii][2] *= alpha[1]; acc[ii][3] *= alpha[1];
+                }
             }
 #pragma unroll
             for (int nd = 0; nd < D / 16; ++nd) {
                 uint32_t b[4];
-                ldmatrix_x4_trans(b, vb + tile_off<D>(warp * 16 + (mi & 1) * 8 + lr, nd * 2 + (mi >> 1)));
+                ldmatrix_x4_trans(b, vb + tile_off<D>((mi & 1) * 8 + lr, nd * 2 + (mi >> 1)));
                 mma_bf16(acc[2 * nd], pa, b[0], b[1]);
                 mma_bf16(acc[2 * nd + 1], pa, b[2], b[3]);
             }
         }
-        __syncthreads();
+        __syncwarp();
+        stage = stage + 1 == AD_STAGES ? 0 : stage + 1;
     }
     cp_async_wait<0>();
     __syncthreads();
 
     // ---- merge the four warps through shared memory (the tiles are no longer needed)
-    float* wm = reinterpret_cast<float*>(k_s);            // [4][16]
+    float* wm = reinterpret_cast<float*>(ring);           // [4][16]
     float* wl = wm + 64;                                  // [4][16]
     float* wacc = wl + 64;                                // [4][16][D]
 #pragma unroll
@@ -274,7 +319,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     const int chunk = (((keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
     int pg_cap = chunk / page_size + 2;
     if (pg_cap > 8192) pg_cap = 8192;
-    const int smem = 16 * D * 2 + 4 * AD_TILE * D * 2 + pg_cap * 4;
+    const int smem = 16 * D * 2 + 4 * AD_STAGES * 2 * 16 * D * 2 + pg_cap * 4;
     static int configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

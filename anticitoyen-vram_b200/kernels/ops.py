@@ -337,10 +337,11 @@ def _decode_scratch(device, floats: int, ml_floats: int, counters: int):
 
 
 def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
-    """How many splits of the context fill the GPU: about two CTAs per SM, no split under 128 keys."""
+    """How many splits of the context: enough CTAs to cover the SMs not quite twice (measured best on a
+    B200: a split costs a fixed few microseconds of merge), and no split shorter than 256 keys."""
     pairs = max(1, n_dec * num_kv_heads)
-    want = -(-2 * _SM_COUNT // pairs)
-    return max(1, min(want, -(-max_kv // 128)))
+    want = max(1, round(256 / pairs))
+    return max(1, min(want, -(-max_kv // 256)))
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
