@@ -65,8 +65,32 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
         for (int i = tid; i < n_pg; i += AC_THREADS) pg_s[i] = bt[first_pg + i];
     __syncthreads();
 
+    // With pages of 16 keys or a multiple, each run of 16 rows of a tile lies in one page and is one
+    // contiguous run of 16*D elements: one table lookup per 16 rows, fixed offsets for every thread.
+    const bool contiguous = page_shift >= 4 && pg_cached;
+    constexpr int ROWS_PER_IT = AC_THREADS / CH;          // rows the CTA covers with one copy instruction
+    const int t_row = tid / CH, t_c = tid % CH;
+
     auto load_tile = [&](int t, int stage) {
         const int j0 = j_first + t * AC_BN;
+        if (contiguous) {
+#pragma unroll
+            for (int it = 0; it < AC_BN / ROWS_PER_IT; ++it) {
+                const int r = t_row + it * ROWS_PER_IT;
+                const int j = j0 + r;
+                bool ok = j <= hi && j >= lo;
+                size_t row_off = 0;
+                if (ok) {
+                    const int pg = pg_s[(j >> page_shift) - first_pg];
+                    ok = pg >= 0 && pg < num_pages;
+                    row_off = (((size_t)pg * NKV + kvh) * page_size + (j & (page_size - 1))) * D + t_c * 8;
+                }
+                const int off = stage * TILE_BYTES + tile_off<D>(r, t_c);
+                cp_async16(smem_u32(k_s + off), ok ? (const void*)(k_pages + row_off) : (const void*)k_pages, ok);
+                cp_async16(smem_u32(v_s + off), ok ? (const void*)(v_pages + row_off) : (const void*)v_pages, ok);
+            }
+            return;
+        }
         for (int id = tid; id < AC_BN * CH; id += AC_THREADS) {
             const int r = id / CH, c = id % CH;
             const int j = j0 + r;
@@ -132,33 +156,43 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                     mma_bf16(s[2 * np + 1], qf[kd], b[2], b[3]);
                 }
             }
+            // Only tiles that cross a row's causal edge (or the window's lower edge) need the mask; the
+            // scores stay unscaled: scale*log2(e) goes into the exponent's fused multiply-add.
+            const bool need_mask = !(j0 + AC_BN - 1 <= pos0 + warp * 16 &&
+                                     (window <= 0 || j0 > pos0 + warp * 16 + 15 - window));
             float mx[2] = {-INFINITY, -INFINITY};
+            if (need_mask) {
+#pragma unroll
+                for (int nt = 0; nt < AC_BN / 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+                        const int p = p_row[e >> 1];
+                        const bool seen = j <= p && (window <= 0 || j > p - window);
+                        if (!seen) s[nt][e] = -INFINITY;
+                    }
+            }
 #pragma unroll
             for (int nt = 0; nt < AC_BN / 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int j = j0 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                    const int p = p_row[e >> 1];
-                    const bool seen = j <= p && (window <= 0 || j > p - window);
-                    const float v = seen ? s[nt][e] * scale_log2 : -INFINITY;
-                    s[nt][e] = v;
-                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
-                }
+                for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
             float alpha[2], m_use[2];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
                 mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
-                const float m_new = fmaxf(m_run[hh], mx[hh]);
+                const float m_new = fmaxf(m_run[hh], mx[hh] * scale_log2);
                 m_use[hh] = m_new == -INFINITY ? 0.f : m_new;
-                alpha[hh] = exp2f(m_run[hh] - m_use[hh]);
+                alpha[hh] = fast_exp2(m_run[hh] - m_use[hh]);
                 m_run[hh] = m_new;
                 l_run[hh] *= alpha[hh];
             }
+            if (alpha[0] != 1.f || alpha[1] != 1.f) {       // the running maximum moved
 #pragma unroll
-            for (int i = 0; i < D / 8; ++i) {
-                acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
-                acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+                for (int i = 0; i < D / 8; ++i) {
+                    acc[i][0] *= alpha[0]; acc[i][1] *= alpha[0];
+                    acc[i][2] *= alpha[1]; acc[i][3] *= alpha[1];
+                }
             }
 #pragma unroll
             for (int kp = 0; kp < AC_BN / 16; ++kp) {
@@ -168,7 +202,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
                 for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        pv[nt][e] = exp2f(s[2 * kp + nt][e] - m_use[e >> 1]);
+                        pv[nt][e] = fast_exp2(fmaf(s[2 * kp + nt][e], scale_log2, -m_use[e >> 1]));
                         l_run[e >> 1] += pv[nt][e];
                     }
                 pa[0] = pack_bf16(pv[0][0], pv[0][1]);

@@ -224,7 +224,7 @@ class BatchBuilder:
         dec = np.nonzero(ql == 1)[0].astype(np.int32)
         tile_seq, tile_q0 = [], []
         for i in np.nonzero(ql > 1)[0]:
-            starts_i = np.arange(0, q_lens[i], QUERY_TILE, dtype=np.int32)
+            starts_i = np.arange(0, q_lens[i], QUERY_TILE, dtype=np.int32)[::-1]   # late tiles see most keys: first
             tile_seq.append(np.full(starts_i.size, i, dtype=np.int32))
             tile_q0.append(starts_i)
         work_counts = {"dec": int(dec.size), "tiles": int(sum(t.size for t in tile_seq))}

@@ -364,7 +364,7 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                     kv_len: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                     scale: float, window: int) -> torch.Tensor:
-    """Causal attention of portions of prompts (tiles of 64 query tokens) over their requests' pages."""
+    """Causal attention of portions of prompts (tiles of QUERY_TILE query tokens) over their requests' pages."""
     _check(library().acv_attention_chunk(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0), n_tiles,
         _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim,

@@ -13,6 +13,7 @@ import argparse
 
 import torch
 
+from .engine.batch import QUERY_TILE
 from .kernels import ops
 
 
@@ -62,7 +63,7 @@ def attention_case(batch: int, q_len: int, context: int, reps: int) -> None:
         gb = batch * context * NKV * D * 2 * 2 / 1e9
         print(f"attention_decode batch={batch} context={context} splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of pages")
     else:
-        tiles = [(b, s) for b in range(batch) for s in range(0, q_len, 64)]
+        tiles = [(b, s) for b in range(batch) for s in range(0, q_len, QUERY_TILE)][::-1]
         tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
         tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
         fn = lambda i: ops.attention_chunk(qkv, out, *pools[i % sets], tile_seq, tile_q0, len(tiles), cu_q, kv_len,

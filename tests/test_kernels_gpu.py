@@ -6,6 +6,7 @@ import pytest
 import torch
 
 import kernel_refs as ref
+from acvram_b200.engine.batch import QUERY_TILE
 
 pytestmark = pytest.mark.gpu
 
@@ -254,7 +255,7 @@ def _tc_case(ops, NH, NKV, D, page, lens, q_lens, window, seed, n_splits=None, s
     ctx.cu_q = torch.tensor(cu, dtype=torch.int32).cuda()
     ctx.kv_len = torch.tensor(lens, dtype=torch.int32).cuda()
     dec = [b for b, q in enumerate(q_lens) if q == 1]
-    tiles = [(b, s) for b, q in enumerate(q_lens) if q > 1 for s in range(0, q, 64)]
+    tiles = [(b, s) for b, q in enumerate(q_lens) if q > 1 for s in range(0, q, QUERY_TILE)]
     i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
     ctx.work = {"dec_tokens": i32([cu[b] for b in dec]), "dec_seqs": i32(dec), "n_dec": len(dec),
                 "tile_seq": i32([t[0] for t in tiles]), "tile_q0": i32([t[1] for t in tiles]), "n_tiles": len(tiles),
