@@ -111,6 +111,7 @@ struct GemmParams {
     int ldc;
     int swap;               // 0: A = x (rows = tokens), 1: A = weight (rows = features)
     int out_f32;
+    int act;                // 1: output features come in (gate, up) pairs and C[:, n/2] = silu(gate) * up
     int tiles_a, tiles_b, splits, kb_per_split, n_kb;
     int stages;             // pipeline depth (2..8); shared memory = stages * (128 + BN) * 128 bytes
     void* C;
@@ -118,6 +119,77 @@ struct GemmParams {
     int* counters;          // [tiles], zero before and after
     int* status;            // 0, or the code of the wait that ran out
 };
+
+// SiLU(gate) * up with the roundings of the unfused path: the product's outputs are rounded to
+// bfloat16, SiLU is computed in float and rounded, then the product is rounded.
+__device__ __forceinline__ bf16 swiglu_pair(float gate, float up) {
+    const float g = __bfloat162float(__float2bfloat16_rn(gate));
+    const float u = __bfloat162float(__float2bfloat16_rn(up));
+    const float s = __bfloat162float(__float2bfloat16_rn(g / (1.f + expf(-g))));
+    return __float2bfloat16_rn(s * u);
+}
+
+// Write 16 accumulator columns of one tensor-memory lane: row_a is the A-operand row the lane holds,
+// col0 the B-operand row of v[0].  Executed by whole warps (the paired form shuffles between lanes).
+__device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int col0, const float (&v)[16], int lane) {
+    if (p.act) {
+        if (p.swap) {       // features lie on lanes: an even lane holds a gate, the next lane its up
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const float up = __shfl_down_sync(0xffffffffu, v[c], 1);
+                const int m = col0 + c;
+                if (!(lane & 1) && row_a + 1 < p.N && m < p.M)
+                    ((bf16*)p.C)[(size_t)m * p.ldc + (row_a >> 1)] = swiglu_pair(v[c], up);
+            }
+        } else if (row_a < p.M) {   // features lie on columns: (v[0], v[1]), (v[2], v[3]) ...
+            bf16* dst = (bf16*)p.C + (size_t)row_a * p.ldc + (col0 >> 1);
+            bf16 o[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = swiglu_pair(v[2 * k], v[2 * k + 1]);
+            if (col0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0) {
+                *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(o);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    if (col0 + 2 * k + 1 < p.N) dst[k] = o[k];
+            }
+        }
+        return;
+    }
+    if (p.swap) {
+        // C[token = col0 + c][feature = row_a]: lanes write neighbouring features
+        if (row_a < p.N) {
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+                const int m = col0 + c;
+                if (m < p.M) {
+                    if (p.out_f32) ((float*)p.C)[(size_t)m * p.ldc + row_a] = v[c];
+                    else ((bf16*)p.C)[(size_t)m * p.ldc + row_a] = __float2bfloat16_rn(v[c]);
+                }
+            }
+        }
+    } else if (row_a < p.M) {
+        if (p.out_f32) {
+            float* dst = (float*)p.C + (size_t)row_a * p.ldc + col0;
+#pragma unroll
+            for (int c = 0; c < 16; ++c)
+                if (col0 + c < p.N) dst[c] = v[c];
+        } else {
+            bf16* dst = (bf16*)p.C + (size_t)row_a * p.ldc + col0;
+            if (col0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0) {
+                __nv_bfloat162 o[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) o[k] = __floats2bfloat162_rn(v[2 * k], v[2 * k + 1]);
+                ((uint4*)dst)[0] = reinterpret_cast<const uint4*>(o)[0];
+                ((uint4*)dst)[1] = reinterpret_cast<const uint4*>(o)[1];
+            } else {
+#pragma unroll
+                for (int c = 0; c < 16; ++c)
+                    if (col0 + c < p.N) dst[c] = __float2bfloat16_rn(v[c]);
+            }
+        }
+    }
+}
 
 template <int BN>
 struct GemmShape {
@@ -228,40 +300,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int c0 = 0; c0 < BN; c0 += 16) {
                     uint32_t r[16];
                     tc_ld16(taddr + c0, r);
-                    if (p.swap) {
-                        // C[token = tb*BN + c][feature = row_a]: lanes write neighbouring features
-                        if (row_a < p.N) {
+                    float v[16];
 #pragma unroll
-                            for (int c = 0; c < 16; ++c) {
-                                const int m = tb * BN + c0 + c;
-                                if (m < p.M) {
-                                    if (p.out_f32) ((float*)p.C)[(size_t)m * p.ldc + row_a] = __uint_as_float(r[c]);
-                                    else ((bf16*)p.C)[(size_t)m * p.ldc + row_a] = __float2bfloat16_rn(__uint_as_float(r[c]));
-                                }
-                            }
-                        }
-                    } else if (row_a < p.M) {
-                        const int n0 = tb * BN + c0;
-                        if (p.out_f32) {
-                            float* dst = (float*)p.C + (size_t)row_a * p.ldc + n0;
-#pragma unroll
-                            for (int c = 0; c < 16; ++c)
-                                if (n0 + c < p.N) dst[c] = __uint_as_float(r[c]);
-                        } else {
-                            bf16* dst = (bf16*)p.C + (size_t)row_a * p.ldc + n0;
-                            if (n0 + 16 <= p.N && (((uintptr_t)dst) & 15) == 0) {
-                                uint4 v0, v1;
-                                v0.x = pack2(r[0], r[1]); v0.y = pack2(r[2], r[3]); v0.z = pack2(r[4], r[5]); v0.w = pack2(r[6], r[7]);
-                                v1.x = pack2(r[8], r[9]); v1.y = pack2(r[10], r[11]); v1.z = pack2(r[12], r[13]); v1.w = pack2(r[14], r[15]);
-                                ((uint4*)dst)[0] = v0;
-                                ((uint4*)dst)[1] = v1;
-                            } else {
-#pragma unroll
-                                for (int c = 0; c < 16; ++c)
-                                    if (n0 + c < p.N) dst[c] = __float2bfloat16_rn(__uint_as_float(r[c]));
-                            }
-                        }
-                    }
+                    for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+                    gt_store16(p, row_a, tb * BN + c0, v, lane);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -288,7 +330,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 __threadfence();
                 const float* wt = p.workspace + (size_t)tile * p.splits * (BN * GT_BM);
                 const int rows_b = min(BN, p.RB - tb * BN);
-                for (int c0 = 0; c0 < rows_b; c0 += 16) {
+                for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (c0 >= rows_b) break;
                     // sixteen columns at a time: all loads of a split are issued before any store
                     float sum[16];
 #pragma unroll
@@ -300,15 +343,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                         for (int c = 0; c < 16; ++c) sum[c] += v[c];
                     }
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        const int m = p.swap ? tb * BN + c0 + c : row_a;
-                        const int n = p.swap ? row_a : tb * BN + c0 + c;
-                        if (c0 + c < rows_b && m < p.M && n < p.N) {
-                            if (p.out_f32) ((float*)p.C)[(size_t)m * p.ldc + n] = sum[c];
-                            else ((bf16*)p.C)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sum[c]);
-                        }
-                    }
+                    gt_store16(p, row_a, tb * BN + c0, sum, lane);
                 }
                 if (et == 0) p.counters[tile] = 0;
             }
@@ -387,7 +422,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
 // splits > 1 needs workspace of tiles*splits*bn*128 floats and `tiles` zeroed counters.
 // status: one int, 0 unless a bounded wait inside the kernel ran out.
 ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
-                        int out_f32, int swap, int bn, int splits, float* workspace, long long workspace_floats,
+                        int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
                         int* counters, long long n_counters, int* status, int sm_count, int stages,
                         cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
@@ -397,7 +432,8 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
     const void* b_ptr = swap ? x : w;
     p.RA = swap ? N : M;
     p.RB = swap ? M : N;
-    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32;
+    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.act = act;
+    if (act && (out_f32 || (N & 1))) return ACV_ERR_SIZE;
     p.tiles_a = (p.RA + GT_BM - 1) / GT_BM;
     p.tiles_b = (p.RB + bn - 1) / bn;
     p.n_kb = (K + GT_BK - 1) / GT_BK;

@@ -73,7 +73,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
-        "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, P],
+        "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "acv_argmax": [P, I, I, I, P, P],
@@ -249,14 +249,21 @@ def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int]:
     return 0, bn, 1
 
 
-def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple[int, int, int] | None = None) -> torch.Tensor:
-    """out[M,N] = x[M,K] @ w[N,K]^T on tcgen05; x, w bfloat16, out bfloat16 or float32."""
+def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | None = None,
+            swiglu_pairs: bool = False) -> torch.Tensor:
+    """out[M,N] = x[M,K] @ w[N,K]^T on tcgen05; x, w bfloat16, out bfloat16 or float32.
+
+    With ``swiglu_pairs`` the rows of w come in (gate, up) pairs and out is [M, N/2]:
+    out[:, i] = silu(x . w[2i]) * (x . w[2i+1]), rounded as the separate kernels round."""
     _need_cuda(x, w, out)
     M, K = x.shape
     N = w.shape[0]
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or out.dtype not in (torch.bfloat16, torch.float32):
         raise KernelError("gemm_tc: operands must be bfloat16 and the output bfloat16 or float32")
-    if w.shape[1] != K or out.shape != (M, N) or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+    n_out = N // 2 if swiglu_pairs else N
+    if swiglu_pairs and (N % 2 or out.dtype != torch.bfloat16):
+        raise KernelError("gemm_tc: the paired SwiGLU output needs an even number of weight rows and a bfloat16 output")
+    if w.shape[1] != K or out.shape != (M, n_out) or x.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError(f"gemm_tc: shapes {tuple(x.shape)} x {tuple(w.shape)} -> {tuple(out.shape)} do not fit")
     plan = plan or gemm_tc_plan(M, N, K)
     swap, bn, splits = plan[:3]
@@ -264,7 +271,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple[int
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     _check(library().acv_gemm_tc(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
-                                 1 if out.dtype == torch.float32 else 0, swap, bn, splits, _p(ws), ws.numel(), _p(cnt),
+                                 1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits,
+                                 _p(ws), ws.numel(), _p(cnt),
                                  cnt.numel(), _p(status), _SM_COUNT, stages, _stream()), "gemm_tc")
     return out
 
@@ -408,6 +416,11 @@ def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Te
     if gemm_tc_takes(x, w):
         return gemm_tc(x, w, out)
     return torch.mm(x, w.t(), out=out)
+
+
+def linear_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[M, I] = silu(x @ Wg^T) * (x @ Wu^T) in one kernel; w_pairs [2I, K] holds (gate_i, up_i) in rows 2i, 2i+1."""
+    return gemm_tc(x, w_pairs, out, swiglu_pairs=True)
 
 
 def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:

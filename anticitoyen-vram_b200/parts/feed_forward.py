@@ -27,11 +27,26 @@ class SwiGLU(FeedForward):
 
     def load(self, tensors, rt: Runtime) -> None:
         w = lambda n: tensors[n].to(device=rt.device, dtype=rt.dtype)
-        self.gate_up = Linear.stacked([w(self.prefix + "gate_proj.weight"), w(self.prefix + "up_proj.weight")])
+        gate, up = w(self.prefix + "gate_proj.weight"), w(self.prefix + "up_proj.weight")
+        # bfloat16 with 16-byte aligned rows: gate and up rows are interleaved (g0, u0, g1, u1 ...) so that the
+        # tensor-core product's epilogue holds each pair together and applies SiLU(gate) * up itself; the
+        # stacked product's output [T, 2I] is then never written.  Otherwise: stacked product, then the kernel.
+        self.fused = rt.dtype == torch.bfloat16 and self.hidden_size % 8 == 0
+        if self.fused:
+            self.gate_up = Linear(torch.stack([gate, up], dim=1).reshape(2 * self.intermediate_size, self.hidden_size))
+        else:
+            self.gate_up = Linear.stacked([gate, up])
         self.down = Linear(w(self.prefix + "down_proj.weight"))
 
     def forward(self, h, ctx):
-        gu = self.gate_up(h)
+        if self.fused and h.shape[0] and ops.gemm_tc_takes(h, self.gate_up.weight):
+            act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
+            ops.linear_bf16_swiglu(h, self.gate_up.weight, act)
+            return self.down(act)
+        if self.fused:      # an input the tensor-core kernel does not take: undo the interleaving for this call
+            gu = self.gate_up(h).view(h.shape[0], self.intermediate_size, 2).transpose(1, 2).reshape(h.shape[0], -1)
+        else:
+            gu = self.gate_up(h)
         act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
         ops.swiglu(gu, act)
         return self.down(act)

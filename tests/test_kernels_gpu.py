@@ -370,3 +370,22 @@ def test_gemm_tc_rows_do_not_depend_on_the_batch(ops):
     whole = ops.gemm_tc(x, w, torch.zeros(16, 640, device="cuda", dtype=torch.float32), (1, 16, 2))
     one = ops.gemm_tc(x[3:4], w, torch.zeros(1, 640, device="cuda", dtype=torch.float32), (1, 16, 2))
     assert torch.equal(whole[3:4], one)
+
+
+@pytest.mark.parametrize("plan", [None, (1, 16, 1), (1, 16, 3), (1, 64, 2), (0, 256, 1), (0, 128, 2), (0, 64, 1)])
+@pytest.mark.parametrize("M,I,K", [(8, 352, 512), (40, 1000, 264), (300, 520, 1160)])
+def test_gemm_tc_fused_swiglu(ops, plan, M, I, K):
+    """The paired epilogue equals the stacked product followed by the SwiGLU kernel, bit for bit."""
+    if plan is not None and plan[0] == 1 and M > plan[1]:
+        pytest.skip("more tokens than the tile's narrow side")
+    x = rnd(M, K, dtype=torch.bfloat16, seed=98)
+    wg = rnd(I, K, dtype=torch.bfloat16, scale=0.05, seed=99)
+    wu = rnd(I, K, dtype=torch.bfloat16, scale=0.05, seed=100)
+    pairs = torch.stack([wg, wu], dim=1).reshape(2 * I, K).contiguous()
+    got = ops.gemm_tc(x, pairs, torch.zeros(M, I, device="cuda", dtype=torch.bfloat16), plan, swiglu_pairs=True)
+    gu = ops.gemm_tc(x, torch.cat([wg, wu]).contiguous(), torch.zeros(M, 2 * I, device="cuda", dtype=torch.bfloat16), plan)
+    want = ops.swiglu(gu, torch.zeros(M, I, device="cuda", dtype=torch.bfloat16))
+    assert ops.gemm_status() == 0
+    assert torch.equal(got, want)
+    torch.testing.assert_close(got, ref.swiglu((x.float() @ torch.cat([wg, wu]).float().T).bfloat16(),
+                                               torch.zeros(M, I, device="cuda", dtype=torch.bfloat16)), **tol(torch.bfloat16))
