@@ -48,11 +48,15 @@ def tiny_config(which: str):
         return Qwen3Config(vocab_size=300, hidden_size=128, intermediate_size=160, num_hidden_layers=2,
                            num_attention_heads=6, num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6,
                            rope_theta=1000000.0, max_position_embeddings=512, tie_word_embeddings=False)
+    if which == "E":  # a width whose rows are not 16-byte aligned (100 elements): the paths beside the tensor-core product
+        return Qwen3Config(vocab_size=211, hidden_size=100, intermediate_size=150, num_hidden_layers=2,
+                           num_attention_heads=3, num_key_value_heads=3, head_dim=16, rms_norm_eps=1e-6,
+                           rope_theta=10000.0, max_position_embeddings=256, tie_word_embeddings=True)
     raise KeyError(which)
 
 
-TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3}
-TINY_PAGE = {"A": 16, "B": 8, "C": 16, "D": 16}
+TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
+TINY_PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16}
 
 
 @pytest.fixture(scope="session")
@@ -60,7 +64,7 @@ def tiny_folders(tmp_path_factory):
     """{name: folder} of the tiny models, written once per session into a temporary folder."""
     from acvram_b200.weights import write_random_model
     out = {}
-    for name in ("A", "B", "C", "D"):
+    for name in ("A", "B", "C", "D", "E"):
         folder = tmp_path_factory.mktemp(f"tiny_{name}")
         write_random_model(tiny_config(name), folder, TINY_SEEDS[name])
         out[name] = str(folder)

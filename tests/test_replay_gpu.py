@@ -141,7 +141,7 @@ def run_trace(folder: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int)
 
 
 def requests_for(name: str, vocab: int) -> dict[str, list[int]]:
-    lengths = {"A": [5, 17, 33, 70, 130], "B": [1, 9, 40, 130, 75], "C": [3, 64, 97, 250], "D": [2, 65, 129, 200, 31]}[name]
+    lengths = {"A": [5, 17, 33, 70, 130], "B": [1, 9, 40, 130, 75], "C": [3, 64, 97, 250], "D": [2, 65, 129, 200, 31], "E": [4, 37, 90]}[name]
     return {str(i): random_ids(vocab, n, seed=100 + i) for i, n in enumerate(lengths)}
 
 
@@ -182,7 +182,7 @@ def worst(got, ref, modes):
     return {modes[m]: v for m, v in out.items()}
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
 def test_replay_float32(name, tiny_folders, plain_logits, tmp_path):
     cfg = json.load(open(os.path.join(tiny_folders[name], "config.json")))
     tr, reqs, modes = build_full_trace(name, cfg["vocab_size"])
@@ -195,7 +195,7 @@ def test_replay_float32(name, tiny_folders, plain_logits, tmp_path):
         assert d <= 2e-5 * max(1.0, scale), f"{mode}: max |logit - plain| = {d:.3e} at request/position {where}"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "D"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
 def test_replay_bfloat16(name, tiny_folders, plain_logits, tmp_path):
     cfg = json.load(open(os.path.join(tiny_folders[name], "config.json")))
     tr, reqs, modes = build_full_trace(name, cfg["vocab_size"])
