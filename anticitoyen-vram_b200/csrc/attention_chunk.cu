@@ -1,8 +1,8 @@
 // Paged causal flash attention for portions of prompts (two or more query tokens
 // of one request in a step), bfloat16.
 //
-// One CTA per (tile of 64 query tokens of one request, query head); its four
-// warps take 16 query rows each.  Keys and values come from the request's pages,
+// One CTA per (tile of 128 query tokens of one request, query head); its eight
+// warps take 16 query rows each.  It serves the shapes the tcgen05 kernel (attention_tc.cu) does not take.  Keys and values come from the request's pages,
 // earlier portions and this step's own tokens alike (they were appended before),
 // in tiles of 64 keys, two in flight.  The query at absolute position p sees the
 // keys j <= p, and with a window w > 0 only j > p - w: the mask follows absolute
@@ -14,8 +14,8 @@
 // maximum and sum of the softmax are float.
 #include "mma_tiles.cuh"
 
-#define AC_THREADS 128
-#define AC_BM 64
+#define AC_THREADS 256
+#define AC_BM 128
 #define AC_BN 64
 #define AC_LOG2E 1.4426950408889634f
 
@@ -29,7 +29,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     constexpr int CH = D / 8;
     constexpr int TILE_BYTES = AC_BN * D * 2;
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* q_s = smem;                       // [64][D]
+    unsigned char* q_s = smem;                       // [128][D]
     unsigned char* k_s = smem + AC_BM * D * 2;       // [2][64][D]
     unsigned char* v_s = k_s + 2 * TILE_BYTES;       // [2][64][D]
     int* pg_s = reinterpret_cast<int*>(v_s + 2 * TILE_BYTES);   // [pg_cap] pages of the keys this tile reads
@@ -266,7 +266,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
     return acv_launch_status();
 }
 
-// tile_seq / tile_q0: for each tile of 64 query tokens, its request's index in the batch and the offset of
+// tile_seq / tile_q0: for each tile of 128 query tokens, its request's index in the batch and the offset of
 // the tile's first token among the request's tokens of this step.
 ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                 const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles,

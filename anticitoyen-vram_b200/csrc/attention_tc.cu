@@ -1,0 +1,311 @@
+// Paged causal flash attention for portions of prompts on the fifth-generation tensor cores.
+//
+// One CTA per (tile of 128 query tokens of one request, query head).  For each tile of 128 keys:
+//   S = Q K^T      tcgen05.mma, Q and K in shared memory (K-major, 128-byte swizzle), S in tensor memory
+//   softmax        four warps, one query row per thread: S row from tensor memory (tcgen05.ld), mask by
+//                  absolute position, running maximum and sum in float, P written to shared memory as the
+//                  bfloat16 A operand of the next product; when a row's maximum moved, the row of O in
+//                  tensor memory is rescaled (tcgen05.ld / tcgen05.st)
+//   O += P V       tcgen05.mma, V in shared memory as it lies in the pages ([keys][D], the MN-major operand)
+// Keys and values come straight from the cache pages by TMA, one box per page (page = box rows), two
+// tiles in flight; Q comes by TMA from the step's projection buffer.  Warp 0 issues the loads, warp 1
+// the MMAs, warps 2..5 are the softmax and the epilogue.  The mask follows absolute positions
+// (key j is seen by the query at position p iff j <= p, and j > p - window when a window is set), so a
+// portion may start anywhere in its prompt (acvram/engine/layers.py:1020-1041); the reference runs this
+// case through SDPA on a gathered dense copy (acvram/engine/attention.py:519-584).
+// Every wait is bounded; a wait that runs out is recorded in `status` and the kernel returns.
+#include "tc_ptx.cuh"
+#include "tensor_map.h"
+
+#define AT_THREADS 192
+#define AT_BM 128
+#define AT_BN 128
+#define AT_LOG2E 1.4426950408889634f
+#define AT_ATOM (128 * 128)          // bytes of one swizzle atom column: 128 rows of 128 bytes
+
+struct AttnTcParams {
+    bf16* out;
+    int out_stride;
+    const int* tile_seq;
+    const int* tile_q0;
+    const int* cu_q;
+    const int* kv_len;
+    const int* block_table;
+    int bt_stride;
+    int NH, NKV, page_size, page_shift, num_pages, window;
+    float scale;
+    int* status;
+};
+
+template <int D>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+               const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
+    constexpr int DA = D / 64;                         // 64-element column atoms of a head
+    constexpr int Q_BYTES = DA * AT_ATOM, P_BYTES = 2 * AT_ATOM, KV_BYTES = DA * AT_ATOM;
+    constexpr int TMEM_COLS = 256;                     // S: columns [0,128), O: columns [128, 128 + D)
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = smem_raw + ((1024u - (gt_smem(smem_raw) & 1023u)) & 1023u);
+    const uint32_t q_s = gt_smem(base), p_s = q_s + Q_BYTES, kv_s = p_s + P_BYTES;   // kv_s: [2 stages][K, V]
+    unsigned char* p_ptr = base + Q_BYTES;
+    uint64_t* bars = (uint64_t*)(base + Q_BYTES + P_BYTES + 4 * KV_BYTES);
+    const uint32_t bar0 = gt_smem(bars);
+    const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_free = bar0 + 24, s_full = bar0 + 40, p_full = bar0 + 48,
+                   o_full = bar0 + 56;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_launch_dependents();
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        mbar_init(q_full, 1);
+        for (int s = 0; s < 2; ++s) { mbar_init(kv_full + 8 * s, 1); mbar_init(kv_free + 8 * s, 1); }
+        mbar_init(s_full, 1);
+        mbar_init(p_full, 4);
+        mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gt_smem(&tmem_base_s)), "r"(TMEM_COLS));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+    }
+    // The key/value ring starts at zero: a page that is skipped (every key of it masked) leaves its rows
+    // as they were, and a masked key's value is multiplied by a zero probability, so it must be finite.
+    for (int i = threadIdx.x; i < 4 * KV_BYTES / 16; i += AT_THREADS)
+        reinterpret_cast<uint4*>(base + Q_BYTES + P_BYTES)[i] = make_uint4(0, 0, 0, 0);
+    fence_proxy_async_smem();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
+    pdl_wait();
+
+    // ---- the tile's geometry (the same in every role)
+    const int seq = p.tile_seq[blockIdx.x], q0 = p.tile_q0[blockIdx.x];
+    const int h = blockIdx.y, kvh = h / (p.NH / p.NKV);
+    const int tok0 = p.cu_q[seq] + q0;
+    const int q_len = p.cu_q[seq + 1] - p.cu_q[seq];
+    const int rows = min(AT_BM, q_len - q0);
+    const int pos0 = p.kv_len[seq] - q_len + q0;            // absolute position of the tile's first query
+    const int hi = pos0 + rows - 1;                         // last key any row sees
+    const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
+    const int j_first = lo & ~(AT_BN - 1);
+    const int n_tiles = (hi - j_first) / AT_BN + 1;
+    const int* bt = p.block_table + (size_t)seq * p.bt_stride;
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_expect_tx(q_full, Q_BYTES);
+#pragma unroll
+            for (int a = 0; a < DA; ++a) tma_load_2d(q_s + a * AT_ATOM, &map_q, q_full, h * D + a * 64, tok0);
+            const int ps = p.page_size, pages_per_tile = AT_BN >> p.page_shift;
+            for (int t = 0; t < n_tiles && !abort_s; ++t) {
+                const int s = t & 1;
+                if (t >= 2 && !mbar_wait(kv_free + 8 * s, ((t >> 1) - 1) & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 11); break; }
+                const int j0 = j_first + t * AT_BN;
+                // pages of this tile that hold keys some row reads; the others are skipped (their rows are masked)
+                uint32_t bytes = 0;
+                for (int i = 0; i < pages_per_tile; ++i) {
+                    const int j = j0 + i * ps;
+                    if (j > hi || j + ps - 1 < lo) continue;
+                    const int pg = bt[j >> p.page_shift];
+                    if (pg >= 0 && pg < p.num_pages) bytes += 2u * DA * ps * 128u;
+                }
+                mbar_expect_tx(kv_full + 8 * s, bytes);
+                const uint32_t k_dst = kv_s + s * 2 * KV_BYTES, v_dst = k_dst + KV_BYTES;
+                for (int i = 0; i < pages_per_tile; ++i) {
+                    const int j = j0 + i * ps;
+                    if (j > hi || j + ps - 1 < lo) continue;
+                    const int pg = bt[j >> p.page_shift];
+                    if (pg < 0 || pg >= p.num_pages) continue;
+                    const int row = (pg * p.NKV + kvh) * ps;
+#pragma unroll
+                    for (int a = 0; a < DA; ++a) {
+                        tma_load_2d(k_dst + a * AT_ATOM + i * ps * 128, &map_k, kv_full + 8 * s, a * 64, row);
+                        tma_load_2d(v_dst + a * AT_ATOM + i * ps * 128, &map_v, kv_full + 8 * s, a * 64, row);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            const uint32_t idesc_s = umma_idesc(AT_BN, 128, 0), idesc_o = umma_idesc(D, 128, 1);
+            bool ok = mbar_wait(q_full, 0, &abort_s);
+            if (!ok) { abort_s = 1; atomicExch(p.status, 12); }
+            for (int t = 0; t < n_tiles && ok && !abort_s; ++t) {
+                const int s = t & 1;
+                if (!mbar_wait(kv_full + 8 * s, (t >> 1) & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 13); break; }
+                tc_fence_after();
+                const uint32_t k_addr = kv_s + s * 2 * KV_BYTES, v_addr = k_addr + KV_BYTES;
+                // S = Q K^T over the head dimension
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk >> 2) * AT_ATOM + (kk & 3) * 32;
+                    tc_mma_bf16(tmem_s, umma_desc(q_s + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
+                }
+                tc_commit(s_full);
+                // O += P V over the tile's keys, once the softmax has written P
+                if (!mbar_wait(p_full, t & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 14); break; }
+                tc_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < AT_BN / 16; ++kk) {
+                    const uint32_t a_off = (kk >> 2) * AT_ATOM + (kk & 3) * 32;
+                    tc_mma_bf16(tmem_o, umma_desc(p_s + a_off), umma_desc_mn(v_addr + kk * 2048, AT_ATOM), idesc_o,
+                                (t > 0 || kk > 0) ? 1u : 0u);
+                }
+                tc_commit(kv_free + 8 * s);      // this stage's keys and values are read
+            }
+            tc_commit(o_full);
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax and epilogue (warps 2..5)
+        const int wq = warp & 3;
+        const int r = wq * 32 + lane;                           // this thread's query row = tensor-memory lane
+        const int pos = pos0 + r;
+        const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const float scale_log2 = p.scale * AT_LOG2E;
+        float m_run = -INFINITY, l_run = 0.f;
+        bool failed = false;
+        for (int t = 0; t < n_tiles && !abort_s; ++t) {
+            if (!mbar_wait(s_full, t & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 15); failed = true; break; }
+            tc_fence_after();
+            const int j0 = j_first + t * AT_BN;
+            float sv[AT_BN];
+#pragma unroll
+            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+                uint32_t raw[32];
+                tc_ld32(tmem_s + lane_base + c0, raw);
+#pragma unroll
+                for (int c = 0; c < 32; ++c) sv[c0 + c] = __uint_as_float(raw[c]);
+            }
+            const bool need_mask = j0 + AT_BN - 1 > pos0 || (p.window > 0 && j0 <= pos0 + AT_BM - 1 - p.window);
+            float mx = -INFINITY;
+            if (need_mask) {
+#pragma unroll
+                for (int c = 0; c < AT_BN; ++c) {
+                    const int j = j0 + c;
+                    const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
+                    if (!seen) sv[c] = -INFINITY;
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < AT_BN; ++c) mx = fmaxf(mx, sv[c]);
+            const float m_new = fmaxf(m_run, mx * scale_log2);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float alpha = exp2f(m_run - m_use);
+            m_run = m_new;
+            // rows whose maximum moved rescale what O holds so far (tensor-memory access is warp-wide)
+            if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    uint32_t o[32];
+                    tc_ld32(tmem_o + lane_base + c0, o);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
+                    tc_st32(tmem_o + lane_base + c0, o);
+                }
+            }
+            l_run *= alpha;
+            // P as the bfloat16 K-major operand: row r, chunk c8 of 8 keys at atom (c8 / 8), swizzled by the row
+#pragma unroll
+            for (int c8 = 0; c8 < AT_BN / 8; ++c8) {
+                float e[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    e[i] = exp2f(fmaf(sv[c8 * 8 + i], scale_log2, -m_use));
+                    l_run += e[i];
+                }
+                uint4 pk;
+                pk.x = pack_bf16x2(e[0], e[1]); pk.y = pack_bf16x2(e[2], e[3]);
+                pk.z = pack_bf16x2(e[4], e[5]); pk.w = pack_bf16x2(e[6], e[7]);
+                *reinterpret_cast<uint4*>(p_ptr + (c8 >> 3) * AT_ATOM + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = pk;
+            }
+            fence_proxy_async_smem();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full);
+        }
+        if (!failed && !abort_s && mbar_wait(o_full, 0, &abort_s)) {
+            tc_fence_after();
+            const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
+            bf16* dst = p.out + (size_t)(tok0 + r) * p.out_stride + (size_t)h * D;
+#pragma unroll
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t o[32];
+                tc_ld32(tmem_o + lane_base + c0, o);
+                if (r < rows) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 pk;
+                        pk.x = pack_bf16x2(__uint_as_float(o[c]) * inv, __uint_as_float(o[c + 1]) * inv);
+                        pk.y = pack_bf16x2(__uint_as_float(o[c + 2]) * inv, __uint_as_float(o[c + 3]) * inv);
+                        pk.z = pack_bf16x2(__uint_as_float(o[c + 4]) * inv, __uint_as_float(o[c + 5]) * inv);
+                        pk.w = pack_bf16x2(__uint_as_float(o[c + 6]) * inv, __uint_as_float(o[c + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + c) = pk;
+                    }
+                }
+            }
+        } else if (!failed && !abort_s) {
+            abort_s = 1;
+            atomicExch(p.status, 16);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base_s), "r"(TMEM_COLS));
+    }
+}
+
+template <int D>
+static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p,
+                          int n_tiles, cudaStream_t stream) {
+    constexpr int SMEM = (D / 64) * AT_ATOM /*Q*/ + 2 * AT_ATOM /*P*/ + 4 * (D / 64) * AT_ATOM /*K,V x2*/ + 1024 + 128;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    acv_launch(PDL_MISC, attn_tc_kernel<D>, dim3(n_tiles, p.NH), AT_THREADS, SMEM, stream, mq, mk, mv, p);
+    return acv_launch_status();
+}
+
+// q: the step's stacked projection [T, q_width] (queries are its first NH*D columns, row stride q_stride);
+// pages [num_pages, NKV, page_size, D]; tile lists as for the tiled kernel, with tiles of 128 query tokens.
+// Takes head sizes 64 and 128 and page sizes that are powers of two from 8 to 128.
+ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
+                             const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
+                             const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int D,
+                             int page_size, int num_pages, float scale, int window, int* status, cudaStream_t stream) {
+    if (n_tiles <= 0) return 0;
+    if (NKV <= 0 || NH % NKV || NH > 65535 || (D != 64 && D != 128)) return ACV_ERR_SIZE;
+    int page_shift = -1;
+    for (int b = 3; b <= 7; ++b)
+        if ((1 << b) == page_size) page_shift = b;
+    if (page_shift < 0) return ACV_ERR_SIZE;
+    if (((uintptr_t)q & 15) || (q_stride % 8) || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
+        ((uintptr_t)out & 15) || (out_stride % 8))
+        return ACV_ERR_ALIGN;
+    CUtensorMap mq, mk, mv;
+    int rc = make_map(&mq, q, T, NH * D, q_stride, AT_BM);
+    if (rc) return rc;
+    const long long pool_rows = (long long)num_pages * NKV * page_size;
+    if (pool_rows > 0x7fffffffLL) return ACV_ERR_SIZE;
+    rc = make_map(&mk, k_pages, (int)pool_rows, D, D, page_size);
+    if (rc) return rc;
+    rc = make_map(&mv, v_pages, (int)pool_rows, D, D, page_size);
+    if (rc) return rc;
+    AttnTcParams p;
+    p.out = (bf16*)out; p.out_stride = out_stride; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.cu_q = cu_q;
+    p.kv_len = kv_len; p.block_table = block_table; p.bt_stride = bt_stride; p.NH = NH; p.NKV = NKV;
+    p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.scale = scale;
+    p.status = status;
+    if (D == 64) return launch_attn_tc<64>(mq, mk, mv, p, n_tiles, stream);
+    return launch_attn_tc<128>(mq, mk, mv, p, n_tiles, stream);
+}

@@ -55,7 +55,7 @@ class StepContext:
         return max(self.q_lens, default=0)
 
 
-QUERY_TILE = 64   # query tokens per tile of the portion-attention kernel
+QUERY_TILE = 128   # query tokens per tile of the portion-attention kernels
 
 
 def _round4(n: int) -> int:

@@ -75,6 +75,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, P],
+        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
@@ -381,6 +382,25 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
     return out
 
 
+def attention_tc(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                 tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
+                 block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 window: int) -> torch.Tensor:
+    """Causal attention of portions of prompts on tcgen05 (tiles of QUERY_TILE query tokens, pages by TMA)."""
+    _, _, status = _gemm_buffers(q.device, 0, 0)
+    _check(library().acv_attention_tc(
+        _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0),
+        n_tiles, _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim,
+        k_pages.shape[2], k_pages.shape[0], scale, window, _p(status), _stream()), "attention_tc")
+    return out
+
+
+def attention_tc_takes(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, head_dim: int) -> bool:
+    page = k_pages.shape[2]
+    return (head_dim in (64, 128) and page in (8, 16, 32, 64, 128) and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+            and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0 and k_pages.is_contiguous())
+
+
 def tensor_core_attention_takes(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
     return dtype == torch.bfloat16 and head_dim in (64, 128) and num_heads // num_kv_heads <= 16
 
@@ -404,7 +424,10 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
         attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
                          block_table, num_heads, num_kv_heads, head_dim, scale, window,
                          w.get("n_splits") or decode_splits(w["n_dec"], num_kv_heads, kv), w["max_dec_kv"])
-    if w["n_tiles"]:
+    if w["n_tiles"] and attention_tc_takes(qkv, out, k_pages, head_dim):
+        attention_tc(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
+                     block_table, num_heads, num_kv_heads, head_dim, scale, window)
+    elif w["n_tiles"]:
         attention_chunk(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
                         block_table, num_heads, num_kv_heads, head_dim, scale, window)
     return out

@@ -41,7 +41,7 @@ def gemm_case(M: int, N: int, K: int, reps: int) -> None:
           f"{N * K * 2 / us / 1e3:.0f} GB/s of weights, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
 
 
-def attention_case(batch: int, q_len: int, context: int, reps: int) -> None:
+def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool = False) -> None:
     NH, NKV, D, page = 32, 8, 128, 16
     pages_per = (context + page - 1) // page
     n_pages = batch * pages_per
@@ -66,11 +66,12 @@ def attention_case(batch: int, q_len: int, context: int, reps: int) -> None:
         tiles = [(b, s) for b in range(batch) for s in range(0, q_len, QUERY_TILE)][::-1]
         tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
         tile_q0 = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
-        fn = lambda i: ops.attention_chunk(qkv, out, *pools[i % sets], tile_seq, tile_q0, len(tiles), cu_q, kv_len,
-                                           table, NH, NKV, D, D ** -0.5, 0)
+        kernel = ops.attention_chunk if legacy else ops.attention_tc
+        fn = lambda i: kernel(qkv, out, *pools[i % sets], tile_seq, tile_q0, len(tiles), cu_q, kv_len, table, NH, NKV,
+                              D, D ** -0.5, 0)
         us = _time(fn, reps)
         flops = batch * 4.0 * NH * D * (q_len * (context - q_len) + q_len * (q_len + 1) / 2)
-        print(f"attention_chunk batch={batch} q_len={q_len} context={context}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+        print(f"{kernel.__name__} batch={batch} q_len={q_len} context={context}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
 
 
 CASES = {
@@ -81,6 +82,8 @@ CASES = {
     "attention_decode": lambda r: attention_case(8, 1, 2048, r),
     "attention_decode_b64": lambda r: attention_case(64, 1, 2048, r),
     "attention_prefill": lambda r: attention_case(1, 2048, 2048, r),
+    "attention_prefill_8k": lambda r: attention_case(1, 2048, 8192, r),
+    "attention_prefill_mma_sync": lambda r: attention_case(1, 2048, 2048, r, legacy=True),
 }
 
 
