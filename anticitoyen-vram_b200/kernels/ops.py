@@ -225,8 +225,8 @@ def _gemm_buffers(device, ws_floats: int, n_counters: int):
     return have
 
 
-def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int]:
-    """(swap, bn, splits) for x[M,K] @ w[N,K]^T.
+def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int, int]:
+    """(swap, bn, splits, stages) for x[M,K] @ w[N,K]^T.
 
     Up to 128 tokens the weight rows fill the tensor core's M = 128 and the tokens are the narrow
     side (weights stream once whatever the batch); above, tokens are the M side with 256 features
@@ -235,8 +235,15 @@ def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int]:
     if M <= 128:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = -(-N // 128) * -(-M // bn)
+        if bn >= 64:
+            # wide token tiles: a split costs a reduction over bn columns, so with enough tiles two CTAs share
+            # an SM instead (4 stages each), and a split is used only to reach the SM count
+            if tiles >= _SM_COUNT:
+                return 1, bn, 1, 4
+            s = 4 if n_kb >= 128 else max(1, min(4, round(_SM_COUNT / tiles / 2)))
+            return 1, bn, s, 6
         if tiles >= 2 * _SM_COUNT:
-            return 1, bn, 1
+            return 1, bn, 1, 8
         best, best_score = 1, -1.0
         for s in range(1, 9):
             if s > 1 and n_kb // s < 8:
@@ -245,9 +252,9 @@ def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int]:
             score = items / (-(-items // _SM_COUNT) * _SM_COUNT) - 0.02 * (s - 1)
             if score > best_score:
                 best, best_score = s, score
-        return 1, bn, best
+        return 1, bn, best, 8
     bn = 256 if N >= 256 else 128 if N > 64 else 64
-    return 0, bn, 1
+    return 0, bn, 1, 8
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | None = None,
