@@ -81,6 +81,33 @@ inline int acv_pdl_flag = 0x3;   // bit set of kernel classes launched with the 
 #define PDL_MISC 32
 
 template <typename... KArgs, typename... Args>
+static inline void acv_launch_cluster(int kernel_class, int cluster_x, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+                                      size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (acv_pdl_flag & kernel_class) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {     // thread-block clusters: the CTAs of a cluster can write each other's shared memory
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster_x;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+template <typename... KArgs, typename... Args>
 static inline void acv_launch(int kernel_class, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                               cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};

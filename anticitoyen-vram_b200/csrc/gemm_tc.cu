@@ -41,6 +41,7 @@ struct GemmParams {
     int out_f32;
     int act;                // 1: output features come in (gate, up) pairs and C[:, n/2] = silu(gate) * up
     int tiles_a, tiles_b, splits, kb_per_split, n_kb;
+    int cluster;            // 1: the splits of a tile are the CTAs of one cluster and are summed through its shared memory
     int stages;             // pipeline depth (2..8); shared memory = stages * (128 + BN) * 128 bytes
     void* C;
     float* workspace;       // [tiles][splits][BN][128] floats when splits > 1
@@ -124,7 +125,10 @@ struct GemmShape {
     static constexpr int STAGE_BYTES = (GT_BM + BN) * GT_BK * 2;
     static constexpr int MAX_STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;     // two accumulator buffers; a power of two
-    static constexpr int smem_bytes(int stages) { return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/; }
+    static constexpr int PART_BYTES = BN * GT_BM * 4;                 // one CTA's partial tile in float
+    static constexpr int smem_bytes(int stages, int cluster_parts) {
+        return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + cluster_parts * PART_BYTES;
+    }
 };
 
 template <int BN>
@@ -139,6 +143,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
     const uint32_t full0 = gt_smem(bars), empty0 = full0 + 8 * STAGES;
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+    const uint32_t part0 = gt_smem(tiles) + STAGES * S::STAGE_BYTES + 256;     // [splits-1][BN][128] floats (cluster mode)
+    const bool cluster_split = p.cluster && p.splits > 1;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
     __shared__ int last_s;
@@ -238,6 +244,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
                 continue;
             }
+            if (cluster_split) {
+                // ---- split K inside a cluster: ranks 1.. put their partial tile into rank 0's shared memory;
+                // rank 0 adds them to its own after the cluster barrier below (one item per CTA in this mode)
+                const uint32_t rank = cluster_ctarank();
+                if (rank != 0) {
+                    const uint32_t remote = cluster_map(part0, 0) + (rank - 1) * S::PART_BYTES + (wq * 32 + lane) * 4;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < BN; c0 += 16) {
+                        uint32_t r[16];
+                        tc_ld16(taddr + c0, r);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) cluster_store_f32(remote + (c0 + c) * (GT_BM * 4), __uint_as_float(r[c]));
+                    }
+                }
+                break;
+            }
             // ---- split K: partial tile to the workspace, the CTA that arrives last sums in split order
             float* ws = p.workspace + ((size_t)tile * p.splits + split) * (BN * GT_BM);
 #pragma unroll 1
@@ -279,6 +301,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         }
     }
 
+    if (cluster_split) {
+        cluster_sync_all();         // every partial tile lies in rank 0's shared memory
+        if (warp >= 2 && cluster_ctarank() == 0 && !abort_s) {
+            const int wq = warp & 3;
+            const int tile = blockIdx.x / p.splits;
+            const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+            const int row_a = ta * GT_BM + wq * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16);
+            const float* part = reinterpret_cast<const float*>(tiles + STAGES * S::STAGE_BYTES + 256) + wq * 32 + lane;
+            const int rows_b = min(BN, p.RB - tb * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (c0 >= rows_b) break;
+                uint32_t r[16];
+                tc_ld16(taddr + c0, r);
+                float sum[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) sum[c] = __uint_as_float(r[c]);
+                for (int sp = 1; sp < p.splits; ++sp)           // split order: the sum does not depend on timing
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) sum[c] += part[((sp - 1) * BN + c0 + c) * GT_BM];
+                gt_store16(p, row_a, tb * BN + c0, sum, lane);
+            }
+        }
+    }
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -294,8 +341,12 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     using S = GemmShape<BN>;
     if (stages < 2) stages = 2;
     if (stages > S::MAX_STAGES) stages = S::MAX_STAGES;
+    // cluster mode needs room for the peers' partial tiles beside the pipeline; else the global workspace serves
+    int parts = p.cluster && p.splits > 1 ? p.splits - 1 : 0;
+    if (parts && (p.splits > 8 || parts * S::PART_BYTES > 100 * 1024)) { p.cluster = 0; parts = 0; }
+    while (parts && stages > 2 && S::smem_bytes(stages, parts) > 226 * 1024) --stages;
     p.stages = stages;
-    const int smem = S::smem_bytes(stages);
+    const int smem = S::smem_bytes(stages, parts);
     static int configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -309,8 +360,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     if (per_sm > 4) per_sm = 4;
     const long long items = (long long)p.tiles_a * p.tiles_b * p.splits;
     const long long cap = (long long)sm_count * per_sm;
-    const int grid = (int)(items < cap ? items : cap);
-    acv_launch(PDL_GEMM, gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
+    const int grid = (int)(parts ? items : (items < cap ? items : cap));
+    acv_launch_cluster(PDL_GEMM, parts ? p.splits : 1, gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
     return acv_launch_status();
 }
 
@@ -320,7 +371,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
 // status: one int, 0 unless a bounded wait inside the kernel ran out.
 ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
                         int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
-                        int* counters, long long n_counters, int* status, int sm_count, int stages,
+                        int* counters, long long n_counters, int* status, int sm_count, int stages, int cluster,
                         cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACV_ERR_ALIGN;
@@ -329,7 +380,7 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
     const void* b_ptr = swap ? x : w;
     p.RA = swap ? N : M;
     p.RB = swap ? M : N;
-    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.act = act;
+    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.act = act; p.cluster = cluster;
     if (act && (out_f32 || (N & 1))) return ACV_ERR_SIZE;
     p.tiles_a = (p.RA + GT_BM - 1) / GT_BM;
     p.tiles_b = (p.RB + bn - 1) / bn;

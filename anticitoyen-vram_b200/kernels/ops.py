@@ -73,7 +73,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
-        "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, P],
+        "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, P],
         "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
@@ -235,24 +235,21 @@ def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int, int]:
     if M <= 128:
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = -(-N // 128) * -(-M // bn)
-        if bn >= 64:
-            # wide token tiles: a split costs a reduction over bn columns, so with enough tiles two CTAs share
-            # an SM instead (4 stages each), and a split is used only to reach the SM count
-            if tiles >= _SM_COUNT:
-                return 1, bn, 1, 4
-            s = 4 if n_kb >= 128 else max(1, min(4, round(_SM_COUNT / tiles / 2)))
-            return 1, bn, s, 6
+        # measured on a B200 at the layer sizes of Qwen3-8B (splits are CTAs of one cluster, summed through
+        # its shared memory): enough tiles -> no split, several CTAs per SM instead; few tiles -> 2..4 splits
         if tiles >= 2 * _SM_COUNT:
             return 1, bn, 1, 8
-        best, best_score = 1, -1.0
-        for s in range(1, 9):
-            if s > 1 and n_kb // s < 8:
-                break
-            items = tiles * s
-            score = items / (-(-items // _SM_COUNT) * _SM_COUNT) - 0.02 * (s - 1)
-            if score > best_score:
-                best, best_score = s, score
-        return 1, bn, best, 8
+        if tiles >= _SM_COUNT:
+            return (1, bn, 2, 3) if bn <= 16 else (1, bn, 1, 4)
+        if n_kb < 16:
+            return 1, bn, 1, 8
+        if n_kb >= 128:
+            return 1, bn, 4, 8 if bn <= 32 else 6
+        if bn <= 16:
+            return 1, bn, 4, 4 if tiles * 4 > _SM_COUNT else 6
+        if bn == 32:
+            return 1, bn, 4 if tiles <= 32 else 2, 6
+        return 1, bn, 3, 6
     bn = 256 if N >= 256 else 128 if N > 64 else 64
     return 0, bn, 1, 8
 
@@ -276,12 +273,13 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
     plan = plan or gemm_tc_plan(M, N, K)
     swap, bn, splits = plan[:3]
     stages = plan[3] if len(plan) > 3 else 8
+    cluster = plan[4] if len(plan) > 4 else (1 if swap and 1 < splits <= 8 else 0)
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     _check(library().acv_gemm_tc(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
                                  1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits,
                                  _p(ws), ws.numel(), _p(cnt),
-                                 cnt.numel(), _p(status), _SM_COUNT, stages, _stream()), "gemm_tc")
+                                 cnt.numel(), _p(status), _SM_COUNT, stages, cluster, _stream()), "gemm_tc")
     return out
 
 
