@@ -31,13 +31,15 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    const int* __restrict__ dec_tokens, const int* __restrict__ dec_seqs,
                    const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride, int NH, int NKV,
                    int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
-                   float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters) {
+                   float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
+                   int cluster_merge) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
     constexpr int WT_BYTES = 16 * D * 2;                         // 16 keys (or values) of one kv-head
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                                   // [16][D]
     unsigned char* ring = smem + 16 * D * 2;                     // [4 warps][AD_STAGES][K, V][16][D]
     int* pg_s = reinterpret_cast<int*>(ring + 4 * AD_STAGES * 2 * WT_BYTES);   // [pg_cap] pages of this CTA's keys
+    float* cm_s = reinterpret_cast<float*>(pg_s + ((pg_cap + 3) & ~3));          // [n_splits][NH/NKV][D + 2] (cluster merge)
     __shared__ int is_last_s;
 
     pdl_launch_dependents();
@@ -268,6 +270,15 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         }
         if (n_splits == 1) {
             out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else if (cluster_merge) {
+            // the splits of a (request, kv-head) are the CTAs of one cluster: each puts its partial into rank 0's
+            // shared memory, rank 0 merges them after the cluster barrier
+            const uint32_t dst = cluster_map(smem_u32(cm_s), 0) + ((split * n_rep + r) * (D + 2) + d) * 4;
+            cluster_store_f32(dst, O);
+            if (d == 0) {
+                cluster_store_f32(dst + D * 4, M);
+                cluster_store_f32(dst + (D + 1) * 4, L);
+            }
         } else {
             part_acc[(part * n_rep + r) * D + d] = O;
             if (d == 0) {
@@ -277,6 +288,26 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         }
     }
     if (n_splits == 1) return;
+    if (cluster_merge) {
+        cluster_sync_all();
+        if (split != 0) return;
+        for (int idx = tid; idx < n_rep * D; idx += AD_THREADS) {
+            const int r = idx / D, d = idx % D;
+            float M = -INFINITY;
+            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, cm_s[(sp * n_rep + r) * (D + 2) + D]);
+            float L = 0.f, O = 0.f;
+            if (M != -INFINITY) {
+                for (int sp = 0; sp < n_splits; ++sp) {          // split order: the sum does not depend on timing
+                    const float* ps = cm_s + (sp * n_rep + r) * (D + 2);
+                    const float f = exp2f(ps[D] - M);
+                    L += ps[D + 1] * f;
+                    O += ps[d] * f;
+                }
+            }
+            out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+        return;
+    }
 
     // ---- the block that arrives last merges the splits, in split order
     __threadfence();
@@ -311,7 +342,7 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
                          const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
                          const int* block_table, int bt_stride, int NH, int NKV, int page_size, int num_pages,
                          float scale, int window, int n_splits, float* part_acc, float* part_ml, int* counters,
-                         int max_kv, cudaStream_t stream) {
+                         int max_kv, int cluster_merge, cudaStream_t stream) {
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
@@ -319,7 +350,10 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     const int chunk = (((keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
     int pg_cap = chunk / page_size + 2;
     if (pg_cap > 8192) pg_cap = 8192;
-    const int smem = 16 * D * 2 + 4 * AD_STAGES * 2 * 16 * D * 2 + pg_cap * 4;
+    if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
+    const int n_rep = NH / NKV;
+    const int smem = 16 * D * 2 + 4 * AD_STAGES * 2 * 16 * D * 2 + ((pg_cap + 3) & ~3) * 4 +
+                     (cluster_merge ? n_splits * n_rep * (D + 2) * 4 : 0);
     static int configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -327,10 +361,10 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
         configured = smem;
     }
     dim3 grid(n_dec, NKV, n_splits);
-    acv_launch(PDL_ATTN, attn_decode_kernel<D>, grid, AD_THREADS, smem, stream,
+    acv_launch_cluster(PDL_ATTN, dim3(1, 1, cluster_merge ? n_splits : 1), attn_decode_kernel<D>, grid, AD_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
         dec_seqs, kv_len, block_table, bt_stride, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
-        n_splits, part_acc, part_ml, counters);
+        n_splits, part_acc, part_ml, counters, cluster_merge);
     return acv_launch_status();
 }
 
@@ -342,20 +376,21 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
                                  const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int D,
                                  int page_size, int num_pages, float scale, int window, int n_splits, float* part_acc,
                                  float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
-                                 long long scratch_counters, int max_kv, cudaStream_t stream) {
+                                 long long scratch_counters, int max_kv, int cluster_merge, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH / NKV > 16 || n_splits < 1 || n_splits > 65535 || NKV > 65535) return ACV_ERR_SIZE;
     if (((uintptr_t)q & 15) || ((size_t)q_stride * 2) % 16 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15))
         return ACV_ERR_ALIGN;
     const long long n_rep = NH / NKV;
-    if (n_splits > 1) {
+    if (n_splits > 1 && !(cluster_merge && n_splits <= 8)) {
         const long long parts = (long long)n_dec * NKV * n_splits;
         if (parts * n_rep * D > scratch_floats || parts * n_rep * 2 > scratch_ml_floats ||
             (long long)n_dec * NKV > scratch_counters)
             return ACV_ERR_SCRATCH;
     }
 #define AD_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
-                bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, max_kv, stream
+                bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, max_kv, \
+                cluster_merge, stream
     switch (D) {
         case 64: return launch_decode<64>(AD_ARGS);
         case 128: return launch_decode<128>(AD_ARGS);
@@ -423,5 +458,5 @@ ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, 
     if (e != cudaSuccess) return (int)e;
     return acv_attention_decode(q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len,
                                 block_table, bt_stride, NH, NKV, D, page_size, num_pages, scale, window, n_splits,
-                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, stream);
+                                part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, stream);
 }

@@ -81,7 +81,7 @@ inline int acv_pdl_flag = 0x3;   // bit set of kernel classes launched with the 
 #define PDL_MISC 32
 
 template <typename... KArgs, typename... Args>
-static inline void acv_launch_cluster(int kernel_class, int cluster_x, void (*kernel)(KArgs...), dim3 grid, dim3 block,
+static inline void acv_launch_cluster(int kernel_class, dim3 cluster, void (*kernel)(KArgs...), dim3 grid, dim3 block,
                                       size_t smem, cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -95,11 +95,11 @@ static inline void acv_launch_cluster(int kernel_class, int cluster_x, void (*ke
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_x > 1) {     // thread-block clusters: the CTAs of a cluster can write each other's shared memory
+    if (cluster.x * cluster.y * cluster.z > 1) {     // thread-block clusters: CTAs of a cluster can write each other's shared memory
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = cluster_x;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = 1;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     cfg.attrs = attr;
@@ -123,4 +123,25 @@ static inline void acv_launch(int kernel_class, void (*kernel)(KArgs...), dim3 g
         cfg.numAttrs = 1;
     }
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+// ----------------------------------------------------------------------------- thread-block clusters
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// address, in the cluster's shared window, of this CTA's shared address `local` in the CTA of rank `rank`
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_store_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+// every thread of every CTA of the cluster passes here once (release before, acquire after)
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }

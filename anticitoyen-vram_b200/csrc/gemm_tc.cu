@@ -361,7 +361,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     const long long items = (long long)p.tiles_a * p.tiles_b * p.splits;
     const long long cap = (long long)sm_count * per_sm;
     const int grid = (int)(parts ? items : (items < cap ? items : cap));
-    acv_launch_cluster(PDL_GEMM, parts ? p.splits : 1, gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
+    acv_launch_cluster(PDL_GEMM, dim3(parts ? p.splits : 1, 1, 1), gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
     return acv_launch_status();
 }
 

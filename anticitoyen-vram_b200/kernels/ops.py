@@ -74,7 +74,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
-        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, I, P],
         "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
         "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
         "acv_argmax": [P, I, I, I, P, P],
@@ -361,16 +361,20 @@ def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                      dec_tokens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, kv_len: torch.Tensor,
                      block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                     window: int, n_splits: int, max_kv: int = 0) -> torch.Tensor:
-    """Attention of requests that bring one token each, over their pages, split over the context."""
+                     window: int, n_splits: int, max_kv: int = 0, cluster_merge: bool = True) -> torch.Tensor:
+    """Attention of requests that bring one token each, over their pages, split over the context.
+
+    Up to 8 splits are merged inside a thread-block cluster (through its shared memory); more, or
+    ``cluster_merge=False``, go through partial results in scratch memory and a last-arriver merge."""
     n_rep = num_heads // num_kv_heads
-    parts = n_dec * num_kv_heads * n_splits if n_splits > 1 else 0
+    use_cluster = cluster_merge and 1 < n_splits <= 8
+    parts = n_dec * num_kv_heads * n_splits if n_splits > 1 and not use_cluster else 0
     acc, ml, cnt = _decode_scratch(q.device, parts * n_rep * head_dim, parts * n_rep * 2, n_dec * num_kv_heads)
     _check(library().acv_attention_decode(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(dec_tokens), _p(dec_seqs), n_dec,
         _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim, k_pages.shape[2],
         k_pages.shape[0], scale, window, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
-        max_kv or block_table.shape[1] * k_pages.shape[2], _stream()), "attention_decode")
+        max_kv or block_table.shape[1] * k_pages.shape[2], 1 if use_cluster else 0, _stream()), "attention_decode")
     return out
 
 
