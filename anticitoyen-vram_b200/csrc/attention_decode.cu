@@ -42,6 +42,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     float* cm_s = reinterpret_cast<float*>(pg_s + ((pg_cap + 3) & ~3));          // [n_splits][NH/NKV][D + 2] (cluster merge)
     __shared__ int is_last_s;
 
+    ACV_TL(TL_ATTN_DECODE, 0);
     pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -227,6 +228,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     }
     cp_async_wait<0>();
     __syncthreads();
+    if (tid == 0) ACV_TL_MARK(TL_M_ATTN_LOOP_DONE);
 
     // ---- merge the four warps through shared memory (the tiles are no longer needed)
     float* wm = reinterpret_cast<float*>(ring);           // [4][16]
@@ -460,3 +462,5 @@ ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, 
                                 block_table, bt_stride, NH, NKV, D, page_size, num_pages, scale, window, n_splits,
                                 part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, stream);
 }
+
+ACV_TL_EXPORT(attention_decode)

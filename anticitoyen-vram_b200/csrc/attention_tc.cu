@@ -56,6 +56,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     __shared__ volatile int abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ACV_TL(TL_ATTN_TC, 64);
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         abort_s = 0;
@@ -309,3 +310,5 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
     if (D == 64) return launch_attn_tc<64>(mq, mk, mv, p, n_tiles, stream);
     return launch_attn_tc<128>(mq, mk, mv, p, n_tiles, stream);
 }
+
+ACV_TL_EXPORT(attention_tc)

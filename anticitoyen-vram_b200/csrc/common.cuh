@@ -67,12 +67,15 @@ static inline int acv_launch_status() { return (int)cudaGetLastError(); }
 // waits for its predecessor's results (pdl_wait) before it touches global memory.  What comes
 // before that wait overlaps the predecessor's tail: block start-up, barrier set-up, tensor-memory
 // allocation.  Launched without the attribute, both instructions do nothing.  Which kernel classes
-// get the attribute is a bit set (acv_set_pdl); measured on the decode step of a Qwen3-8B shape,
-// the matrix product and the norm gain from it, the others do not, so those two are the default.
+// get the attribute is a bit set (acv_set_pdl); measured on the decode step of a Qwen3-8B shape with
+// the device timeline, every class gains (the gaps of 1.7 us before the rotation and the attention
+// kernels close), so all are on by default.  A kernel launched with the attribute must execute
+// pdl_wait in every CTA before it reads or writes what earlier kernels touch: its own successor's
+// wait covers only this kernel's completion, which therefore has to imply its predecessors'.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-inline int acv_pdl_flag = 0x3;   // bit set of kernel classes launched with the attribute; acv_set_pdl changes it
+inline int acv_pdl_flag = 0x3f;   // bit set of kernel classes launched with the attribute; acv_set_pdl changes it
 #define PDL_GEMM 1
 #define PDL_NORM 2
 #define PDL_ROPE 4
@@ -145,3 +148,85 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+
+// ----------------------------------------------------------------------------- timeline (diagnostic builds only)
+// Compiled with -DACV_TIMELINE every instrumented kernel logs, per CTA, when it began and ended (the
+// device-wide nanosecond timer), its kernel id, block, grid size and SM; single events carry an id of their
+// own.  Each source file keeps its own log (no relocatable device code); acv_tl_read_<file> copies it out.
+// Without the flag the macros expand to nothing.
+#ifdef ACV_TIMELINE
+#define ACV_TL_CAP (1 << 16)
+#define ACV_TL_MARKS 8
+struct AcvTlRecord { unsigned long long t0, t1; int kernel, block, grid, smid; unsigned long long mark[ACV_TL_MARKS]; };
+static __device__ AcvTlRecord acv_tl_log[ACV_TL_CAP];
+static __device__ unsigned int acv_tl_count;
+__device__ __forceinline__ unsigned long long acv_tl_now() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// begin at construction, end at destruction; the marks of the CTA's threads wait in shared memory and the
+// whole record is written once, by one thread, when the kernel ends (nothing is sent to memory before)
+struct AcvTlScope {
+    unsigned long long t0; int kernel; bool mine; unsigned long long* marks;
+    __device__ __forceinline__ AcvTlScope(int k, int thread, unsigned long long* m)
+        : kernel(k), mine((int)threadIdx.x == thread), marks(m) {
+        if (mine) {
+            t0 = acv_tl_now();
+            for (int i = 0; i < ACV_TL_MARKS; ++i) marks[i] = 0;
+        }
+    }
+    __device__ __forceinline__ ~AcvTlScope() {
+        if (!mine) return;
+        const unsigned long long t1 = acv_tl_now();
+        const unsigned int i = atomicAdd(&acv_tl_count, 1u);
+        if (i >= ACV_TL_CAP) return;
+        unsigned int smid;
+        asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+        AcvTlRecord r;
+        r.t0 = t0; r.t1 = t1; r.kernel = kernel;
+        r.block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+        r.grid = gridDim.x * gridDim.y * gridDim.z; r.smid = (int)smid;
+        for (int k = 0; k < ACV_TL_MARKS; ++k) r.mark[k] = marks[k];
+        acv_tl_log[i] = r;
+    }
+};
+#define ACV_TL(kernel_id, thread)                                   \
+    __shared__ unsigned long long acv_tl_marks[ACV_TL_MARKS];       \
+    AcvTlScope acv_tl_scope(kernel_id, thread, acv_tl_marks)
+#define ACV_TL_MARK(i) (acv_tl_marks[i] = acv_tl_now())             // by one thread; i < ACV_TL_MARKS
+#define ACV_TL_EXPORT(file)                                                                                     \
+    ACV_API int acv_tl_read_##file(void* host, int cap, int reset) {                                            \
+        unsigned int n = 0;                                                                                     \
+        if (cudaMemcpyFromSymbol(&n, acv_tl_count, sizeof(n)) != cudaSuccess) return -1;                        \
+        if (n > ACV_TL_CAP) n = ACV_TL_CAP;                                                                     \
+        if ((int)n > cap) n = cap;                                                                              \
+        if (n && cudaMemcpyFromSymbol(host, acv_tl_log, n * sizeof(AcvTlRecord)) != cudaSuccess) return -1;     \
+        if (reset) { const unsigned int z = 0; cudaMemcpyToSymbol(acv_tl_count, &z, sizeof(z)); }               \
+        return (int)n;                                                                                          \
+    }
+#else
+#define ACV_TL(kernel_id, thread)
+#define ACV_TL_MARK(i)
+#define ACV_TL_EXPORT(file)
+#endif
+// kernel ids of the timeline
+#define TL_GEMM 1
+#define TL_NORM 2
+#define TL_ROPE 3
+#define TL_ATTN_DECODE 4
+#define TL_ATTN_TC 5
+#define TL_ATTN_CHUNK 6
+#define TL_EMBED 7
+#define TL_ARGMAX 8
+#define TL_SWIGLU 9
+// marks of the matrix product
+#define TL_M_FIRST_FULL 0      // the first operand stage has landed
+#define TL_M_LAST_MMA 1        // the last k-block has been issued
+#define TL_M_ACC_DONE 2        // the epilogue sees the finished accumulator
+#define TL_M_PART_SENT 3       // split K in a cluster: this CTA's partial tile is on its way to rank 0
+#define TL_M_CLUSTER_MET 4     // ... and the cluster's CTAs have met
+#define TL_M_STORED 5          // the CTA's results are written
+#define TL_M_WAIT_OVER 6       // the producer's wait for the predecessor has ended
+// marks of the decode attention
+#define TL_M_ATTN_LOOP_DONE 0  // a CTA's keys are done, the merge begins

@@ -13,6 +13,7 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ tokens, T* __restrict__ out,
                              int H, int V) {
+    ACV_TL(TL_EMBED, 0);
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -78,6 +79,7 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ 
                                        T* __restrict__ out, const int* __restrict__ rows, int H, float eps) {
     constexpr int E = 16 / sizeof(T);          // elements per 16-byte chunk
     __shared__ float red[32];
+    ACV_TL(TL_NORM, 0);
     pdl_launch_dependents();
     pdl_wait();
     const int r_out = blockIdx.x;
@@ -243,3 +245,5 @@ ACV_API int acv_swiglu(const void* gu, void* out, int T, int I, int dtype, cudaS
 
 // Bit set of the kernel classes (PDL_* in common.cuh) launched with programmatic stream serialization; 0: none.
 ACV_API void acv_set_pdl(int classes) { acv_pdl_flag = classes; }
+
+ACV_TL_EXPORT(elementwise)

@@ -41,6 +41,7 @@ struct GemmParams {
     int out_f32;
     int act;                // 1: output features come in (gate, up) pairs and C[:, n/2] = silu(gate) * up
     int tiles_a, tiles_b, splits, kb_per_split, n_kb;
+    int early_w;            // 1: the weights were written long before this launch: their first tiles are loaded before the predecessor ends
     int cluster;            // 1: the splits of a tile are the CTAs of one cluster and are summed through its shared memory
     int stages;             // pipeline depth (2..8); shared memory = stages * (128 + BN) * 128 bytes
     void* C;
@@ -150,6 +151,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __shared__ int last_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    ACV_TL(TL_GEMM, 64);
     pdl_launch_dependents();
     if (threadIdx.x == 0) {
         abort_s = 0;
@@ -172,7 +174,23 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
+            // The weights do not depend on the kernel before this one: the first stages' weight tiles are
+            // asked for at once, while the predecessor still runs, and only the activations wait for it.
+            int early = 0;
+            if (p.early_w && (int)blockIdx.x < n_items) {
+                const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
+                const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+                const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
+                early = min(STAGES, kb1 - kb0);
+                for (int i = 0; i < early; ++i) {
+                    mbar_expect_tx(full0 + 8 * i, S::STAGE_BYTES);
+                    const uint32_t a_dst = tiles_addr + i * S::STAGE_BYTES;
+                    if (p.swap) tma_load_2d(a_dst, &map_a, full0 + 8 * i, (kb0 + i) * GT_BK, ta * GT_BM);
+                    else tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * i, (kb0 + i) * GT_BK, tb * BN);
+                }
+            }
             pdl_wait();             // the activations are the predecessor's output
+            ACV_TL_MARK(TL_M_WAIT_OVER);
             int s = 0;              // stage of the current k-block, and the parity its "empty" barrier is awaited with
             uint32_t ph = 0;
             for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x) {
@@ -180,11 +198,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
-                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 1); break; }
-                    mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
                     const uint32_t a_dst = tiles_addr + s * S::STAGE_BYTES;
-                    tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * GT_BK, ta * GT_BM);
-                    tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * s, kb * GT_BK, tb * BN);
+                    const bool half_done = early > 0;       // this stage's weight tile is already on its way
+                    if (half_done) {
+                        --early;
+                    } else {
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 1); break; }
+                        mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
+                    }
+                    if (!(half_done && p.swap)) tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * GT_BK, ta * GT_BM);
+                    if (!(half_done && !p.swap)) tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * s, kb * GT_BK, tb * BN);
                 }
             }
         }
@@ -205,6 +228,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     if (!mbar_wait(full0 + 8 * s, ph, &abort_s)) { abort_s = 1; atomicExch(p.status, 3); failed = true; break; }
                     tc_fence_after();
+                    if (local == 0 && kb == kb0) ACV_TL_MARK(TL_M_FIRST_FULL);
                     const uint32_t a_addr = tiles_addr + s * S::STAGE_BYTES, b_addr = a_addr + GT_BM * GT_BK * 2;
 #pragma unroll
                     for (int k = 0; k < GT_BK / 16; ++k)
@@ -213,6 +237,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 }
                 if (failed) break;
                 tc_commit(tfull0 + 8 * buf);        // the accumulator is complete
+                if (item + (int)gridDim.x >= n_items) ACV_TL_MARK(TL_M_LAST_MMA);
             }
         }
     } else {
@@ -227,6 +252,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const uint32_t buf = local & 1, use = local >> 1;
             if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 4); break; }
             tc_fence_after();
+            if (et == 0 && item + (int)gridDim.x >= n_items) ACV_TL_MARK(TL_M_ACC_DONE);
             const int row_a = ta * GT_BM + wq * 32 + lane;          // row of the A operand this thread holds
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(wq * 32) << 16);
             if (p.splits == 1) {
@@ -302,7 +328,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 
     if (cluster_split) {
+        if (threadIdx.x == 64) ACV_TL_MARK(TL_M_PART_SENT);
         cluster_sync_all();         // every partial tile lies in rank 0's shared memory
+        if (threadIdx.x == 64) ACV_TL_MARK(TL_M_CLUSTER_MET);
         if (warp >= 2 && cluster_ctarank() == 0 && !abort_s) {
             const int wq = warp & 3;
             const int tile = blockIdx.x / p.splits;
@@ -326,6 +354,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
         }
     }
+    if (threadIdx.x == 64) ACV_TL_MARK(TL_M_STORED);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
@@ -371,7 +400,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
 // status: one int, 0 unless a bounded wait inside the kernel ran out.
 ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
                         int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
-                        int* counters, long long n_counters, int* status, int sm_count, int stages, int cluster,
+                        int* counters, long long n_counters, int* status, int sm_count, int stages, int flags,
                         cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACV_ERR_ALIGN;
@@ -380,7 +409,7 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
     const void* b_ptr = swap ? x : w;
     p.RA = swap ? N : M;
     p.RB = swap ? M : N;
-    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.act = act; p.cluster = cluster;
+    p.K = K; p.M = M; p.N = N; p.ldc = ldc; p.swap = swap; p.out_f32 = out_f32; p.act = act; p.cluster = flags & 1; p.early_w = (flags >> 1) & 1;
     if (act && (out_f32 || (N & 1))) return ACV_ERR_SIZE;
     p.tiles_a = (p.RA + GT_BM - 1) / GT_BM;
     p.tiles_b = (p.RB + bn - 1) / bn;
@@ -407,3 +436,5 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
         default: return ACV_ERR_SIZE;
     }
 }
+
+ACV_TL_EXPORT(gemm_tc)

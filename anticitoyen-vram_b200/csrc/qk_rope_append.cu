@@ -97,6 +97,7 @@ __global__ void qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, int row_stri
                                                int num_pages) {
     constexpr int D = VEC * 32;
     struct __align__(sizeof(T) * VEC) Vec { T e[VEC]; };
+    ACV_TL(TL_ROPE, 0);
     pdl_launch_dependents();
     pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -211,3 +212,5 @@ ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, in
         return ACV_ERR_DTYPE;
     return acv_launch_status();
 }
+
+ACV_TL_EXPORT(qk_rope_append)

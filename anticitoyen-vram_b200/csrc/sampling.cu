@@ -116,6 +116,7 @@ argmax_split_kernel(const float* __restrict__ logits, int ld, int V, int* __rest
     __shared__ float redf[32];
     __shared__ int redi[32];
     __shared__ int last_s;
+    ACV_TL(TL_ARGMAX, 0);
     pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x, part = blockIdx.y;
@@ -343,3 +344,5 @@ ACV_API int acv_sample(const float* logits, int ld, int rows, int V, const float
                                                     out_token, out_logprob);
     return acv_launch_status();
 }
+
+ACV_TL_EXPORT(sampling)

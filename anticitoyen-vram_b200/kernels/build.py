@@ -27,6 +27,10 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
+LIB_PREFIX = "libacvram_b200_"
+if os.environ.get("ACVRAM_B200_TIMELINE", "0") not in ("", "0"):
+    NVCC_FLAGS.append("-DACV_TIMELINE")      # diagnostic build: kernels log their CTAs' begin and end times
+    LIB_PREFIX = "libacvram_b200tl_"         # a library of its own beside the serving one
 
 
 class BuildError(RuntimeError):
@@ -80,11 +84,11 @@ def library_path(build: bool = True, verbose: bool = True) -> str:
     """Path of the compiled library; compiles it first if it is not there."""
     tag = source_hash()
     bdir = _build_dir()
-    lib = os.path.join(bdir, f"libacvram_b200_{tag}.so")
+    lib = os.path.join(bdir, f"{LIB_PREFIX}{tag}.so")
     if os.path.isfile(lib):
         return lib
     # a library built in-tree travels with the checkout even when the folder is read-only
-    in_tree_lib = os.path.join(CSRC, "_build", f"libacvram_b200_{tag}.so")
+    in_tree_lib = os.path.join(CSRC, "_build", f"{LIB_PREFIX}{tag}.so")
     if os.path.isfile(in_tree_lib):
         return in_tree_lib
     if not build:
@@ -133,7 +137,7 @@ def _compile(bdir: str, lib: str, tag: str, verbose: bool) -> None:
             raise BuildError(f"linking {lib} failed:\n{proc.stdout}")
         os.replace(tmp, lib)
         for name in os.listdir(bdir):       # libraries of earlier source states are never loaded again
-            if name.startswith("libacvram_b200_") and name.endswith(".so") and os.path.join(bdir, name) != lib:
+            if name.startswith(LIB_PREFIX) and name.endswith(".so") and os.path.join(bdir, name) != lib:
                 try:
                     os.remove(os.path.join(bdir, name))
                 except OSError:

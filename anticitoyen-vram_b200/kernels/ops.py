@@ -56,7 +56,7 @@ def set_programmatic_launch(classes: int | bool) -> None:
     (bit set: 1 matrix product, 2 norm, 4 rope/append, 8 decode attention, 16 SwiGLU, 32 the rest;
     True = the default set, False = none)."""
     if classes is True:
-        classes = 0x3
+        classes = 0x3f
     library().acv_set_pdl(int(classes))
 
 
@@ -255,8 +255,11 @@ def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int, int]:
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | None = None,
-            swiglu_pairs: bool = False) -> torch.Tensor:
+            swiglu_pairs: bool = False, static_weights: bool = False) -> torch.Tensor:
     """out[M,N] = x[M,K] @ w[N,K]^T on tcgen05; x, w bfloat16, out bfloat16 or float32.
+
+    ``static_weights``: w was written long before this call (a model's weights), so the kernel may
+    read its first tiles while the kernel before it in the stream is still running.
 
     With ``swiglu_pairs`` the rows of w come in (gate, up) pairs and out is [M, N/2]:
     out[:, i] = silu(x . w[2i]) * (x . w[2i+1]), rounded as the separate kernels round."""
@@ -279,7 +282,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
     _check(library().acv_gemm_tc(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
                                  1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits,
                                  _p(ws), ws.numel(), _p(cnt),
-                                 cnt.numel(), _p(status), _SM_COUNT, stages, cluster, _stream()), "gemm_tc")
+                                 cnt.numel(), _p(status), _SM_COUNT, stages, cluster | (2 if static_weights else 0), _stream()), "gemm_tc")
     return out
 
 
@@ -442,21 +445,22 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     return out
 
 
-def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False) -> torch.Tensor:
     """out = x @ w^T in bfloat16 with float accumulation: the tcgen05 kernel; rows that are not 16-byte
     aligned (K or a stride no multiple of 8) go to the library product, as all do in the reference."""
     if gemm_tc_takes(x, w):
-        return gemm_tc(x, w, out)
+        return gemm_tc(x, w, out, static_weights=static_weights)
     return torch.mm(x, w.t(), out=out)
 
 
-def linear_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def linear_bf16_swiglu(x: torch.Tensor, w_pairs: torch.Tensor, out: torch.Tensor,
+                       static_weights: bool = False) -> torch.Tensor:
     """out[M, I] = silu(x @ Wg^T) * (x @ Wu^T) in one kernel; w_pairs [2I, K] holds (gate_i, up_i) in rows 2i, 2i+1."""
-    return gemm_tc(x, w_pairs, out, swiglu_pairs=True)
+    return gemm_tc(x, w_pairs, out, swiglu_pairs=True, static_weights=static_weights)
 
 
-def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+def linear_bf16_f32out(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False) -> torch.Tensor:
     """out (float32) = x @ w^T from bfloat16 operands, accumulated in float32."""
     if gemm_tc_takes(x, w):
-        return gemm_tc(x, w, out)
+        return gemm_tc(x, w, out, static_weights=static_weights)
     return gemm_simt(x, w, out)

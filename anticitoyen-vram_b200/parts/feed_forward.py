@@ -41,7 +41,7 @@ class SwiGLU(FeedForward):
     def forward(self, h, ctx):
         if self.fused and h.shape[0] and ops.gemm_tc_takes(h, self.gate_up.weight):
             act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)
-            ops.linear_bf16_swiglu(h, self.gate_up.weight, act)
+            ops.linear_bf16_swiglu(h, self.gate_up.weight, act, static_weights=True)
             return self.down(act)
         if self.fused:      # an input the tensor-core kernel does not take: undo the interleaving for this call
             gu = self.gate_up(h).view(h.shape[0], self.intermediate_size, 2).transpose(1, 2).reshape(h.shape[0], -1)

@@ -35,5 +35,5 @@ class Linear:
         if x.dtype == torch.float32:
             return ops.gemm_simt(x, w, out)
         if out_dtype == torch.float32:
-            return ops.linear_bf16_f32out(x, w, out)
-        return ops.linear_bf16(x, w, out)
+            return ops.linear_bf16_f32out(x, w, out, static_weights=True)
+        return ops.linear_bf16(x, w, out, static_weights=True)
