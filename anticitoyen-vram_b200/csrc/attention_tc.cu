@@ -1,15 +1,24 @@
 // Paged causal flash attention for portions of prompts on the fifth-generation tensor cores.
 //
-// One CTA per (tile of 128 query tokens of one request, query head).  For each tile of 128 keys:
-//   S = Q K^T      tcgen05.mma, Q and K in shared memory (K-major, 128-byte swizzle), S in tensor memory
-//   softmax        four warps, one query row per thread: S row from tensor memory (tcgen05.ld), mask by
-//                  absolute position, running maximum and sum in float, P written to shared memory as the
-//                  bfloat16 A operand of the next product; when a row's maximum moved, the row of O in
-//                  tensor memory is rescaled (tcgen05.ld / tcgen05.st)
-//   O += P V       tcgen05.mma, V in shared memory as it lies in the pages ([keys][D], the MN-major operand)
-// Keys and values come straight from the cache pages by TMA, one box per page (page = box rows), two
+// One CTA per (tile of 128 query tokens of one request, pair of query heads that share a key/value
+// head).  The two heads see the same keys, the same values and the same mask, so a tile of keys is
+// loaded once for both, and while the softmax of one head runs, the tensor core works for the other:
+//   S_h = Q_h K^T   tcgen05.mma, Q and K in shared memory (K-major, 128-byte swizzle), S_h in tensor memory
+//   softmax         four warps per head, one query row per thread: the row of S_h from tensor memory
+//                   (tcgen05.ld), mask by absolute position, running maximum and sum in float; P_h goes
+//                   back into the columns of S_h as packed bfloat16 (tcgen05.st), the A operand of the next
+//                   product; the row of O_h in tensor memory is rescaled only when its maximum has grown
+//                   by more than 2^8 since the last rescale (the sum and O carry the same stale maximum,
+//                   so the quotient at the end is unchanged)
+//   O_h += P_h V    tcgen05.mma with A from tensor memory, V in shared memory as it lies in the pages
+//                   ([keys][D], the MN-major operand)
+// The MMA warp issues, per tile t of keys: P0.V, then S0 of tile t+1, P1.V, S1 of tile t+1; products of
+// one thread run in the order of issue, so the next S_h overwrites P_h only after P_h.V has read it, and
+// a finished S_h(t+1) tells the softmax warps that O_h is at rest.
+// Keys and values come straight from the cache pages by TMA, one box per page and 64 columns, two
 // tiles in flight; Q comes by TMA from the step's projection buffer.  Warp 0 issues the loads, warp 1
-// the MMAs, warps 2..5 are the softmax and the epilogue.  The mask follows absolute positions
+// the MMAs, warps 2..5 are head 0's softmax and epilogue, warps 6..9 head 1's.  A group with an odd
+// number of query heads leaves the second half of its last CTA idle.  The mask follows absolute positions
 // (key j is seen by the query at position p iff j <= p, and j > p - window when a window is set), so a
 // portion may start anywhere in its prompt (acvram/engine/layers.py:1020-1041); the reference runs this
 // case through SDPA on a gathered dense copy (acvram/engine/attention.py:519-584).
@@ -17,11 +26,12 @@
 #include "tc_ptx.cuh"
 #include "tensor_map.h"
 
-#define AT_THREADS 192
+#define AT_THREADS 320
 #define AT_BM 128
 #define AT_BN 128
 #define AT_LOG2E 1.4426950408889634f
 #define AT_ATOM (128 * 128)          // bytes of one swizzle atom column: 128 rows of 128 bytes
+#define AT_LAZY 8.0f                 // a row's maximum may lag by this much (log2 units) before O is rescaled
 
 struct AttnTcParams {
     bf16* out;
@@ -42,28 +52,25 @@ __global__ void __launch_bounds__(AT_THREADS, 1)
 attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
     constexpr int DA = D / 64;                         // 64-element column atoms of a head
-    constexpr int Q_BYTES = DA * AT_ATOM, P_BYTES = 2 * AT_ATOM, KV_BYTES = DA * AT_ATOM;
-    constexpr int TMEM_COLS = 256;                     // S: columns [0,128), O: columns [128, 128 + D)
+    constexpr int Q_BYTES = DA * AT_ATOM, KV_BYTES = DA * AT_ATOM;
+    constexpr int TMEM_COLS = 512;                     // S_h: columns [128h, 128h + 128), O_h: [256 + 128h, 256 + 128h + D)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = smem_raw + ((1024u - (gt_smem(smem_raw) & 1023u)) & 1023u);
-    const uint32_t q_s = gt_smem(base), p_s = q_s + Q_BYTES, kv_s = p_s + P_BYTES;   // kv_s: [2 stages][K, V]
-    unsigned char* p_ptr = base + Q_BYTES;
-    uint64_t* bars = (uint64_t*)(base + Q_BYTES + P_BYTES + 4 * KV_BYTES);
+    const uint32_t q_s = gt_smem(base), kv_s = q_s + 2 * Q_BYTES;   // q_s: [2 heads]; kv_s: [2 stages][K, V]
+    uint64_t* bars = (uint64_t*)(base + 2 * Q_BYTES + 4 * KV_BYTES);
     const uint32_t bar0 = gt_smem(bars);
-    const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_free = bar0 + 24, s_full = bar0 + 40, p_full = bar0 + 48,
-                   o_full = bar0 + 56;
+    const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_free = bar0 + 24, s_full = bar0 + 40, p_full = bar0 + 56,
+                   o_full = bar0 + 72;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ACV_TL(TL_ATTN_TC, 64);
-    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         abort_s = 0;
         mbar_init(q_full, 1);
         for (int s = 0; s < 2; ++s) { mbar_init(kv_full + 8 * s, 1); mbar_init(kv_free + 8 * s, 1); }
-        mbar_init(s_full, 1);
-        mbar_init(p_full, 4);
+        for (int h = 0; h < 2; ++h) { mbar_init(s_full + 8 * h, 1); mbar_init(p_full + 8 * h, 4); }
         mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -74,17 +81,26 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // The key/value ring starts at zero: a page that is skipped (every key of it masked) leaves its rows
     // as they were, and a masked key's value is multiplied by a zero probability, so it must be finite.
     for (int i = threadIdx.x; i < 4 * KV_BYTES / 16; i += AT_THREADS)
-        reinterpret_cast<uint4*>(base + Q_BYTES + P_BYTES)[i] = make_uint4(0, 0, 0, 0);
+        reinterpret_cast<uint4*>(base + 2 * Q_BYTES)[i] = make_uint4(0, 0, 0, 0);
     fence_proxy_async_smem();
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s = tmem_base_s, tmem_o = tmem_base_s + 128;
+    const uint32_t tmem = tmem_base_s;
+    // only now may the next kernel's CTAs come: one that took tensor memory before this CTA had its own
+    // would wait for this grid to end while this CTA waits for its columns
+    pdl_launch_dependents();
     pdl_wait();
 
     // ---- the tile's geometry (the same in every role)
-    const int seq = p.tile_seq[blockIdx.x], q0 = p.tile_q0[blockIdx.x];
-    const int h = blockIdx.y, kvh = h / (p.NH / p.NKV);
+    // blocks are numbered tile-major: the tile list begins with the longest tiles, and the hardware hands
+    // out blocks in the order of their numbers, so every head pair of a long tile starts before a short one
+    const int n_rep = p.NH / p.NKV, pairs = (n_rep + 1) >> 1;
+    const int tile = blockIdx.x / (p.NKV * pairs), hp = blockIdx.x - tile * (p.NKV * pairs);
+    const int seq = p.tile_seq[tile], q0 = p.tile_q0[tile];
+    const int kvh = hp / pairs, pair = hp - kvh * pairs;
+    const int h0 = kvh * n_rep + 2 * pair;                  // the CTA's first head; the second is h0 + 1
+    const int n_heads = 2 * pair + 1 < n_rep ? 2 : 1;
     const int tok0 = p.cu_q[seq] + q0;
     const int q_len = p.cu_q[seq + 1] - p.cu_q[seq];
     const int rows = min(AT_BM, q_len - q0);
@@ -98,9 +114,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_expect_tx(q_full, Q_BYTES);
+            mbar_expect_tx(q_full, n_heads * Q_BYTES);
+            for (int h = 0; h < n_heads; ++h)
 #pragma unroll
-            for (int a = 0; a < DA; ++a) tma_load_2d(q_s + a * AT_ATOM, &map_q, q_full, h * D + a * 64, tok0);
+                for (int a = 0; a < DA; ++a)
+                    tma_load_2d(q_s + h * Q_BYTES + a * AT_ATOM, &map_q, q_full, (h0 + h) * D + a * 64, tok0);
             const int ps = p.page_size, pages_per_tile = AT_BN >> p.page_shift;
             for (int t = 0; t < n_tiles && !abort_s; ++t) {
                 const int s = t & 1;
@@ -134,109 +152,160 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
             const uint32_t idesc_s = umma_idesc(AT_BN, 128, 0), idesc_o = umma_idesc(D, 128, 1);
-            bool ok = mbar_wait(q_full, 0, &abort_s);
-            if (!ok) { abort_s = 1; atomicExch(p.status, 12); }
-            for (int t = 0; t < n_tiles && ok && !abort_s; ++t) {
-                const int s = t & 1;
-                if (!mbar_wait(kv_full + 8 * s, (t >> 1) & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 13); break; }
-                tc_fence_after();
-                const uint32_t k_addr = kv_s + s * 2 * KV_BYTES, v_addr = k_addr + KV_BYTES;
-                // S = Q K^T over the head dimension
+            // S_h = Q_h K^T over the head dimension, for the tile of keys in stage s
+            auto issue_s = [&](int h, int s) {
+                const uint32_t k_addr = kv_s + s * 2 * KV_BYTES, q_addr = q_s + h * Q_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = (kk >> 2) * AT_ATOM + (kk & 3) * 32;
-                    tc_mma_bf16(tmem_s, umma_desc(q_s + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
+                    tc_mma_bf16(tmem + h * 128, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
                 }
-                tc_commit(s_full);
-                // O += P V over the tile's keys, once the softmax has written P
-                if (!mbar_wait(p_full, t & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 14); break; }
+                tc_commit(s_full + 8 * h);
+            };
+            bool ok = mbar_wait(q_full, 0, &abort_s);
+            if (!ok) { abort_s = 1; atomicExch(p.status, 12); }
+            if (ok && !mbar_wait(kv_full, 0, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 13); }
+            if (ok) {
                 tc_fence_after();
+                for (int h = 0; h < n_heads; ++h) issue_s(h, 0);
+            }
+            for (int t = 0; t < n_tiles && ok && !abort_s; ++t) {
+                const int s = t & 1;
+                const uint32_t v_addr = kv_s + s * 2 * KV_BYTES + KV_BYTES;
+                for (int h = 0; h < n_heads && ok; ++h) {
+                    // O_h += P_h V over the tile's keys, once head h's softmax has written P_h
+                    if (!mbar_wait(p_full + 8 * h, t & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 14); break; }
+                    tc_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < AT_BN / 16; ++kk) {
-                    const uint32_t a_off = (kk >> 2) * AT_ATOM + (kk & 3) * 32;
-                    tc_mma_bf16(tmem_o, umma_desc(p_s + a_off), umma_desc_mn(v_addr + kk * 2048, AT_ATOM), idesc_o,
-                                (t > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < AT_BN / 16; ++kk)
+                        tc_mma_bf16_ts(tmem + 256 + h * 128, tmem + h * 128 + kk * 8, umma_desc_mn(v_addr + kk * 2048, AT_ATOM),
+                                       idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                    if (h == n_heads - 1) tc_commit(kv_free + 8 * s);      // this stage's keys and values are read
+                    if (t + 1 < n_tiles) {
+                        if (h == 0) {
+                            if (!mbar_wait(kv_full + 8 * (s ^ 1), ((t + 1) >> 1) & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 13); break; }
+                            tc_fence_after();
+                        }
+                        issue_s(h, s ^ 1);
+                    }
                 }
-                tc_commit(kv_free + 8 * s);      // this stage's keys and values are read
             }
             tc_commit(o_full);
         }
-    } else {
-        // ------------------------------------------------------------------ softmax and epilogue (warps 2..5)
-        const int wq = warp & 3;
+    } else if (((warp - 2) >> 2) < n_heads) {
+        // ------------------------------------------------------------------ softmax and epilogue of one head
+        const int hs = (warp - 2) >> 2;                         // head slot 0 or 1
+        const int wq = warp & 3;                                // the tensor-memory lanes this warp may touch
         const int r = wq * 32 + lane;                           // this thread's query row = tensor-memory lane
         const int pos = pos0 + r;
         const uint32_t lane_base = (uint32_t)(wq * 32) << 16;
+        const uint32_t tmem_s = tmem + hs * 128 + lane_base, tmem_o = tmem + 256 + hs * 128 + lane_base;
         const float scale_log2 = p.scale * AT_LOG2E;
         float m_run = -INFINITY, l_run = 0.f;
         bool failed = false;
+#ifdef ACV_TIMELINE
+        unsigned long long tl_acc[7] = {0, 0, 0, 0, 0, 0, 0}, tl_t = acv_tl_now();
+#define TL_PHASE(i) do { const unsigned long long n_ = acv_tl_now(); tl_acc[i] += n_ - tl_t; tl_t = n_; } while (0)
+#else
+#define TL_PHASE(i)
+#endif
         for (int t = 0; t < n_tiles && !abort_s; ++t) {
-            if (!mbar_wait(s_full, t & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 15); failed = true; break; }
+            if (!mbar_wait(s_full + 8 * hs, t & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 15); failed = true; break; }
             tc_fence_after();
+            TL_PHASE(0);
             const int j0 = j_first + t * AT_BN;
-            float sv[AT_BN];
+            const bool need_mask = j0 + AT_BN - 1 > pos0 || (p.window > 0 && j0 <= pos0 + AT_BM - 1 - p.window);
+            // first pass: the row's maximum
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
             for (int c0 = 0; c0 < AT_BN; c0 += 32) {
                 uint32_t raw[32];
-                tc_ld32(tmem_s + lane_base + c0, raw);
+                tc_ld32(tmem_s + c0, raw);
+                if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) sv[c0 + c] = __uint_as_float(raw[c]);
-            }
-            const bool need_mask = j0 + AT_BN - 1 > pos0 || (p.window > 0 && j0 <= pos0 + AT_BM - 1 - p.window);
-            float mx = -INFINITY;
-            if (need_mask) {
-#pragma unroll
-                for (int c = 0; c < AT_BN; ++c) {
-                    const int j = j0 + c;
-                    const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
-                    if (!seen) sv[c] = -INFINITY;
+                    for (int c = 0; c < 32; ++c) {
+                        const int j = j0 + c0 + c;
+                        const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
+                        raw[c] = seen ? raw[c] : 0xff800000u;       // -inf
+                    }
                 }
-            }
 #pragma unroll
-            for (int c = 0; c < AT_BN; ++c) mx = fmaxf(mx, sv[c]);
-            const float m_new = fmaxf(m_run, mx * scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float alpha = exp2f(m_run - m_use);
-            m_run = m_new;
+                for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(raw[c]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            TL_PHASE(1);
+            // the maximum in use moves only when the true one has run ahead of it by more than AT_LAZY
+            const float m_true = fmaxf(m_run, mx * scale_log2);
+            float alpha = 1.f;
+            if (m_true > m_run + AT_LAZY) {         // also the first finite maximum of a row (-inf + 8 = -inf)
+                alpha = m_run == -INFINITY ? 0.f : tc_exp2(m_run - m_true);
+                m_run = m_true;
+            }
+            const float m_use = m_run == -INFINITY ? 0.f : m_run;
             // rows whose maximum moved rescale what O holds so far (tensor-memory access is warp-wide)
             if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t o[32];
-                    tc_ld32(tmem_o + lane_base + c0, o);
+                    tc_ld32(tmem_o + c0, o);
 #pragma unroll
                     for (int c = 0; c < 32; ++c) o[c] = __float_as_uint(__uint_as_float(o[c]) * alpha);
-                    tc_st32(tmem_o + lane_base + c0, o);
+                    tc_st32(tmem_o + c0, o);
                 }
             }
             l_run *= alpha;
-            // P as the bfloat16 K-major operand: row r, chunk c8 of 8 keys at atom (c8 / 8), swizzled by the row
+            TL_PHASE(2);
+            // second pass: P = 2^(s * scale - m) as packed bfloat16 into the first 64 columns of S (the
+            // columns it overwrites have been read: chunk c of P covers columns [16c, 16c + 16) of [0, 32c + 32))
 #pragma unroll
-            for (int c8 = 0; c8 < AT_BN / 8; ++c8) {
-                float e[8];
+            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
+                uint32_t raw[32];
+                tc_ld32(tmem_s + c0, raw);
+                TL_PHASE(5);
+                if (need_mask) {
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    e[i] = exp2f(fmaf(sv[c8 * 8 + i], scale_log2, -m_use));
-                    l_run += e[i];
+                    for (int c = 0; c < 32; ++c) {
+                        const int j = j0 + c0 + c;
+                        const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
+                        raw[c] = seen ? raw[c] : 0xff800000u;       // -inf
+                    }
                 }
-                uint4 pk;
-                pk.x = pack_bf16x2(e[0], e[1]); pk.y = pack_bf16x2(e[2], e[3]);
-                pk.z = pack_bf16x2(e[4], e[5]); pk.w = pack_bf16x2(e[6], e[7]);
-                *reinterpret_cast<uint4*>(p_ptr + (c8 >> 3) * AT_ATOM + r * 128 + (((c8 & 7) ^ (r & 7)) << 4)) = pk;
+                float e[32];
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    e[c] = tc_exp2(fmaf(__uint_as_float(raw[c]), scale_log2, -m_use));
+                    part[c & 3] += e[c];
+                }
+                l_run += (part[0] + part[1]) + (part[2] + part[3]);
+                uint32_t pk[16];
+#pragma unroll
+                for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(e[2 * c], e[2 * c + 1]);
+                TL_PHASE(3);
+                tc_st16_nowait(tmem_s + (c0 >> 1), pk);
+                TL_PHASE(6);
             }
-            fence_proxy_async_smem();
+            tc_wait_st();
+            TL_PHASE(6);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full);
+            if (lane == 0) mbar_arrive(p_full + 8 * hs);
+            TL_PHASE(4);
         }
+#ifdef ACV_TIMELINE
+        if (threadIdx.x == 64) {
+            for (int i = 0; i < 7; ++i) acv_tl_marks[i] = tl_acc[i];
+            acv_tl_marks[7] = (unsigned long long)n_tiles;
+        }
+#endif
         if (!failed && !abort_s && mbar_wait(o_full, 0, &abort_s)) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
-            bf16* dst = p.out + (size_t)(tok0 + r) * p.out_stride + (size_t)h * D;
+            bf16* dst = p.out + (size_t)(tok0 + r) * p.out_stride + (size_t)(h0 + hs) * D;
 #pragma unroll
             for (int c0 = 0; c0 < D; c0 += 32) {
                 uint32_t o[32];
-                tc_ld32(tmem_o + lane_base + c0, o);
+                tc_ld32(tmem_o + c0, o);
                 if (r < rows) {
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
@@ -266,14 +335,15 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 template <int D>
 static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p,
                           int n_tiles, cudaStream_t stream) {
-    constexpr int SMEM = (D / 64) * AT_ATOM /*Q*/ + 2 * AT_ATOM /*P*/ + 4 * (D / 64) * AT_ATOM /*K,V x2*/ + 1024 + 128;
+    constexpr int SMEM = 2 * (D / 64) * AT_ATOM /*Q of two heads*/ + 4 * (D / 64) * AT_ATOM /*K,V x2*/ + 1024 + 128;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    acv_launch(PDL_MISC, attn_tc_kernel<D>, dim3(n_tiles, p.NH), AT_THREADS, SMEM, stream, mq, mk, mv, p);
+    const int n_rep = p.NH / p.NKV;
+    acv_launch(PDL_MISC, attn_tc_kernel<D>, dim3((unsigned)(n_tiles * (p.NKV * ((n_rep + 1) / 2)))), AT_THREADS, SMEM, stream, mq, mk, mv, p);
     return acv_launch_status();
 }
 
@@ -286,6 +356,7 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
                              int page_size, int num_pages, float scale, int window, int* status, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535 || (D != 64 && D != 128)) return ACV_ERR_SIZE;
+    if ((long long)n_tiles * NH > 0x7fffffffLL) return ACV_ERR_SIZE;
     int page_shift = -1;
     for (int b = 3; b <= 7; ++b)
         if ((1 << b) == page_size) page_shift = b;

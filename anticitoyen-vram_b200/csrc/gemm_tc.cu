@@ -152,7 +152,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ACV_TL(TL_GEMM, 64);
-    pdl_launch_dependents();
     if (threadIdx.x == 0) {
         abort_s = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
@@ -167,6 +166,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    // only now may the next kernel's CTAs come: one that took tensor memory before this CTA had its own
+    // could wait for this grid to end while this CTA waits for its columns
+    pdl_launch_dependents();
 
     const int n_items = p.tiles_a * p.tiles_b * p.splits;
     const uint32_t tiles_addr = gt_smem(tiles);

@@ -41,8 +41,8 @@ def gemm_case(M: int, N: int, K: int, reps: int) -> None:
           f"{N * K * 2 / us / 1e3:.0f} GB/s of weights, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
 
 
-def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool = False) -> None:
-    NH, NKV, D, page = 32, 8, 128, 16
+def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool = False, page: int = 16) -> None:
+    NH, NKV, D = 32, 8, 128
     pages_per = (context + page - 1) // page
     n_pages = batch * pages_per
     sets = 3       # rotate over three pools so that a launch finds nothing of its pages in L2
@@ -61,7 +61,7 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
                                             D ** -0.5, 0, splits, context)
         us = _time(fn, reps)
         gb = batch * context * NKV * D * 2 * 2 / 1e9
-        print(f"attention_decode batch={batch} context={context} splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of pages")
+        print(f"attention_decode batch={batch} context={context} page={page} splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of pages")
     else:
         tiles = [(b, s) for b in range(batch) for s in range(0, q_len, QUERY_TILE)][::-1]
         tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
@@ -71,7 +71,7 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
                               D, D ** -0.5, 0)
         us = _time(fn, reps)
         flops = batch * 4.0 * NH * D * (q_len * (context - q_len) + q_len * (q_len + 1) / 2)
-        print(f"{kernel.__name__} batch={batch} q_len={q_len} context={context}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+        print(f"{kernel.__name__} batch={batch} q_len={q_len} context={context} page={page}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
 
 
 CASES = {

@@ -234,7 +234,7 @@ class _Ctx:
     pass
 
 
-def _tc_case(ops, NH, NKV, D, page, lens, q_lens, window, seed, n_splits=None, spike=None):
+def _tc_case(ops, NH, NKV, D, page, lens, q_lens, window, seed, n_splits=None, spike=None, k_growth=0.0):
     """A mixed batch through ops.attention (decode kernel for one-token requests, tile kernel for portions)."""
     dtype = torch.bfloat16
     B = len(lens)
@@ -244,7 +244,7 @@ def _tc_case(ops, NH, NKV, D, page, lens, q_lens, window, seed, n_splits=None, s
     for b, l in enumerate(lens):
         for j in range(l):
             pg = int(table[b, j // page])
-            kp[pg, :, j % page] = torch.randn(NKV, D, device="cuda", generator=g).to(dtype)
+            kp[pg, :, j % page] = (torch.randn(NKV, D, device="cuda", generator=g) * (1.0 + k_growth * j)).to(dtype)
             vp[pg, :, j % page] = torch.randn(NKV, D, device="cuda", generator=g).to(dtype)
     ctx = _Ctx()
     ctx.positions = torch.cat([torch.arange(l - q, l) for l, q in zip(lens, q_lens)]).to(torch.int32).cuda()
@@ -389,3 +389,11 @@ def test_gemm_tc_fused_swiglu(ops, plan, M, I, K):
     assert torch.equal(got, want)
     torch.testing.assert_close(got, ref.swiglu((x.float() @ torch.cat([wg, wu]).float().T).bfloat16(),
                                                torch.zeros(M, I, device="cuda", dtype=torch.bfloat16)), **tol(torch.bfloat16))
+
+
+def test_tensor_core_attention_growing_scores(ops):
+    """Keys whose scores grow along a long prompt: the running maximum moves in every tile of keys, far enough
+    that the rows of O are rescaled again and again (and by different amounts in the rows of one warp)."""
+    for q_lens, lens in (([700, 130], [700, 400]), ([257, 2], [900, 514])):
+        o1, o2 = _tc_case(ops, 6, 2, 128, 16, lens=lens, q_lens=q_lens, window=0, seed=91, k_growth=1.0 / 20.0)
+        torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
