@@ -27,7 +27,7 @@ def _engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     p.add_argument("--max-model-len", type=int, default=8192)
     p.add_argument("--max-batch", type=int, default=16)
-    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--page-size", type=int, default=64)
     p.add_argument("--num-pages", type=int, default=None, help="pages of the cache pool (default: from free memory)")
     p.add_argument("--token-budget", type=int, default=2048, help="most tokens that one step runs")
     p.add_argument("--device", default="cuda:0")

@@ -64,7 +64,7 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 
 class Engine:
     def __init__(self, model, dtype="bfloat16", *, max_batch_size: int = 16, max_model_len: int = 8192,
-                 page_size: int = 16, num_pages: int | None = None, token_budget: int = 2048,
+                 page_size: int = 64, num_pages: int | None = None, token_budget: int = 2048,
                  random_weights: bool = False, seed: int = 0, device: str = "cuda:0",
                  enable_cuda_graphs: bool = True, tokenizer=None) -> None:
         """``model``: a folder with config.json and model.safetensors, or (with

@@ -122,6 +122,7 @@ def main(argv=None) -> int:
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--no-cuda-graphs", action="store_true")
     ap.add_argument("--prefill", type=int, default=0, help="record one prompt step of this many tokens instead of a decode step")
+    ap.add_argument("--page", type=int, default=64)
     ap.add_argument("--out", default="")
     ap.add_argument("--dump", default="", help="also save the raw records (numpy .npy)")
     args = ap.parse_args(argv)
@@ -135,10 +136,10 @@ def main(argv=None) -> int:
                       num_attention_heads=32, num_key_value_heads=8, head_dim=128, max_position_embeddings=40960,
                       rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False)
     model = build_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
-    pages = args.batch * (args.context // 16 + 8) + 8
+    pages = args.batch * (args.context // args.page + 8) + 8
     if args.prefill:
-        pages = max(pages, 3 * (args.prefill // 16 + 2))
-    engine = Engine(model, "bfloat16", max_batch_size=args.batch, max_model_len=8192, page_size=16, num_pages=pages,
+        pages = max(pages, 3 * (args.prefill // args.page + 2))
+    engine = Engine(model, "bfloat16", max_batch_size=args.batch, max_model_len=8192, page_size=args.page, num_pages=pages,
                     token_budget=4096, enable_cuda_graphs=not args.no_cuda_graphs)
     runner = engine.runner
     if args.prefill:
