@@ -154,11 +154,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             const uint32_t idesc_s = umma_idesc(AT_BN, 128, 0), idesc_o = umma_idesc(D, 128, 1);
             // S_h = Q_h K^T over the head dimension, for the tile of keys in stage s
             auto issue_s = [&](int h, int s) {
-                const uint32_t k_addr = kv_s + s * 2 * KV_BYTES, q_addr = q_s + h * Q_BYTES;
+                const uint32_t k_lo = umma_desc_lo(kv_s + s * 2 * KV_BYTES), q_lo = umma_desc_lo(q_s + h * Q_BYTES);
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk >> 2) * AT_ATOM + (kk & 3) * 32;
-                    tc_mma_bf16(tmem + h * 128, umma_desc(q_addr + off), umma_desc(k_addr + off), idesc_s, kk > 0 ? 1u : 0u);
+                    const uint32_t off = ((kk >> 2) * AT_ATOM + (kk & 3) * 32) >> 4;
+                    tc_mma_bf16_h(tmem + h * 128, q_lo + off, k_lo + off, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 tc_commit(s_full + 8 * h);
             };
@@ -176,10 +176,11 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                     // O_h += P_h V over the tile's keys, once head h's softmax has written P_h
                     if (!mbar_wait(p_full + 8 * h, t & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 14); break; }
                     tc_fence_after();
+                    const uint32_t v_lo = umma_desc_lo(v_addr, AT_ATOM);
 #pragma unroll
                     for (int kk = 0; kk < AT_BN / 16; ++kk)
-                        tc_mma_bf16_ts(tmem + 256 + h * 128, tmem + h * 128 + kk * 8, umma_desc_mn(v_addr + kk * 2048, AT_ATOM),
-                                       idesc_o, (t > 0 || kk > 0) ? 1u : 0u);
+                        tc_mma_bf16_ts_h(tmem + 256 + h * 128, tmem + h * 128 + kk * 8, v_lo + kk * (2048 >> 4), idesc_o,
+                                         (t > 0 || kk > 0) ? 1u : 0u);
                     if (h == n_heads - 1) tc_commit(kv_free + 8 * s);      // this stage's keys and values are read
                     if (t + 1 < n_tiles) {
                         if (h == 0) {
