@@ -33,6 +33,13 @@ template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __f
 // value rounded to T and read back as float: the "rounded to the model dtype" step
 template <typename T> __device__ __forceinline__ float round_to(float v) { return to_f32(from_f32<T>(v)); }
 
+// SiLU in float.  The 32-bit path divides and exponentiates exactly; the bfloat16 path, whose result is
+// rounded to 8 bits of mantissa at once, uses the hardware's approximations (a few units in the last
+// place of a float) - the same function in the SwiGLU kernel and in the matrix product's epilogue.
+template <typename T> __device__ __forceinline__ float silu_f32(float g);
+template <> __device__ __forceinline__ float silu_f32<float>(float g) { return g / (1.f + expf(-g)); }
+template <> __device__ __forceinline__ float silu_f32<bf16>(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -187,7 +187,7 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
         const int i = (int)(idx - t * I);
         const float g = to_f32(gu[t * 2 * I + i]);
         const float u = to_f32(gu[t * 2 * I + I + i]);
-        const float s = round_to<T>(g / (1.f + expf(-g)));
+        const float s = round_to<T>(silu_f32<T>(g));
         out[idx] = from_f32<T>(s * u);
     }
 }
@@ -211,7 +211,7 @@ __global__ void swiglu_vec_kernel(const T* __restrict__ gu, T* __restrict__ out,
 #pragma unroll
         for (int e = 0; e < E; ++e) {
             const float gv = to_f32(g[e]);
-            res[e] = from_f32<T>(round_to<T>(gv / (1.f + expf(-gv))) * to_f32(u[e]));
+            res[e] = from_f32<T>(round_to<T>(silu_f32<T>(gv)) * to_f32(u[e]));
         }
         *reinterpret_cast<uint4*>(out + t * I + (size_t)c * E) = *reinterpret_cast<const uint4*>(res);
     }

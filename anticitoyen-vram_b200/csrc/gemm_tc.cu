@@ -44,6 +44,7 @@ struct GemmParams {
     int early_w;            // 1: the weights were written long before this launch: their first tiles are loaded before the predecessor ends
     int cluster;            // 1: the splits of a tile are the CTAs of one cluster and are summed through its shared memory
     int stages;             // pipeline depth (2..8); shared memory = stages * (128 + BN) * 128 bytes
+    int staged;             // 1: swapped roles, one work item per CTA, C aligned: the tile goes out through shared memory in 16-byte rows
     void* C;
     float* workspace;       // [tiles][splits][BN][128] floats when splits > 1
     int* counters;          // [tiles], zero before and after
@@ -55,7 +56,7 @@ struct GemmParams {
 __device__ __forceinline__ bf16 swiglu_pair(float gate, float up) {
     const float g = __bfloat162float(__float2bfloat16_rn(gate));
     const float u = __bfloat162float(__float2bfloat16_rn(up));
-    const float s = __bfloat162float(__float2bfloat16_rn(g / (1.f + expf(-g))));
+    const float s = __bfloat162float(__float2bfloat16_rn(silu_f32<bf16>(g)));
     return __float2bfloat16_rn(s * u);
 }
 
@@ -117,6 +118,48 @@ __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int c
                 for (int c = 0; c < 16; ++c)
                     if (col0 + c < p.N) dst[c] = __float2bfloat16_rn(v[c]);
             }
+        }
+    }
+}
+
+// Swapped roles put features on tensor-memory lanes and tokens on columns, the transpose of C's rows.
+// With one work item per CTA the pipeline's shared memory is free once the accumulator is complete:
+// the tile is put there as C has it ([token][feature of the tile], in the output type) and leaves in
+// 16-byte pieces of whole rows, instead of one 2-byte store per token and thread.
+// gt_stage16: 16 tokens (col0 ..) of the feature this lane holds (f = 0..127 within the tile).
+__device__ __forceinline__ void gt_stage16(const GemmParams& p, unsigned char* stage, int f, int col0, const float (&v)[16], int lane) {
+    if (p.act) {            // an even lane holds a gate, the next lane its up: 64 output features per tile
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            const float up = __shfl_down_sync(0xffffffffu, v[c], 1);
+            if (!(lane & 1)) reinterpret_cast<bf16*>(stage)[(col0 + c) * 64 + (f >> 1)] = swiglu_pair(v[c], up);
+        }
+    } else if (p.out_f32) {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) reinterpret_cast<float*>(stage)[(col0 + c) * 128 + f] = v[c];
+    } else {
+#pragma unroll
+        for (int c = 0; c < 16; ++c) reinterpret_cast<bf16*>(stage)[(col0 + c) * 128 + f] = __float2bfloat16_rn(v[c]);
+    }
+}
+// gt_flush: the staged tile (tokens tb*BN .., features ta*128 ..) to C, by the 128 epilogue threads
+__device__ __forceinline__ void gt_flush(const GemmParams& p, const unsigned char* stage, int ta, int tb, int bn, int et) {
+    const int esz = p.out_f32 ? 4 : 2;
+    const int feats = p.act ? 64 : 128;                    // output features of the tile
+    const int n_out = p.act ? p.N >> 1 : p.N;
+    const int f0 = ta * feats;
+    const int row_bytes = feats * esz, chunks = row_bytes >> 4, per_chunk = 16 / esz;
+    const int rows = min(bn, p.M - tb * bn);
+    for (int q = et; q < rows * chunks; q += 128) {
+        const int r = q / chunks, ch = q - r * chunks;
+        const int f = f0 + ch * per_chunk;
+        if (f >= n_out) continue;
+        unsigned char* dst = (unsigned char*)p.C + ((size_t)(tb * bn + r) * p.ldc + f) * esz;
+        const unsigned char* src = stage + r * row_bytes + (ch << 4);
+        if (f + per_chunk <= n_out) {
+            *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(src);
+        } else {
+            for (int b = 0; b < (n_out - f) * esz; ++b) dst[b] = src[b];
         }
     }
 }
@@ -258,18 +301,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int row_a = ta * GT_BM + wq * 32 + lane;          // row of the A operand this thread holds
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(wq * 32) << 16);
             if (p.splits == 1) {
+                const int rows_b = min(BN, p.RB - tb * BN);
 #pragma unroll 1
                 for (int c0 = 0; c0 < BN; c0 += 16) {
+                    if (p.staged && c0 >= rows_b) break;
                     uint32_t r[16];
                     tc_ld16(taddr + c0, r);
                     float v[16];
 #pragma unroll
                     for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
-                    gt_store16(p, row_a, tb * BN + c0, v, lane);
+                    if (p.staged) gt_stage16(p, tiles, wq * 32 + lane, c0, v, lane);
+                    else gt_store16(p, row_a, tb * BN + c0, v, lane);
                 }
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+                if (p.staged) {         // the only item of this CTA: its loads have all been consumed
+                    asm volatile("bar.sync 1, 128;" ::: "memory");
+                    gt_flush(p, tiles, ta, tb, BN, et);
+                }
                 continue;
             }
             if (cluster_split) {
@@ -352,7 +402,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 for (int sp = 1; sp < p.splits; ++sp)           // split order: the sum does not depend on timing
 #pragma unroll
                     for (int c = 0; c < 16; ++c) sum[c] += part[((sp - 1) * BN + c0 + c) * GT_BM];
-                gt_store16(p, row_a, tb * BN + c0, sum, lane);
+                if (p.staged) gt_stage16(p, tiles, wq * 32 + lane, c0, sum, lane);
+                else gt_store16(p, row_a, tb * BN + c0, sum, lane);
+            }
+            if (p.staged) {
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                gt_flush(p, tiles, ta, tb, BN, threadIdx.x - 64);
             }
         }
     }
@@ -392,6 +447,11 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     const long long items = (long long)p.tiles_a * p.tiles_b * p.splits;
     const long long cap = (long long)sm_count * per_sm;
     const int grid = (int)(parts ? items : (items < cap ? items : cap));
+    // one item per CTA and rows of C that 16-byte stores can take: the tile leaves through shared memory
+    // (the work-space path of split K keeps its direct stores)
+    const int esz = p.out_f32 ? 4 : 2;
+    p.staged = p.swap && grid == items && (parts || p.splits == 1) && !((uintptr_t)p.C & 15) && !((p.ldc * esz) & 15) &&
+               stages * S::STAGE_BYTES >= BN * 128 * esz;
     acv_launch_cluster(PDL_GEMM, dim3(parts ? p.splits : 1, 1, 1), gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
     return acv_launch_status();
 }

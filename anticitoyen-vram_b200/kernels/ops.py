@@ -355,10 +355,15 @@ def _decode_scratch(device, floats: int, ml_floats: int, counters: int):
 
 def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
     """How many splits of the context: enough CTAs to cover the SMs not quite twice (measured best on a
-    B200: a split costs a fixed few microseconds of merge), and no split shorter than 256 keys."""
+    B200: a split costs a fixed few microseconds of merge), and no split shorter than 256 keys.  Up to 8
+    splits merge inside a cluster, which is so much cheaper than the merge through scratch memory that
+    more than 8 pay only when a split would otherwise hold more than 1024 keys."""
     pairs = max(1, n_dec * num_kv_heads)
     want = max(1, round(256 / pairs))
-    return max(1, min(want, -(-max_kv // 256)))
+    splits = max(1, min(want, -(-max_kv // 256)))
+    if splits > 8 and max_kv <= 8 * 1024:
+        splits = 8
+    return splits
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,

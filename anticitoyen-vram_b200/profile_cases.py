@@ -41,7 +41,7 @@ def gemm_case(M: int, N: int, K: int, reps: int) -> None:
           f"{N * K * 2 / us / 1e3:.0f} GB/s of weights, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
 
 
-def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool = False, page: int = 16) -> None:
+def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool = False, page: int = 64) -> None:
     NH, NKV, D = 32, 8, 128
     pages_per = (context + page - 1) // page
     n_pages = batch * pages_per
