@@ -125,9 +125,36 @@ argmax_split_kernel(const float* __restrict__ logits, int ld, int V, int* __rest
     const float* r = logits + (size_t)row * ld;
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
-        const float v = r[i];
-        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    if ((((uintptr_t)r) & 15) == 0 && (lo & 3) == 0) {
+        // 16-byte loads, four in flight per thread before the first comparison (the slice is short: what
+        // counts is that its loads are all on their way at once)
+        const int n4 = (hi - lo) >> 2;
+        const float4* r4 = reinterpret_cast<const float4*>(r + lo);
+        for (int c0 = threadIdx.x; c0 < n4; c0 += 4 * blockDim.x) {
+            float4 v[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int c = c0 + k * blockDim.x;
+                v[k] = c < n4 ? r4[c] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+            }
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const int i = lo + 4 * (c0 + k * blockDim.x);
+                if (v[k].x > best) { best = v[k].x; bi = i; }
+                if (v[k].y > best) { best = v[k].y; bi = i + 1; }
+                if (v[k].z > best) { best = v[k].z; bi = i + 2; }
+                if (v[k].w > best) { best = v[k].w; bi = i + 3; }
+            }
+        }
+        for (int i = lo + (n4 << 2) + threadIdx.x; i < hi; i += blockDim.x) {
+            const float v = r[i];
+            if (v > best) { best = v; bi = i; }
+        }
+    } else {
+        for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) {
+            const float v = r[i];
+            if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+        }
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
