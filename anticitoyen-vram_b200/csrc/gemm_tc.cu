@@ -175,8 +175,12 @@ struct GemmShape {
     }
 };
 
+// Registers are handed out to a CTA for its warps rounded up to four: 192 threads count as 8 warps, and three
+// such CTAs share an SM (what the narrow decode products with short pipelines want) only up to 80 registers
+// a thread (measured: at 106 registers two came to an SM and the gate/up product of a decode step ran in
+// two waves).  The narrow tile is held to that; the wider ones never come three to an SM.
 template <int BN>
-__global__ void __launch_bounds__(GT_THREADS, 1)
+__global__ void __launch_bounds__(GT_THREADS, 1) __maxnreg__(BN <= 16 ? 80 : 232)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
     using S = GemmShape<BN>;
     extern __shared__ unsigned char smem_raw[];
