@@ -45,6 +45,22 @@ struct GemmParams {
     int cluster;            // 1: the splits of a tile are the CTAs of one cluster and are summed through its shared memory
     int stages;             // pipeline depth (2..8); shared memory = stages * (128 + BN) * 128 bytes
     int staged;             // 1: swapped roles, one work item per CTA, C aligned: the tile goes out through shared memory in 16-byte rows
+    // stacked q,k,v projection (staged tiles, up to 32 tokens): per-head RMS norm of q and k, rotation, and the
+    // append of k and v to their pages, made on the tile as it leaves; only the q columns of C are written
+    int qkv;
+    int q_heads, kv_heads, head_dim;            // head_dim 64 or 128
+    const float* q_w;
+    const float* k_w;
+    float qk_eps;
+    const float* cos_sin;                       // [table_rows][head_dim]: cos then sin, or null
+    int table_rows;
+    const int* positions;
+    const int* seq_of_token;
+    const int* block_table;
+    int bt_stride;
+    bf16* k_pages;
+    bf16* v_pages;
+    int page_size, num_pages;
     void* C;
     float* workspace;       // [tiles][splits][BN][128] floats when splits > 1
     int* counters;          // [tiles], zero before and after
@@ -164,14 +180,99 @@ __device__ __forceinline__ void gt_flush(const GemmParams& p, const unsigned cha
     }
 }
 
+// gt_flush_qkv: the staged tile of a stacked q,k,v projection.  A row of the tile is 128 features of one token:
+// one head of 128 or two of 64.  The 16 threads of a row hold 8 features each; a head's threads add their squares
+// for the RMS norm, and the rotation's partner (i +- D/2) sits half a head's threads away.  The arithmetic is the
+// rotation kernel's (acvram/kernels/acvram_kernels.cu:4397-4430): norm, weight and rotation in float on the
+// bfloat16 values of the projection, one rounding at the end.  aux: positions [BN], pages [BN], cos/sin rows [BN][D].
+__device__ __forceinline__ void gt_flush_qkv(const GemmParams& p, const unsigned char* stage, const unsigned char* aux,
+                                             int ta, int tb, int bn, int et) {
+    const int D = p.head_dim, tph = D >> 3;                 // threads per head: 16 or 8
+    const int* pos_s = reinterpret_cast<const int*>(aux);
+    const int* pg_s = pos_s + bn;
+    const float* cs_s = reinterpret_cast<const float*>(pg_s + bn);
+    const int rows = min(bn, p.M - tb * bn);
+    const int ch = et & 15;
+    const int f = ta * 128 + ch * 8;                        // first of this thread's features in the stacked output
+    const int head = f / D, off = f - head * D;             // the same in every turn of the loop
+    const bool in_n = f < p.N;
+    const bool is_q = head < p.q_heads, is_k = !is_q && head < p.q_heads + p.kv_heads, is_v = !is_q && !is_k;
+    const float* w = is_q ? p.q_w : (is_k ? p.k_w : nullptr);
+    float wv[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wv[e] = (w && in_n) ? w[off + e] : 1.f;
+    const int i0 = off & ((D >> 1) - 1);                    // index of the first angle
+    const bool first_half = off < (D >> 1);
+    for (int q = et; q < ((bn * 16 + 127) & ~127); q += 128) {     // every thread takes every turn: the shuffles need all lanes
+        const int r = q >> 4;
+        const bool live = r < rows && in_n;
+        float a[8];
+        {
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (r < bn) raw = *reinterpret_cast<const uint4*>(stage + r * 256 + (ch << 4));
+            const bf16* e8 = reinterpret_cast<const bf16*>(&raw);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = __bfloat162float(e8[e]);
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss += a[e] * a[e];
+        ss += __shfl_xor_sync(0xffffffffu, ss, 1);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 2);
+        ss += __shfl_xor_sync(0xffffffffu, ss, 4);
+        if (tph == 16) ss += __shfl_xor_sync(0xffffffffu, ss, 8);
+        if (w) {
+            const float inv = rsqrtf(ss / (float)D + p.qk_eps);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) a[e] = a[e] * inv * wv[e];
+        }
+        const int pos = r < bn ? pos_s[r] : 0;
+        float o[8];
+        if (p.cos_sin) {
+            const bool rotate = !is_v && pos >= 0 && pos < p.table_rows;
+            const float* cs = cs_s + (size_t)(r < bn ? r : 0) * D;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float partner = __shfl_xor_sync(0xffffffffu, a[e], tph >> 1);
+                const float c = cs[i0 + e], sn = cs[(D >> 1) + i0 + e];
+                const float rot = first_half ? a[e] * c - partner * sn : a[e] * c + partner * sn;
+                o[e] = rotate ? rot : a[e];
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = a[e];
+        }
+        if (!live) continue;
+        bf16* dst = nullptr;
+        if (is_q) {
+            dst = (bf16*)p.C + (size_t)(tb * bn + r) * p.ldc + f;
+        } else {
+            const int pg = pg_s[r];
+            if (pg >= 0) {
+                const int kvh = is_k ? head - p.q_heads : head - p.q_heads - p.kv_heads;
+                dst = (is_k ? p.k_pages : p.v_pages) +
+                      (((size_t)pg * p.kv_heads + kvh) * p.page_size + (pos % p.page_size)) * D + off;
+            }
+        }
+        if (dst) {
+            uint4 out;
+            out.x = pack2(__float_as_uint(o[0]), __float_as_uint(o[1]));
+            out.y = pack2(__float_as_uint(o[2]), __float_as_uint(o[3]));
+            out.z = pack2(__float_as_uint(o[4]), __float_as_uint(o[5]));
+            out.w = pack2(__float_as_uint(o[6]), __float_as_uint(o[7]));
+            *reinterpret_cast<uint4*>(dst) = out;
+        }
+    }
+}
+
 template <int BN>
 struct GemmShape {
     static constexpr int STAGE_BYTES = (GT_BM + BN) * GT_BK * 2;
     static constexpr int MAX_STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
     static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;     // two accumulator buffers; a power of two
     static constexpr int PART_BYTES = BN * GT_BM * 4;                 // one CTA's partial tile in float
-    static constexpr int smem_bytes(int stages, int cluster_parts) {
-        return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + cluster_parts * PART_BYTES;
+    static constexpr int smem_bytes(int stages, int cluster_parts, int aux_bytes = 0) {
+        return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + cluster_parts * PART_BYTES + aux_bytes;
     }
 };
 
@@ -193,6 +294,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
     const uint32_t part0 = gt_smem(tiles) + STAGES * S::STAGE_BYTES + 256;     // [splits-1][BN][128] floats (cluster mode)
     const bool cluster_split = p.cluster && p.splits > 1;
+    // the q,k,v epilogue's tables lie behind the partial tiles
+    unsigned char* aux = tiles + STAGES * S::STAGE_BYTES + 256 + (cluster_split ? (p.splits - 1) * S::PART_BYTES : 0);
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
     __shared__ int last_s;
@@ -294,6 +397,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int wq = warp & 3;                    // the 32 tensor-memory lanes this warp may read
         const int et = threadIdx.x - 64;            // 0..127 among the epilogue threads
         pdl_wait();                                 // results, workspace and counters are shared with earlier kernels
+        if (p.qkv && (int)blockIdx.x < n_items && (!cluster_split || cluster_ctarank() == 0)) {
+            // where each token of the tile stands and goes, and its angles: read now, needed when the tile leaves
+            const int tile = blockIdx.x / p.splits;
+            const int tb = tile / p.tiles_a;
+            int* pos_s = reinterpret_cast<int*>(aux);
+            int* pg_s = pos_s + BN;
+            float* cs_s = reinterpret_cast<float*>(pg_s + BN);
+            const int D = p.head_dim;
+            for (int r = et; r < BN; r += 128) {
+                const int t = tb * BN + r;
+                int pos = 0, pg = -1;
+                if (t < p.M) {
+                    pos = p.positions[t];
+                    pg = p.block_table[(size_t)p.seq_of_token[t] * p.bt_stride + pos / p.page_size];
+                    if (pg >= p.num_pages) pg = -1;
+                }
+                pos_s[r] = pos;
+                pg_s[r] = pg;
+            }
+            if (p.cos_sin) {
+                for (int i = et; i < BN * (D >> 2); i += 128) {
+                    const int r = i / (D >> 2), c4 = i - r * (D >> 2);
+                    const int t = tb * BN + r;
+                    int pos = t < p.M ? p.positions[t] : 0;
+                    if (pos < 0 || pos >= p.table_rows) pos = 0;
+                    reinterpret_cast<float4*>(cs_s)[i] = reinterpret_cast<const float4*>(p.cos_sin + (size_t)pos * D)[c4];
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
         uint32_t local = 0;
         for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
             const int split = item % p.splits, tile = item / p.splits;
@@ -322,7 +455,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
                 if (p.staged) {         // the only item of this CTA: its loads have all been consumed
                     asm volatile("bar.sync 1, 128;" ::: "memory");
-                    gt_flush(p, tiles, ta, tb, BN, et);
+                    if (p.qkv) gt_flush_qkv(p, tiles, aux, ta, tb, BN, et);
+                    else gt_flush(p, tiles, ta, tb, BN, et);
                 }
                 continue;
             }
@@ -411,7 +545,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             }
             if (p.staged) {
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                gt_flush(p, tiles, ta, tb, BN, threadIdx.x - 64);
+                if (p.qkv) gt_flush_qkv(p, tiles, aux, ta, tb, BN, threadIdx.x - 64);
+                else gt_flush(p, tiles, ta, tb, BN, threadIdx.x - 64);
             }
         }
     }
@@ -434,9 +569,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     // cluster mode needs room for the peers' partial tiles beside the pipeline; else the global workspace serves
     int parts = p.cluster && p.splits > 1 ? p.splits - 1 : 0;
     if (parts && (p.splits > 8 || parts * S::PART_BYTES > 100 * 1024)) { p.cluster = 0; parts = 0; }
-    while (parts && stages > 2 && S::smem_bytes(stages, parts) > 226 * 1024) --stages;
+    const int aux_bytes = p.qkv ? BN * 8 + BN * p.head_dim * 4 : 0;
+    while ((parts || aux_bytes) && stages > 2 && S::smem_bytes(stages, parts, aux_bytes) > 226 * 1024) --stages;
     p.stages = stages;
-    const int smem = S::smem_bytes(stages, parts);
+    const int smem = S::smem_bytes(stages, parts, aux_bytes);
     static int configured = 0;
     if (smem > configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -456,6 +592,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     const int esz = p.out_f32 ? 4 : 2;
     p.staged = p.swap && grid == items && (parts || p.splits == 1) && !((uintptr_t)p.C & 15) && !((p.ldc * esz) & 15) &&
                stages * S::STAGE_BYTES >= BN * 128 * esz;
+    if (p.qkv && (!p.staged || BN > 32 || p.act || p.out_f32)) return ACV_ERR_SIZE;     // the fused q,k,v epilogue has no other form
     acv_launch_cluster(PDL_GEMM, dim3(parts ? p.splits : 1, 1, 1), gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
     return acv_launch_status();
 }
@@ -464,13 +601,12 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
 // bn: rows of the B operand per tile (16, 32, 64, 128 or 256); swap: the weight is the A operand.
 // splits > 1 needs workspace of tiles*splits*bn*128 floats and `tiles` zeroed counters.
 // status: one int, 0 unless a bounded wait inside the kernel ran out.
-ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
-                        int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
-                        int* counters, long long n_counters, int* status, int sm_count, int stages, int flags,
-                        cudaStream_t stream) {
+static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
+                       int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
+                       int* counters, long long n_counters, int* status, int sm_count, int stages, int flags,
+                       cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || (K % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15)) return ACV_ERR_ALIGN;
-    GemmParams p;
     const void* a_ptr = swap ? w : x;
     const void* b_ptr = swap ? x : w;
     p.RA = swap ? N : M;
@@ -504,3 +640,37 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
 }
 
 ACV_TL_EXPORT(gemm_tc)
+
+ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
+                        int out_f32, int act, int swap, int bn, int splits, float* workspace, long long workspace_floats,
+                        int* counters, long long n_counters, int* status, int sm_count, int stages, int flags,
+                        cudaStream_t stream) {
+    GemmParams p;
+    p.qkv = 0;
+    return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, out_f32, act, swap, bn, splits, workspace, workspace_floats,
+                       counters, n_counters, status, sm_count, stages, flags, stream);
+}
+
+// The stacked q,k,v projection with its epilogue: C [M, (NH + 2 NKV) D] gets the normed and rotated queries (its
+// key and value columns are not written), keys (normed, rotated) and values go to their pages
+// [num_pages, NKV, page_size, D] at page block_table[seq][pos / page_size], row pos % page_size; a page index < 0
+// writes nothing.  q_w, k_w (float [D]) and cos_sin ([table_rows][D]) may each be null.  Swapped roles, up to 32
+// tokens, head size 64 or 128; anything else is refused with ACV_ERR_SIZE.
+ACV_API int acv_gemm_tc_qkv(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
+                            int swap, int bn, int splits, float* workspace, long long workspace_floats, int* counters,
+                            long long n_counters, int* status, int sm_count, int stages, int flags, int NH, int NKV, int D,
+                            const float* q_w, const float* k_w, float eps, const float* cos_sin, int table_rows,
+                            const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
+                            void* k_pages, void* v_pages, int page_size, int num_pages, cudaStream_t stream) {
+    if ((D != 64 && D != 128) || NH <= 0 || NKV <= 0 || N != (NH + 2 * NKV) * D || !swap || bn > 32 || !k_pages || !v_pages ||
+        !positions || !seq_of_token || !block_table || page_size <= 0 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
+        (cos_sin && ((uintptr_t)cos_sin & 15)))
+        return ACV_ERR_SIZE;
+    GemmParams p;
+    p.qkv = 1; p.q_heads = NH; p.kv_heads = NKV; p.head_dim = D; p.q_w = q_w; p.k_w = k_w; p.qk_eps = eps;
+    p.cos_sin = cos_sin; p.table_rows = table_rows; p.positions = positions; p.seq_of_token = seq_of_token;
+    p.block_table = block_table; p.bt_stride = bt_stride; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages;
+    p.page_size = page_size; p.num_pages = num_pages;
+    return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, 0, 0, swap, bn, splits, workspace, workspace_floats, counters,
+                       n_counters, status, sm_count, stages, flags, stream);
+}

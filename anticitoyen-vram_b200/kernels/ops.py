@@ -73,6 +73,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
         "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
+        "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
         "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, I, P],
         "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
@@ -283,6 +284,44 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
                                  1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits,
                                  _p(ws), ws.numel(), _p(cnt),
                                  cnt.numel(), _p(status), _SM_COUNT, stages, cluster | (2 if static_weights else 0), _stream()), "gemm_tc")
+    return out
+
+
+def gemm_tc_qkv_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, cos_sin: torch.Tensor | None,
+                      k_pages: torch.Tensor | None) -> bool:
+    """Whether the stacked q,k,v projection of x can take its epilogue (norm, rotation, append) with it: bfloat16,
+    up to 32 tokens, heads of 64 or 128 rotated as a whole, and a plan that gives every CTA one tile."""
+    if k_pages is None or x.dtype != torch.bfloat16 or head_dim not in (64, 128) or not gemm_tc_takes(x, w):
+        return False
+    if cos_sin is not None and (cos_sin.shape[1] != head_dim or cos_sin.dtype != torch.float32):
+        return False
+    M, K = x.shape
+    N = w.shape[0]
+    swap, bn, splits = gemm_tc_plan(M, N, K)[:3]
+    tiles = -(-N // 128) * -(-M // bn)
+    return bool(swap) and bn <= 32 and (1 < splits <= 8 or (splits == 1 and tiles <= _SM_COUNT))
+
+
+def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
+                q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
+                positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
+                v_pages: torch.Tensor, static_weights: bool = False) -> torch.Tensor:
+    """The stacked q,k,v projection out[M, (NH+2NKV)*D] = x @ w^T with the epilogue of ``qk_norm_rope_append``
+    inside the product's kernel: the query columns of out hold the normed, rotated queries, keys and values go
+    to their pages (the key and value columns of out are not written).  ``gemm_tc_qkv_takes`` says when."""
+    _need_cuda(x, w, out, k_pages, v_pages)
+    M, K = x.shape
+    N = w.shape[0]
+    swap, bn, splits, stages = gemm_tc_plan(M, N, K)
+    cluster = 1 if swap and 1 < splits <= 8 else 0
+    tiles = -(-N // 128) * -(-M // bn)
+    ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
+    _check(library().acv_gemm_tc_qkv(
+        _p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K, swap, bn, splits, _p(ws), ws.numel(),
+        _p(cnt), cnt.numel(), _p(status), _SM_COUNT, stages, cluster | (2 if static_weights else 0), num_heads,
+        num_kv_heads, head_dim, _p(q_weight), _p(k_weight), eps, _p(cos_sin),
+        cos_sin.shape[0] if cos_sin is not None else 0, _p(positions), _p(seq_of_token), _p(block_table),
+        block_table.stride(0), _p(k_pages), _p(v_pages), k_pages.shape[2], k_pages.shape[0], _stream()), "gemm_tc_qkv")
     return out
 
 

@@ -68,16 +68,22 @@ class Attention(Mixer):
 
     def forward(self, h, ctx, cache: CacheView):
         NH, NKV, D = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = self.qkv(h)
         table = ctx.block_tables[cache.group]
         kp, vp = (cache.k_pages, cache.v_pages) if cache.writes else (None, None)
         eps = self.qk_norm_eps if self.qk_norm_eps is not None else 0.0
         rotary = self.position.rotary_table()
-        if rotary is not None:
+        if rotary is not None and ops.gemm_tc_qkv_takes(h, self.qkv.weight, D, rotary, kp):
+            # a few tokens: norm, rotation and append ride on the projection's kernel as its tile leaves
+            qkv = torch.empty((h.shape[0], self.qkv.out_features), device=h.device, dtype=h.dtype)
+            ops.gemm_tc_qkv(h, self.qkv.weight, qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, rotary, ctx.positions,
+                            ctx.seq_of_token, table, kp, vp, static_weights=True)
+        elif rotary is not None:
+            qkv = self.qkv(h)
             ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, rotary, ctx.positions,
                                     ctx.seq_of_token, table if kp is not None else None, kp, vp)
         else:
             # another position encoding: norm, then the part's own change of q and k, then the append
+            qkv = self.qkv(h)
             if self.q_norm is not None:
                 ops.qk_norm_rope_append(qkv, NH, NKV, D, self.q_norm, self.k_norm, eps, None, ctx.positions,
                                         ctx.seq_of_token, None, None, None)

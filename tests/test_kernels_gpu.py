@@ -397,3 +397,41 @@ def test_tensor_core_attention_growing_scores(ops):
     for q_lens, lens in (([700, 130], [700, 400]), ([257, 2], [900, 514])):
         o1, o2 = _tc_case(ops, 6, 2, 128, 16, lens=lens, q_lens=q_lens, window=0, seed=91, k_growth=1.0 / 20.0)
         torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("NH,NKV,D,T,K", [(32, 8, 128, 8, 4096), (6, 2, 64, 5, 264), (5, 1, 64, 17, 128), (4, 4, 128, 1, 512),
+                                          (3, 1, 128, 32, 136)])
+@pytest.mark.parametrize("normed,rotated", [(True, True), (False, True), (True, False)])
+def test_gemm_tc_qkv_epilogue(ops, NH, NKV, D, T, K, normed, rotated):
+    """The stacked projection with norm, rotation and append in its own kernel against the projection followed by the
+    rotation kernel: the same queries, and the same keys and values in the same pages (the sums of squares are added
+    in another order, so a rounding may move here and there)."""
+    page, n_pages = 16, 12
+    N = (NH + 2 * NKV) * D
+    x = rnd(T, K, dtype=torch.bfloat16, seed=150)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=151)
+    qw = (1.0 + 0.1 * rnd(D, dtype=torch.float32, seed=152)) if normed else None
+    kw = (1.0 + 0.1 * rnd(D, dtype=torch.float32, seed=153)) if normed else None
+    table_rows = 200
+    ang = torch.rand(table_rows, D // 2, device="cuda") * 6.28
+    cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous() if rotated else None
+    # tokens of three requests at scattered positions; one token's page is missing (-1)
+    seq = torch.tensor([i % 3 for i in range(T)], dtype=torch.int32, device="cuda")
+    pos = torch.tensor([(7 * i + 3) % 150 for i in range(T)], dtype=torch.int32, device="cuda")
+    table = torch.randperm(n_pages, device="cuda").to(torch.int32)[:3 * 4].view(3, 4).repeat(1, 3).contiguous()
+    if T > 2:
+        table[int(seq[2]), int(pos[2]) // page] = -1
+    if not ops.gemm_tc_qkv_takes(x, w, D, cos_sin, torch.empty(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)):
+        pytest.skip("no fused form for this plan")
+    kp1 = torch.zeros(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)
+    vp1, kp2, vp2 = torch.zeros_like(kp1), torch.zeros_like(kp1), torch.zeros_like(kp1)
+    want = ops.gemm_tc(x, w, torch.zeros(T, N, device="cuda", dtype=torch.bfloat16))
+    ops.qk_norm_rope_append(want, NH, NKV, D, qw, kw, 1e-6, cos_sin, pos, seq, table, kp1, vp1)
+    got = torch.zeros(T, N, device="cuda", dtype=torch.bfloat16)
+    ops.gemm_tc_qkv(x, w, got, NH, NKV, D, qw, kw, 1e-6, cos_sin, pos, seq, table, kp2, vp2)
+    assert ops.gemm_status() == 0
+    q1, q2 = want[:, :NH * D], got[:, :NH * D]
+    torch.testing.assert_close(q2, q1, **tol(torch.bfloat16))
+    torch.testing.assert_close(kp2, kp1, **tol(torch.bfloat16))
+    assert torch.equal(vp2, vp1)
+    assert (q2 != q1).float().mean() < 0.02 and (kp2 != kp1).float().mean() < 0.02
