@@ -62,11 +62,25 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
 
+@dataclass
+class _Flight:
+    """A step that has been launched and not yet read."""
+    plan: StepPlan
+    rows: list                 # the requests that get a token, in the order of ``tokens``
+    tokens: torch.Tensor | None
+    logprobs: torch.Tensor | None
+    host: torch.Tensor | None  # pinned copy of ``tokens``, valid after ``event``
+    event: torch.cuda.Event
+    t0: float
+    decode: int
+    prefill: int
+
+
 class Engine:
     def __init__(self, model, dtype="bfloat16", *, max_batch_size: int = 16, max_model_len: int = 8192,
                  page_size: int = 64, num_pages: int | None = None, token_budget: int = 2048,
                  random_weights: bool = False, seed: int = 0, device: str = "cuda:0",
-                 enable_cuda_graphs: bool = True, tokenizer=None) -> None:
+                 enable_cuda_graphs: bool = True, run_ahead: bool = True, tokenizer=None) -> None:
         """``model``: a folder with config.json and model.safetensors, or (with
         ``random_weights``) a typed configuration or a folder whose config.json alone is read."""
         from ..config import load_config
@@ -98,6 +112,11 @@ class Engine:
         if self.enable_cuda_graphs:
             self.runner.enable_graphs()
         self._ids = itertools.count()
+        # one step ahead (see ``step``): the launched, unread step and two pinned buffers for sampled tokens
+        self.pipeline = run_ahead
+        self._flight: _Flight | None = None
+        self._pinned = [torch.empty(max_batch_size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._pinned_turn = 0
         self._requests: dict[Hashable, Request] = {}
         self._seq_ids: dict[Hashable, int] = {}
 
@@ -134,10 +153,23 @@ class Engine:
 
     @property
     def idle(self) -> bool:
-        return self.scheduler.idle
+        return self.scheduler.idle and self._flight is None
 
     # ------------------------------------------------------------------ one step
     def step(self) -> list[GenerationOutput]:
+        """Run one step and deliver what is known by its end.
+
+        While every running request decodes and nobody waits, the engine works one step ahead: it launches
+        step k+1 (whose tokens it feeds on the device) before it reads step k's tokens, so that the host's
+        share of a step (planning, the batch's tables, the launch, reading the tokens) falls into the time
+        the device computes.  A call then delivers the tokens of the step launched one call earlier; the
+        first such call delivers nothing.  ``idle`` stays false until the last launched step is delivered."""
+        flight, self._flight = self._flight, None
+        if flight is not None:
+            ahead = self.scheduler.schedule_ahead(flight.plan) if self._can_run_ahead(flight) else None
+            if ahead is not None:
+                self._flight = self._launch(ahead, flight)
+            return self._complete(flight)
         plan = self.scheduler.schedule()
         outputs = [self._output(r, []) for r in plan.refused + plan.truncated]
         self.stats.preempted += len(plan.preempted)
@@ -145,37 +177,77 @@ class Engine:
         self.stats.truncated += len(plan.truncated)
         if not plan.entries:
             return outputs
+        flight = self._launch(plan, None)
+        if self.pipeline and self._can_run_ahead(flight) and self.scheduler.schedule_ahead_possible(plan):
+            self._flight = flight          # delivered by the next call, which launches the step after it first
+            return outputs
+        return outputs + self._complete(flight)
+
+    def _can_run_ahead(self, flight: "_Flight") -> bool:
+        return (self.pipeline and flight.logprobs is None and not flight.prefill
+                and all(not r.params.penalised for r in flight.rows))
+
+    def _launch(self, plan: StepPlan, after: "_Flight | None") -> "_Flight":
+        """Enqueue the step, its sampling and the copy of the sampled tokens to pinned memory; no wait.
+        ``after``: the step before, still unread; its sampled tokens are this step's inputs, on the device."""
         t0 = time.perf_counter()
-        entries = [StepEntry(e.request.request_id, e.request.tokens[e.start:e.start + e.count],
-                             (e.count - 1,) if e.samples else ()) for e in plan.entries]
-        logits = self.runner.step(entries)
+        device_tokens = None
+        lag = 0
+        if after is not None:
+            lag = 1
+            pos = {id(r): i for i, r in enumerate(after.rows)}
+            idx = [pos[id(e.request)] for e in plan.entries]
+            device_tokens = after.tokens
+            if idx != list(range(len(after.rows))):
+                # some requests ended with the step before: the others' tokens, gathered run by run with plain
+                # device copies (no kernel of another library on the step's path)
+                device_tokens = torch.empty(len(idx), dtype=after.tokens.dtype, device=after.tokens.device)
+                a = 0
+                while a < len(idx):
+                    b = a + 1
+                    while b < len(idx) and idx[b] == idx[b - 1] + 1:
+                        b += 1
+                    device_tokens[a:b].copy_(after.tokens[idx[a]:idx[a] + (b - a)])
+                    a = b
+            entries = [StepEntry(e.request.request_id, [0], (0,)) for e in plan.entries]
+        else:
+            entries = [StepEntry(e.request.request_id, e.request.tokens[e.start:e.start + e.count],
+                                 (e.count - 1,) if e.samples else ()) for e in plan.entries]
+        logits = self.runner.step(entries, device_tokens=device_tokens)
         rows = [e.request for e in plan.entries if e.samples]
-        sampled: list[int] = []
-        logprobs = None
+        tokens = logprobs = host = None
+        event = torch.cuda.Event()
         if rows:
             want_lp = any(r.params.logprobs is not None for r in rows)
             tokens, logprobs = self.sampler(
                 logits, [r.params for r in rows], [r.tokens if r.params.penalised else () for r in rows],
-                [r.seed for r in rows], [len(r.output) for r in rows], want_lp)
-            sampled = tokens.tolist()          # the step's one wait for the device
-            if logprobs is not None:
-                logprobs = logprobs.tolist()
-        else:
-            torch.cuda.current_stream().synchronize()
-        dt = time.perf_counter() - t0
-        before = {id(r): len(r.output) for r in rows}
-        touched = self.scheduler.commit(plan, sampled, self.model.plan.eos_token_ids)
-        for i, r in enumerate(touched):
+                [r.seed for r in rows], [len(r.output) + lag for r in rows], want_lp)
+            host = self._pinned[self._pinned_turn][:len(rows)]
+            self._pinned_turn ^= 1
+            host.copy_(tokens, non_blocking=True)
+        event.record()
+        decode = sum(1 for e in plan.entries if e.count == 1 and e.start > 0)
+        return _Flight(plan, rows, tokens, logprobs, host, event, t0, decode, plan.num_tokens - decode)
+
+    def _complete(self, f: "_Flight") -> list[GenerationOutput]:
+        """Wait for the step's tokens (the step's one wait for the device), record them, make the outputs."""
+        f.event.synchronize()
+        sampled = f.host.tolist() if f.host is not None else []
+        logprobs = f.logprobs.tolist() if f.logprobs is not None else None
+        dt = time.perf_counter() - f.t0
+        before = {id(r): len(r.output) for r in f.rows}
+        touched = self.scheduler.commit(f.plan, sampled, self.model.plan.eos_token_ids)
+        row_of = {id(r): i for i, r in enumerate(f.rows)}
+        outputs = []
+        for r in touched:
             new = r.output[before[id(r)]:]
             if logprobs is not None and new:
-                r.logprob_sum += logprobs[i]
+                r.logprob_sum += logprobs[row_of[id(r)]]
             outputs.append(self._output(r, new))
-        decode = sum(1 for e in plan.entries if e.count == 1 and e.start > 0)
-        prefill = plan.num_tokens - decode
         self.stats.steps += 1
-        self.stats.decode_tokens += decode
-        self.stats.prefill_tokens += prefill
-        if prefill:
+        self.stats.decode_tokens += f.decode
+        self.stats.prefill_tokens += f.prefill
+        if f.prefill:
             self.stats.prefill_seconds += dt
         else:
             self.stats.decode_seconds += dt

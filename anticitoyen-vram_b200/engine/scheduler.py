@@ -181,6 +181,43 @@ class Scheduler:
             self.counters["truncated"] += 1
         return plan
 
+    def schedule_ahead_possible(self, prev: StepPlan) -> bool:
+        """Whether ``prev`` is of the kind after which a step can be planned ahead (see ``schedule_ahead``)."""
+        return (not self.waiting and bool(prev.entries) and len(prev.entries) == len(self.running)
+                and not (prev.preempted or prev.refused or prev.truncated)
+                and all(e.count == 1 and e.samples for e in prev.entries))
+
+    def schedule_ahead(self, prev: StepPlan) -> StepPlan | None:
+        """The step after ``prev``, planned before ``prev``'s tokens are known, or None when that cannot be done.
+
+        It can when ``prev`` is single tokens of every running request and nobody waits: each request then
+        brings its next token, whatever it is (the engine feeds it on the device).  Requests that ``prev``
+        brings to their length limit are left out; one that stops on a token of its own (end of sequence, a
+        stop token) is found out only when ``prev`` is committed, and its entry here is then ignored
+        (``commit`` skips finished requests).  Nothing is preempted here: if a page is missing the caller
+        falls back to ``schedule``."""
+        if self.waiting or not prev.entries or prev.preempted or prev.refused or prev.truncated:
+            return None
+        if len(prev.entries) != len(self.running) or len(prev.entries) > self.token_budget:
+            return None
+        m = self.manager
+        keep = []
+        for e in prev.entries:
+            r = e.request
+            if e.count != 1 or not e.samples or r.finished or r not in self.running:
+                return None
+            n_out = len(r.output) + 1                      # after prev
+            if r.params.max_tokens <= 0 or n_out >= r.params.max_tokens or len(r.prompt) + n_out >= self.max_model_len:
+                continue                                   # prev is its last step
+            keep.append(e)
+        if not keep or not all(m.can_grow(e.request.request_id, e.start + 2) for e in keep):
+            return None
+        plan = StepPlan()
+        for e in keep:
+            m.grow(e.request.request_id, e.start + 2)
+            plan.entries.append(PlannedEntry(e.request, e.start + 1, 1, True))
+        return plan
+
     def schedule_after_preemption(self, earlier: StepPlan) -> StepPlan:
         plan = self.schedule()
         plan.preempted = earlier.preempted + plan.preempted
@@ -213,6 +250,10 @@ class Scheduler:
         touched = []
         for e in plan.entries:
             r = e.request
+            if r.finished:          # stopped (or aborted) after this step was planned ahead: its token is dropped
+                if e.samples:
+                    next(it, None)
+                continue
             r.computed = e.start + e.count
             if not e.samples:
                 continue

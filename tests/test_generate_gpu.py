@@ -150,3 +150,36 @@ def test_command_line_generate_and_random_model(tiny_folders, plain_models, tmp_
     a = load_file(os.path.join(tiny_folders["B"], "model.safetensors"))
     b = load_file(str(tmp_path / "m" / "model.safetensors"))
     assert all(torch.equal(a[k], b[k]) for k in a)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_one_step_ahead_changes_no_token(tiny_folders, plain_models, dtype):
+    """The engine launches a decode step before it has read the tokens of the step before it.  Requests that end on
+    a token of their own (a stop token), by their length, at different times, with seeded sampling: the same tokens,
+    the same finish reasons, every page back."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["A"]
+    prompts = [random_ids(cfg["vocab_size"], n, 300 + n) for n in (4, 19, 33, 8)]
+    ref = engine_for(tiny_folders["A"], dtype, run_ahead=False, page_size=TINY_PAGE["A"]).generate_batch(
+        prompts, SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True))
+    params = [SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True),
+              SamplingParams(temperature=0.8, top_p=0.9, seed=11, max_tokens=13, ignore_eos=True),
+              SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, stop_token_ids=[ref[2][6]]),
+              SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True)]
+    results = []
+    for ahead in (False, True):
+        eng = engine_for(tiny_folders["A"], dtype, run_ahead=ahead, page_size=TINY_PAGE["A"])
+        ids = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+        got = {i: ([], None) for i in ids}
+        calls = 0
+        while not eng.idle:
+            calls += 1
+            for out in eng.step():
+                toks, _ = got[out.request_id]
+                got[out.request_id] = (toks + out.token_ids, out.finish_reason if out.finished else None)
+        assert eng.runner.manager.free_pages() == [64]
+        eng.runner.manager.check()
+        results.append([got[i] for i in ids])
+    assert results[0] == results[1]
+    assert results[1][0] == (ref[0], "length") and results[1][2][1] == "stop" and len(results[1][2][0]) <= 7
+    assert len(results[1][1][0]) == 13 and len(results[1][3][0]) == 1

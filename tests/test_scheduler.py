@@ -185,3 +185,58 @@ def test_random_traffic_ends_with_every_page_free(seed):
         if r.finish_reason == "length" and len(r.prompt) + len(r.output) < 24:
             assert len(r.output) == r.params.max_tokens or m.paged_groups[0].pool.num_pages * 4 <= len(r.prompt) + len(r.output) + 4
     assert m.free_pages() == [m.paged_groups[0].pool.num_pages] and not m.live()
+
+
+# ----------------------------------------------------------------------------- one step ahead
+def _decode_state(n_req=3, prompt=5, max_tokens=6, **kw):
+    m, s = make(num_pages=32, page=4, max_batch=4, budget=64, **kw)
+    rs = [req(i, prompt, max_tokens=max_tokens) for i in range(n_req)]
+    for r in rs:
+        s.add(r)
+    run_step(m, s)                      # the prompts, first tokens
+    return m, s, rs
+
+
+def test_step_planned_ahead_of_the_tokens_before_it():
+    m, s, rs = _decode_state()
+    prev = s.schedule()
+    assert s.schedule_ahead_possible(prev)
+    ahead = s.schedule_ahead(prev)
+    assert [(e.request, e.start, e.count, e.samples) for e in ahead.entries] == \
+        [(e.request, e.start + 1, 1, True) for e in prev.entries]
+    s.commit(prev, [7] * 3)
+    s.commit(ahead, [8] * 3)
+    assert all(r.output[-2:] == [7, 8] and r.computed == len(r.tokens) - 1 for r in rs)
+    m.check()
+
+
+def test_ahead_leaves_out_requests_at_their_length_and_ignores_stopped_ones():
+    m, s, rs = _decode_state(max_tokens=3)
+    rs[1].params = SamplingParams(max_tokens=2)            # its next token is its last
+    prev = s.schedule()
+    ahead = s.schedule_ahead(prev)
+    assert [e.request for e in ahead.entries] == [rs[0], rs[2]]
+    # rs[0] stops on the token of prev (end of sequence): the step planned ahead still holds it, its token is dropped
+    s.commit(prev, [99, 7, 7], eos_token_ids=(99,))
+    assert rs[0].finished and rs[0].finish_reason == "stop" and rs[1].finished and rs[1].finish_reason == "length"
+    touched = s.commit(ahead, [5, 6])
+    assert touched == [rs[2]] and rs[2].output[-1] == 6 and rs[0].output[-1] == 99
+    m.check()
+    assert s.running == [] or s.running == [rs[2]] or rs[2].finished
+
+
+def test_no_step_ahead_while_someone_waits_or_a_prompt_runs_or_pages_lack():
+    m, s, rs = _decode_state()
+    s.add(req(9, 4))
+    prev = s.schedule()                                     # admits the newcomer: a prompt portion is in the plan
+    assert not s.schedule_ahead_possible(prev) and s.schedule_ahead(prev) is None
+    run = s.commit(prev, [7] * len([e for e in prev.entries if e.samples]))
+    # pages: a pool that holds exactly what is used now lets nobody grow across a page's edge
+    m2, s2 = make(num_pages=4, page=4, max_batch=2, budget=64)
+    a, b = req(0, 7, max_tokens=8), req(1, 7, max_tokens=8)
+    s2.add(a); s2.add(b)
+    run_step(m2, s2)                                        # 8 tokens each: two full pages each, pool empty
+    prev = s2.schedule()                                    # may preempt to go on; whatever it does, ahead must not steal
+    if prev.entries and not prev.preempted:
+        assert s2.schedule_ahead(prev) is None
+    m2.check()
