@@ -265,6 +265,112 @@ __device__ __forceinline__ void gt_flush_qkv(const GemmParams& p, const unsigned
     }
 }
 
+// The q,k,v epilogue with tokens on the tensor-memory lanes (many tokens, features on columns): a thread holds one
+// token's row of the tile, whole heads of it, so norm and rotation stay inside the thread.  Head by head: the
+// head's D columns are read from tensor memory and rounded to bfloat16 (what the projection's output would hold),
+// their squares summed; then, 16 angles at a time, both halves of the head are scaled, rotated and written: queries to
+// C, keys and values to the token's page.  The same arithmetic as gt_flush_qkv and the rotation kernel.
+template <int BN, int D>                         // D: head size, 64 or 128; BN is a multiple of it
+__device__ __forceinline__ void gt_store_qkv_rows(const GemmParams& p, uint32_t taddr, int token, int tb) {
+    const bool live = token < p.M;
+    int pos = 0, pg = -1;
+    if (live) {
+        pos = p.positions[token];
+        pg = p.block_table[(size_t)p.seq_of_token[token] * p.bt_stride + pos / p.page_size];
+        if (pg >= p.num_pages) pg = -1;
+    }
+    const bool in_table = pos >= 0 && pos < p.table_rows;
+    const float* cs = p.cos_sin ? p.cos_sin + (size_t)(in_table ? pos : 0) * D : nullptr;
+#pragma unroll 1
+    for (int h0 = 0; h0 < BN; h0 += D) {
+        const int f0 = tb * BN + h0;                // first feature of the head in the stacked output
+        if (f0 >= p.N) break;
+        const int head = f0 / D;
+        const bool is_q = head < p.q_heads, is_k = !is_q && head < p.q_heads + p.kv_heads, is_v = !is_q && !is_k;
+        const float* w = is_q ? p.q_w : (is_k ? p.k_w : nullptr);
+        // the head's values, rounded as the projection rounds, kept as pairs
+        uint32_t packed[D / 2];
+        float ss = 0.f;
+#pragma unroll
+        for (int c0 = 0; c0 < D; c0 += 16) {
+            {                                       // tensor-memory loads are executed by whole warps
+                uint32_t r[16];
+                tc_ld16(taddr + h0 + c0, r);
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                    const uint32_t pk = pack2(r[c], r[c + 1]);
+                    packed[(c0 + c) >> 1] = pk;
+                    const __nv_bfloat162 b2 = *reinterpret_cast<const __nv_bfloat162*>(&pk);
+                    const float x0 = __low2float(b2), x1 = __high2float(b2);
+                    ss += x0 * x0 + x1 * x1;
+                }
+            }
+        }
+        const float inv = w ? rsqrtf(ss / (float)D + p.qk_eps) : 1.f;
+        bf16* dst = nullptr;
+        if (live) {
+            if (is_q) {
+                dst = (bf16*)p.C + (size_t)token * p.ldc + f0;
+            } else if (pg >= 0) {
+                const int kvh = is_k ? head - p.q_heads : head - p.q_heads - p.kv_heads;
+                dst = (is_k ? p.k_pages : p.v_pages) + (((size_t)pg * p.kv_heads + kvh) * p.page_size + (pos % p.page_size)) * D;
+            }
+        }
+        const bool rotate = cs && !is_v && in_table;
+        constexpr int half = D >> 1;
+#pragma unroll
+        for (int i0 = 0; i0 < half; i0 += 16) {
+            {
+                float lo[16], hi[16];               // elements i0 .. i0+15 and their partners half further
+#pragma unroll
+                for (int c = 0; c < 16; c += 2) {
+                    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&packed[(i0 + c) >> 1]);
+                    const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&packed[(half + i0 + c) >> 1]);
+                    lo[c] = __low2float(a); lo[c + 1] = __high2float(a);
+                    hi[c] = __low2float(b); hi[c + 1] = __high2float(b);
+                }
+                if (w) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        lo[c] = lo[c] * inv * __ldg(w + i0 + c);
+                        hi[c] = hi[c] * inv * __ldg(w + half + i0 + c);
+                    }
+                }
+                if (rotate) {
+#pragma unroll
+                    for (int c4 = 0; c4 < 16; c4 += 4) {
+                        const float4 c = *reinterpret_cast<const float4*>(cs + i0 + c4);
+                        const float4 sn = *reinterpret_cast<const float4*>(cs + half + i0 + c4);
+                        const float cc[4] = {c.x, c.y, c.z, c.w}, sv[4] = {sn.x, sn.y, sn.z, sn.w};
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            const float a = lo[c4 + u], b = hi[c4 + u];
+                            lo[c4 + u] = a * cc[u] - b * sv[u];
+                            hi[c4 + u] = b * cc[u] + a * sv[u];
+                        }
+                    }
+                }
+                if (dst) {
+                    uint4 o;
+#pragma unroll
+                    for (int g = 0; g < 2; ++g) {
+                        o.x = pack2(__float_as_uint(lo[8 * g]), __float_as_uint(lo[8 * g + 1]));
+                        o.y = pack2(__float_as_uint(lo[8 * g + 2]), __float_as_uint(lo[8 * g + 3]));
+                        o.z = pack2(__float_as_uint(lo[8 * g + 4]), __float_as_uint(lo[8 * g + 5]));
+                        o.w = pack2(__float_as_uint(lo[8 * g + 6]), __float_as_uint(lo[8 * g + 7]));
+                        *reinterpret_cast<uint4*>(dst + i0 + 8 * g) = o;
+                        o.x = pack2(__float_as_uint(hi[8 * g]), __float_as_uint(hi[8 * g + 1]));
+                        o.y = pack2(__float_as_uint(hi[8 * g + 2]), __float_as_uint(hi[8 * g + 3]));
+                        o.z = pack2(__float_as_uint(hi[8 * g + 4]), __float_as_uint(hi[8 * g + 5]));
+                        o.w = pack2(__float_as_uint(hi[8 * g + 6]), __float_as_uint(hi[8 * g + 7]));
+                        *reinterpret_cast<uint4*>(dst + half + i0 + 8 * g) = o;
+                    }
+                }
+            }
+        }
+    }
+}
+
 template <int BN>
 struct GemmShape {
     static constexpr int STAGE_BYTES = (GT_BM + BN) * GT_BK * 2;
@@ -397,7 +503,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         const int wq = warp & 3;                    // the 32 tensor-memory lanes this warp may read
         const int et = threadIdx.x - 64;            // 0..127 among the epilogue threads
         pdl_wait();                                 // results, workspace and counters are shared with earlier kernels
-        if (p.qkv && (int)blockIdx.x < n_items && (!cluster_split || cluster_ctarank() == 0)) {
+        if (p.qkv && p.swap && (int)blockIdx.x < n_items && (!cluster_split || cluster_ctarank() == 0)) {
             // where each token of the tile stands and goes, and its angles: read now, needed when the tile leaves
             const int tile = blockIdx.x / p.splits;
             const int tb = tile / p.tiles_a;
@@ -437,6 +543,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (et == 0 && item + (int)gridDim.x >= n_items) ACV_TL_MARK(TL_M_ACC_DONE);
             const int row_a = ta * GT_BM + wq * 32 + lane;          // row of the A operand this thread holds
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(wq * 32) << 16);
+            if (p.splits == 1 && p.qkv && !p.swap) {
+                if constexpr (BN >= 128) {
+                    if (p.head_dim == 128) gt_store_qkv_rows<BN, 128>(p, taddr, row_a, tb);
+                    else gt_store_qkv_rows<BN, 64>(p, taddr, row_a, tb);
+                } else if constexpr (BN == 64) {
+                    gt_store_qkv_rows<BN, 64>(p, taddr, row_a, tb);
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+                continue;
+            }
             if (p.splits == 1) {
                 const int rows_b = min(BN, p.RB - tb * BN);
 #pragma unroll 1
@@ -569,7 +687,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     // cluster mode needs room for the peers' partial tiles beside the pipeline; else the global workspace serves
     int parts = p.cluster && p.splits > 1 ? p.splits - 1 : 0;
     if (parts && (p.splits > 8 || parts * S::PART_BYTES > 100 * 1024)) { p.cluster = 0; parts = 0; }
-    const int aux_bytes = p.qkv ? BN * 8 + BN * p.head_dim * 4 : 0;
+    const int aux_bytes = p.qkv && p.swap ? BN * 8 + BN * p.head_dim * 4 : 0;
     while ((parts || aux_bytes) && stages > 2 && S::smem_bytes(stages, parts, aux_bytes) > 226 * 1024) --stages;
     p.stages = stages;
     const int smem = S::smem_bytes(stages, parts, aux_bytes);
@@ -592,7 +710,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     const int esz = p.out_f32 ? 4 : 2;
     p.staged = p.swap && grid == items && (parts || p.splits == 1) && !((uintptr_t)p.C & 15) && !((p.ldc * esz) & 15) &&
                stages * S::STAGE_BYTES >= BN * 128 * esz;
-    if (p.qkv && (!p.staged || BN > 32 || p.act || p.out_f32)) return ACV_ERR_SIZE;     // the fused q,k,v epilogue has no other form
+    // the fused q,k,v epilogue exists for staged tiles of up to 32 tokens, and for tokens on M with whole heads in a tile
+    if (p.qkv && p.swap && (!p.staged || BN > 32)) return ACV_ERR_SIZE;
+    if (p.qkv && !p.swap && (p.splits != 1 || BN < p.head_dim || BN % p.head_dim)) return ACV_ERR_SIZE;
+    if (p.qkv && (p.act || p.out_f32)) return ACV_ERR_SIZE;
     acv_launch_cluster(PDL_GEMM, dim3(parts ? p.splits : 1, 1, 1), gemm_tc_kernel<BN>, grid, GT_THREADS, smem, stream, ma, mb, p);
     return acv_launch_status();
 }
@@ -654,15 +775,15 @@ ACV_API int acv_gemm_tc(const void* x, int ldx, const void* w, int ldw, void* C,
 // The stacked q,k,v projection with its epilogue: C [M, (NH + 2 NKV) D] gets the normed and rotated queries (its
 // key and value columns are not written), keys (normed, rotated) and values go to their pages
 // [num_pages, NKV, page_size, D] at page block_table[seq][pos / page_size], row pos % page_size; a page index < 0
-// writes nothing.  q_w, k_w (float [D]) and cos_sin ([table_rows][D]) may each be null.  Swapped roles, up to 32
-// tokens, head size 64 or 128; anything else is refused with ACV_ERR_SIZE.
+// writes nothing.  q_w, k_w (float [D]) and cos_sin ([table_rows][D]) may each be null.  Swapped roles with up to 32
+// tokens, or tokens on M without a split of K; head size 64 or 128; anything else is refused with ACV_ERR_SIZE.
 ACV_API int acv_gemm_tc_qkv(const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
                             int swap, int bn, int splits, float* workspace, long long workspace_floats, int* counters,
                             long long n_counters, int* status, int sm_count, int stages, int flags, int NH, int NKV, int D,
                             const float* q_w, const float* k_w, float eps, const float* cos_sin, int table_rows,
                             const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
                             void* k_pages, void* v_pages, int page_size, int num_pages, cudaStream_t stream) {
-    if ((D != 64 && D != 128) || NH <= 0 || NKV <= 0 || N != (NH + 2 * NKV) * D || !swap || bn > 32 || !k_pages || !v_pages ||
+    if ((D != 64 && D != 128) || NH <= 0 || NKV <= 0 || N != (NH + 2 * NKV) * D || (swap && bn > 32) || !k_pages || !v_pages ||
         !positions || !seq_of_token || !block_table || page_size <= 0 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
         (cos_sin && ((uintptr_t)cos_sin & 15)))
         return ACV_ERR_SIZE;

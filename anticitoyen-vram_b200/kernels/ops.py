@@ -290,7 +290,8 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
 def gemm_tc_qkv_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, cos_sin: torch.Tensor | None,
                       k_pages: torch.Tensor | None) -> bool:
     """Whether the stacked q,k,v projection of x can take its epilogue (norm, rotation, append) with it: bfloat16,
-    up to 32 tokens, heads of 64 or 128 rotated as a whole, and a plan that gives every CTA one tile."""
+    heads of 64 or 128 rotated as a whole, and either up to 32 tokens with a plan that gives every CTA one tile
+    (features on the tensor-memory lanes) or more than 128 tokens (tokens on the lanes, whole heads in a tile)."""
     if k_pages is None or x.dtype != torch.bfloat16 or head_dim not in (64, 128) or not gemm_tc_takes(x, w):
         return False
     if cos_sin is not None and (cos_sin.shape[1] != head_dim or cos_sin.dtype != torch.float32):
@@ -298,8 +299,10 @@ def gemm_tc_qkv_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, cos_sin: 
     M, K = x.shape
     N = w.shape[0]
     swap, bn, splits = gemm_tc_plan(M, N, K)[:3]
+    if not swap:            # tokens on M: a thread of the epilogue holds whole heads of one token
+        return splits == 1 and bn >= head_dim and bn % head_dim == 0
     tiles = -(-N // 128) * -(-M // bn)
-    return bool(swap) and bn <= 32 and (1 < splits <= 8 or (splits == 1 and tiles <= _SM_COUNT))
+    return bn <= 32 and (1 < splits <= 8 or (splits == 1 and tiles <= _SM_COUNT))
 
 
 def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -314,7 +317,7 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_heads: 
     N = w.shape[0]
     swap, bn, splits, stages = gemm_tc_plan(M, N, K)
     cluster = 1 if swap and 1 < splits <= 8 else 0
-    tiles = -(-N // 128) * -(-M // bn)
+    tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     _check(library().acv_gemm_tc_qkv(
         _p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K, swap, bn, splits, _p(ws), ws.numel(),

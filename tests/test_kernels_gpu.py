@@ -400,7 +400,9 @@ def test_tensor_core_attention_growing_scores(ops):
 
 
 @pytest.mark.parametrize("NH,NKV,D,T,K", [(32, 8, 128, 8, 4096), (6, 2, 64, 5, 264), (5, 1, 64, 17, 128), (4, 4, 128, 1, 512),
-                                          (3, 1, 128, 32, 136)])
+                                          (3, 1, 128, 32, 136),
+                                          # many tokens: tokens on the tensor-memory lanes, whole heads inside a thread's row
+                                          (8, 2, 128, 300, 512), (6, 2, 64, 129, 264), (5, 1, 64, 700, 128), (3, 1, 128, 257, 136)])
 @pytest.mark.parametrize("normed,rotated", [(True, True), (False, True), (True, False)])
 def test_gemm_tc_qkv_epilogue(ops, NH, NKV, D, T, K, normed, rotated):
     """The stacked projection with norm, rotation and append in its own kernel against the projection followed by the
@@ -412,13 +414,15 @@ def test_gemm_tc_qkv_epilogue(ops, NH, NKV, D, T, K, normed, rotated):
     w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=151)
     qw = (1.0 + 0.1 * rnd(D, dtype=torch.float32, seed=152)) if normed else None
     kw = (1.0 + 0.1 * rnd(D, dtype=torch.float32, seed=153)) if normed else None
-    table_rows = 200
+    table_rows = max(200, T)
     ang = torch.rand(table_rows, D // 2, device="cuda") * 6.28
     cos_sin = torch.cat([ang.cos(), ang.sin()], dim=1).contiguous() if rotated else None
     # tokens of three requests at scattered positions; one token's page is missing (-1)
     seq = torch.tensor([i % 3 for i in range(T)], dtype=torch.int32, device="cuda")
-    pos = torch.tensor([(7 * i + 3) % 150 for i in range(T)], dtype=torch.int32, device="cuda")
-    table = torch.randperm(n_pages, device="cuda").to(torch.int32)[:3 * 4].view(3, 4).repeat(1, 3).contiguous()
+    pos = torch.tensor([(7 * i + 3) % 150 if T <= 32 else i // 3 for i in range(T)], dtype=torch.int32, device="cuda")
+    per_request = int(pos.max()) // page + 1
+    n_pages = 3 * per_request + 2
+    table = torch.randperm(n_pages, device="cuda").to(torch.int32)[:3 * per_request].view(3, per_request).contiguous()
     if T > 2:
         table[int(seq[2]), int(pos[2]) // page] = -1
     if not ops.gemm_tc_qkv_takes(x, w, D, cos_sin, torch.empty(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)):
