@@ -12,6 +12,8 @@ static metadata buffer; a step only copies its packed metadata there and replays
 
 from __future__ import annotations
 
+import gc
+
 import torch
 
 from ..kernels import ops
@@ -88,8 +90,19 @@ class DecodeGraphs:
         torch.cuda.synchronize(r.rt.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
-        with torch.cuda.graph(graph):
-            logits = r.model.forward(ctx, r.storage)
+        # While a stream is being captured, CUDA by default refuses calls it counts as unsafe from anywhere in the
+        # process (freeing pinned memory, destroying another graph, querying an event) and the capture is lost.
+        # The garbage collector makes such calls when it finalises objects of an engine that is no longer used; seen
+        # as a capture that failed now and then in a process that had built many engines.  None of them touches the
+        # capturing stream, so the capture runs in relaxed mode, and the collector rests while it lasts.
+        gc_was_on = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+                logits = r.model.forward(ctx, r.storage)
+        finally:
+            if gc_was_on:
+                gc.enable()
         kernels = ops.LAUNCHES - before
         graph.replay()
         slot = {"graph": graph, "dev": dev, "ctx": ctx, "logits": logits, "kernels": kernels}

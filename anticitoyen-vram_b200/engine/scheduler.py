@@ -210,7 +210,13 @@ class Scheduler:
             if r.params.max_tokens <= 0 or n_out >= r.params.max_tokens or len(r.prompt) + n_out >= self.max_model_len:
                 continue                                   # prev is its last step
             keep.append(e)
-        if not keep or not all(m.can_grow(e.request.request_id, e.start + 2) for e in keep):
+        if not keep:
+            return None
+        needed = [0] * len(m.paged_groups)                 # pages of every group, for all of them together
+        for e in keep:
+            for gi, n in enumerate(m.pages_missing(e.request.request_id, e.start + 2)):
+                needed[gi] += n
+        if any(n > g.pool.num_free for n, g in zip(needed, m.paged_groups)):
             return None
         plan = StepPlan()
         for e in keep:

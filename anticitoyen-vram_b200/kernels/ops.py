@@ -100,7 +100,18 @@ def _check(code: int, name: str) -> None:
         return
     if code < 0:
         raise KernelError(f"{name}: {_ERRORS.get(code, f'refused with code {code}')}")
-    raise KernelError(f"{name}: CUDA error {code} ({torch.cuda.cudart().cudaGetErrorString(code) if hasattr(torch.cuda.cudart(), 'cudaGetErrorString') else 'see cudaError_t'})")
+    raise KernelError(f"{name}: CUDA error {code} ({_cuda_error_text(code)})")
+
+
+def _cuda_error_text(code: int) -> str:
+    """The runtime's own words for a cudaError_t, asked of the library that the kernels are linked against."""
+    try:
+        fn = ctypes.CDLL("libcudart.so.12").cudaGetErrorString
+        fn.restype = ctypes.c_char_p
+        fn.argtypes = [ctypes.c_int]
+        return fn(code).decode()
+    except Exception:       # no such library name on this system: the number has to do
+        return "see cudaError_t"
 
 
 def _stream() -> int:

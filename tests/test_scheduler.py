@@ -240,3 +240,16 @@ def test_no_step_ahead_while_someone_waits_or_a_prompt_runs_or_pages_lack():
     if prev.entries and not prev.preempted:
         assert s2.schedule_ahead(prev) is None
     m2.check()
+
+
+def test_ahead_counts_the_pages_of_all_requests_together():
+    """Two requests that each need a new page for the step ahead, one free page: no step ahead (and nothing taken)."""
+    m, s = make(num_pages=5, page=4, max_batch=2, budget=64)
+    a, b = req(0, 3, max_tokens=8), req(1, 3, max_tokens=8)
+    s.add(a); s.add(b)
+    run_step(m, s)                  # 3 tokens each in the cache, one page each; both now bring their 4th token
+    prev = s.schedule()             # positions 3: still the first page
+    free = m.free_pages()
+    assert free == [3]
+    m.paged_groups[0].pool.allocate(2)          # somebody else's pages: one page left for two requests that both need one
+    assert s.schedule_ahead(prev) is None and m.free_pages() == [1]
