@@ -183,3 +183,56 @@ def test_running_one_step_ahead_changes_no_token(tiny_folders, plain_models, dty
     assert results[0] == results[1]
     assert results[1][0] == (ref[0], "length") and results[1][2][1] == "stop" and len(results[1][2][0]) <= 7
     assert len(results[1][1][0]) == 13 and len(results[1][3][0]) == 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_traffic_gives_the_same_tokens_one_step_ahead_or_not(tiny_folders, plain_models, dtype):
+    """Random requests (greedy, seeded sampling, stop tokens, lengths from 1 token up) arriving at random steps into
+    pools small enough to preempt and to make requests wait: every request gets the same tokens and the same end
+    whether the engine runs one step ahead or not, and every page comes back."""
+    import random
+    from acvram_b200 import SamplingParams
+    cfg, _ = plain_models["A"]
+    vocab = cfg["vocab_size"]
+
+    def run(seed, ahead):
+        rng = random.Random(seed)
+        pages = rng.choice([10, 14, 40])
+        eng = engine_for(tiny_folders["A"], dtype, run_ahead=ahead, page_size=16, num_pages=pages, max_model_len=200,
+                         token_budget=rng.choice([8, 32, 64]))
+        reqs = []
+        for i in range(rng.randint(3, 8)):
+            prompt = [rng.randrange(vocab) for _ in range(rng.randint(1, 60))]
+            kind = rng.random()
+            if kind < 0.5:
+                sp = SamplingParams(temperature=0.0, max_tokens=rng.randint(1, 40), ignore_eos=rng.random() < 0.5)
+            elif kind < 0.8:
+                sp = SamplingParams(temperature=0.9, top_p=0.9, top_k=rng.choice([0, 5]), seed=rng.randrange(1000),
+                                    max_tokens=rng.randint(1, 40), ignore_eos=True)
+            else:
+                sp = SamplingParams(temperature=0.0, max_tokens=rng.randint(5, 40), ignore_eos=True,
+                                    stop_token_ids=[rng.randrange(vocab) for _ in range(40)])
+            reqs.append((prompt, sp, rng.randint(0, 30)))
+        got, step, pending = {}, 0, list(enumerate(reqs))
+        while pending or not eng.idle:
+            for k, (p, sp, at) in list(pending):
+                if at <= step:
+                    eng.add_request(p, sp, request_id=f"r{k}")
+                    pending.remove((k, (p, sp, at)))
+            for o in eng.step():
+                toks, _ = got.get(o.request_id, ([], None))
+                got[o.request_id] = (toks + o.token_ids, o.finish_reason if o.finished else None)
+            step += 1
+            assert step < 3000
+        eng.runner.manager.check()
+        assert eng.runner.manager.free_pages() == [pages]
+        return got, eng.stats.preempted
+
+    preempted = 0
+    for seed in range(10):
+        a, pa = run(seed, False)
+        b, pb = run(seed, True)
+        assert a == b, f"seed {seed}"
+        assert all(reason is not None for _, reason in a.values())
+        preempted += pa + pb
+    assert preempted > 0       # the small pools did make requests give way
