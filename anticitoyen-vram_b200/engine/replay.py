@@ -73,5 +73,9 @@ def main(argv=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens that live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE,
+                    help="tokens per cache page (a divisor of 64, so that the rounding of --max-tokens holds)")
     args = ap.parse_args(argv)
-    return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout, args.device)
+    if args.page_size < 1 or 64 % args.page_size:
+        ap.error("--page-size must divide 64")
+    return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout, args.device, args.page_size)

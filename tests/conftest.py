@@ -52,11 +52,15 @@ def tiny_config(which: str):
         return Qwen3Config(vocab_size=211, hidden_size=100, intermediate_size=150, num_hidden_layers=2,
                            num_attention_heads=3, num_key_value_heads=3, head_dim=16, rms_norm_eps=1e-6,
                            rope_theta=10000.0, max_position_embeddings=256, tie_word_embeddings=True)
+    if which == "F":  # heads of 128, the main head size of the tensor-core kernels; pairs of query heads on a kv head
+        return Qwen3Config(vocab_size=512, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
+                           num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
+                           rope_theta=1000000.0, max_position_embeddings=1024, tie_word_embeddings=False)
     raise KeyError(which)
 
 
-TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4}
-TINY_PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16}
+TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5}
+TINY_PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16, "F": 64}
 
 
 @pytest.fixture(scope="session")
@@ -64,7 +68,7 @@ def tiny_folders(tmp_path_factory):
     """{name: folder} of the tiny models, written once per session into a temporary folder."""
     from acvram_b200.weights import write_random_model
     out = {}
-    for name in ("A", "B", "C", "D", "E"):
+    for name in ("A", "B", "C", "D", "E", "F"):
         folder = tmp_path_factory.mktemp(f"tiny_{name}")
         write_random_model(tiny_config(name), folder, TINY_SEEDS[name])
         out[name] = str(folder)

@@ -115,10 +115,11 @@ def play_mixed(tr: Trace, reqs, tag: str, seed: int, max_live: int = 4, tail: in
 
 
 # --------------------------------------------------------------------------- running
-def run_trace(folder: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int) -> dict:
+def run_trace(folder: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int, page_size: int | None = None) -> dict:
     env = dict(os.environ)
+    extra = ["--page-size", str(page_size)] if page_size else []
     proc = subprocess.Popen([sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
-                             "--max-tokens", str(max_tokens)], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
+                             "--max-tokens", str(max_tokens), *extra], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
                             text=True, env=env)
     try:
         for s in tr.steps:
@@ -141,7 +142,8 @@ def run_trace(folder: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int)
 
 
 def requests_for(name: str, vocab: int) -> dict[str, list[int]]:
-    lengths = {"A": [5, 17, 33, 70, 130], "B": [1, 9, 40, 130, 75], "C": [3, 64, 97, 250], "D": [2, 65, 129, 200, 31], "E": [4, 37, 90]}[name]
+    lengths = {"A": [5, 17, 33, 70, 130], "B": [1, 9, 40, 130, 75], "C": [3, 64, 97, 250], "D": [2, 65, 129, 200, 31], "E": [4, 37, 90],
+               "F": [3, 66, 131, 300, 129]}[name]
     return {str(i): random_ids(vocab, n, seed=100 + i) for i, n in enumerate(lengths)}
 
 
@@ -182,7 +184,7 @@ def worst(got, ref, modes):
     return {modes[m]: v for m, v in out.items()}
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "E"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "E", "F"])
 def test_replay_float32(name, tiny_folders, plain_logits, tmp_path):
     cfg = json.load(open(os.path.join(tiny_folders[name], "config.json")))
     tr, reqs, modes = build_full_trace(name, cfg["vocab_size"])
@@ -195,11 +197,13 @@ def test_replay_float32(name, tiny_folders, plain_logits, tmp_path):
         assert d <= 2e-5 * max(1.0, scale), f"{mode}: max |logit - plain| = {d:.3e} at request/position {where}"
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E"])
-def test_replay_bfloat16(name, tiny_folders, plain_logits, tmp_path):
+@pytest.mark.parametrize("name,page", [("A", None), ("B", None), ("C", None), ("D", None), ("E", None), ("F", None), ("F", 64),
+                                       ("D", 32)])
+def test_replay_bfloat16(name, page, tiny_folders, plain_logits, tmp_path):
+    """page None: trace_run's own page of 16; F and D also with the serving default of 64 and with 32."""
     cfg = json.load(open(os.path.join(tiny_folders[name], "config.json")))
     tr, reqs, modes = build_full_trace(name, cfg["vocab_size"])
-    got = run_trace(tiny_folders[name], "bfloat16", tr, str(tmp_path), tr.live_peak)
+    got = run_trace(tiny_folders[name], "bfloat16", tr, str(tmp_path), tr.live_peak, page)
     ref = plain_logits(name)
     ref_bf16 = plain_logits(name, torch.bfloat16)
     # the yardstick: how far the plain implementation's own bfloat16 run is from its float32 run
