@@ -113,38 +113,40 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
+        // lane i brings page i of a key tile, so the block-table reads of a tile's pages run side by side
         if (lane == 0) {
             mbar_expect_tx(q_full, n_heads * Q_BYTES);
             for (int h = 0; h < n_heads; ++h)
 #pragma unroll
                 for (int a = 0; a < DA; ++a)
                     tma_load_2d(q_s + h * Q_BYTES + a * AT_ATOM, &map_q, q_full, (h0 + h) * D + a * 64, tok0);
-            const int ps = p.page_size, pages_per_tile = AT_BN >> p.page_shift;
-            for (int t = 0; t < n_tiles && !abort_s; ++t) {
-                const int s = t & 1;
-                if (t >= 2 && !mbar_wait(kv_free + 8 * s, ((t >> 1) - 1) & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 11); break; }
-                const int j0 = j_first + t * AT_BN;
-                // pages of this tile that hold keys some row reads; the others are skipped (their rows are masked)
-                uint32_t bytes = 0;
-                for (int i = 0; i < pages_per_tile; ++i) {
-                    const int j = j0 + i * ps;
-                    if (j > hi || j + ps - 1 < lo) continue;
-                    const int pg = bt[j >> p.page_shift];
-                    if (pg >= 0 && pg < p.num_pages) bytes += 2u * DA * ps * 128u;
+        }
+        const int ps = p.page_size, pages_per_tile = AT_BN >> p.page_shift;
+        for (int t = 0; t < n_tiles; ++t) {
+            const int s = t & 1;
+            int go = 1;
+            if (lane == 0) {
+                if (abort_s) go = 0;
+                else if (t >= 2 && !mbar_wait(kv_free + 8 * s, ((t >> 1) - 1) & 1, &abort_s)) {
+                    abort_s = 1; atomicExch(p.status, 11); go = 0;
                 }
-                mbar_expect_tx(kv_full + 8 * s, bytes);
-                const uint32_t k_dst = kv_s + s * 2 * KV_BYTES, v_dst = k_dst + KV_BYTES;
-                for (int i = 0; i < pages_per_tile; ++i) {
-                    const int j = j0 + i * ps;
-                    if (j > hi || j + ps - 1 < lo) continue;
-                    const int pg = bt[j >> p.page_shift];
-                    if (pg < 0 || pg >= p.num_pages) continue;
-                    const int row = (pg * p.NKV + kvh) * ps;
+            }
+            if (!__shfl_sync(0xffffffffu, go, 0)) break;
+            // pages of this tile that hold keys some row reads; the others are skipped (their rows are masked)
+            const int j = j_first + t * AT_BN + lane * ps;
+            int pg = -1;
+            if (lane < pages_per_tile && j <= hi && j + ps - 1 >= lo) pg = bt[j >> p.page_shift];
+            const bool take = pg >= 0 && pg < p.num_pages;
+            const uint32_t taken = __ballot_sync(0xffffffffu, take);
+            if (lane == 0) mbar_expect_tx(kv_full + 8 * s, __popc(taken) * 2u * DA * ps * 128u);
+            __syncwarp();
+            if (take) {
+                const uint32_t k_dst = kv_s + s * 2 * KV_BYTES + lane * ps * 128, v_dst = k_dst + KV_BYTES;
+                const int row = (pg * p.NKV + kvh) * ps;
 #pragma unroll
-                    for (int a = 0; a < DA; ++a) {
-                        tma_load_2d(k_dst + a * AT_ATOM + i * ps * 128, &map_k, kv_full + 8 * s, a * 64, row);
-                        tma_load_2d(v_dst + a * AT_ATOM + i * ps * 128, &map_v, kv_full + 8 * s, a * 64, row);
-                    }
+                for (int a = 0; a < DA; ++a) {
+                    tma_load_2d(k_dst + a * AT_ATOM, &map_k, kv_full + 8 * s, a * 64, row);
+                    tma_load_2d(v_dst + a * AT_ATOM, &map_v, kv_full + 8 * s, a * 64, row);
                 }
             }
         }

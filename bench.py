@@ -7,7 +7,7 @@ The model has the layer sizes of Qwen3-8B (36 layers, hidden 4096, 32 query and
 8 key/value heads of 128, intermediate 12288, vocabulary 151936, rope theta 1e6,
 eps 1e-6, untied head) with random weights N(0, 0.02) in bfloat16; the default
 run decodes a batch of 8 requests that each hold a 2048-token synthetic context
-in a paged bfloat16 cache (page 64).  A step is one decode step of the whole
+in a paged bfloat16 cache (pages of 16 tokens, as the baseline's configuration has them).  A step is one decode step of the whole
 batch.  One JSON line is printed: ``value`` is decoded tokens per second timed on
 the device over exactly K steps after W warm-up steps; ``e2e`` is the same through
 ``Engine.step()`` with host token ids in and out; ``prefill`` is one 2048-token
@@ -71,7 +71,7 @@ def run_ours(args) -> int:
     print(f"[bench] model built in {time.time() - t0:.1f} s ({model.weight_bytes() / 1e9:.2f} GB)", file=sys.stderr)
 
     K, W = args.steps, args.warmup
-    page = 64     # the serving default: a page is one TMA box of the prompt attention
+    page = args.page_size
     per_request = args.context + 2 * (K + W) + 3 * page
     max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
     num_pages = max_batch * ((per_request + page - 1) // page) + 8 + (2048 + page) // page
@@ -162,6 +162,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
+    ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (the engine's own default is 64)")
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 and 64 points")
     ap.add_argument("--no-cuda-graphs", action="store_true")
     args = ap.parse_args()
