@@ -84,10 +84,12 @@ def run(args) -> int:
     sys.path.insert(0, REF)
     work = tempfile.mkdtemp(prefix="acvram_ref_", dir=os.environ.get("ACVRAM_REF_TMP", tempfile.gettempdir()))
     try:
-        from bench import QWEN3_8B  # the sizes bench.py names
+        from bench import SHAPES  # the sizes bench.py names
 
-        layers = args.layers or QWEN3_8B["num_hidden_layers"]
-        cfg = {**QWEN3_8B, "num_hidden_layers": layers, "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
+        shape = SHAPES[getattr(args, "shape", "8b")]
+        shape_name = f"Qwen3-{getattr(args, 'shape', '8b').upper()} shape"
+        layers = args.layers or shape["num_hidden_layers"]
+        cfg = {**shape, "num_hidden_layers": layers, "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3",
                "hidden_act": "silu", "torch_dtype": "bfloat16", "eos_token_id": 151645, "bos_token_id": 151643}
         hf = os.path.join(work, "hf")
         t0 = time.time()
@@ -136,11 +138,11 @@ def run(args) -> int:
             tokens += sum(len(o.token_ids) for o in engine.step())
         torch.cuda.synchronize()
         dt = time.perf_counter() - t0
-        line = {"impl": "reference", "metric": "decode tok/s at batch 8 (Qwen3-8B shape, 2048-token contexts)",
+        line = {"impl": "reference", "metric": f"decode tok/s at batch {args.batch} ({shape_name}, {args.context}-token contexts)",
                 "value": round(tokens / dt, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
                 "ms_per_step": round(dt / K * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02)",
-                "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": QWEN3_8B["num_hidden_layers"],
+                "config": {"model": shape_name, "layers": layers, "layers_full": shape["num_hidden_layers"],
                            "global_batch": args.batch, "seq_len": args.context, "max_model_len": max_len,
                            "kv_dtype": "bf16", "parallelism": "single GPU", "timing": "wall clock around Engine.step"},
                 "e2e": {"value": round(tokens / dt, 1), "unit": "tokens/s"}}

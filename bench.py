@@ -30,6 +30,12 @@ sys.path.insert(0, ROOT)
 QWEN3_8B = dict(vocab_size=151936, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36,
                 num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1000000.0,
                 max_position_embeddings=40960, tie_word_embeddings=False)
+# the larger shapes that the baseline's configurations name, for `--shape`; the default run is the 8B shape
+SHAPES = {
+    "8b": QWEN3_8B,
+    "14b": {**QWEN3_8B, "hidden_size": 5120, "intermediate_size": 17408, "num_hidden_layers": 40, "num_attention_heads": 40},
+    "32b": {**QWEN3_8B, "hidden_size": 5120, "intermediate_size": 25600, "num_hidden_layers": 64, "num_attention_heads": 64},
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -62,9 +68,10 @@ def run_ours(args) -> int:
     from acvram_b200.config import Qwen3Config
     from acvram_b200.models import build_random
 
-    full_layers = QWEN3_8B["num_hidden_layers"]
+    shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
     layers = args.layers or full_layers
-    cfg = Qwen3Config(**{**QWEN3_8B, "num_hidden_layers": layers})
+    cfg = Qwen3Config(**{**shape, "num_hidden_layers": layers})
     t0 = time.time()
     model = build_random(cfg, seed=0, dtype=torch.bfloat16, device="cuda:0")
     torch.cuda.synchronize()
@@ -128,11 +135,11 @@ def run_ours(args) -> int:
         engine.step()
 
     line = {
-        "metric": "decode tok/s at batch 8 (Qwen3-8B shape, 2048-token contexts)",
+        "metric": f"decode tok/s at batch {args.batch} (Qwen3-{args.shape.upper()} shape, {args.context}-token contexts)",
         "value": round(main["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(main["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02)",
-        "config": {"model": "Qwen3-8B shape", "layers": layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": layers, "layers_full": full_layers, "hidden": cfg.hidden_size,
                    "q_heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": args.batch,
                    "seq_len": args.context, "max_model_len": 8192, "page_size": page, "kv_dtype": "bf16",
@@ -160,6 +167,7 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's (named in config)")
+    ap.add_argument("--shape", default="8b", choices=sorted(SHAPES), help="layer sizes (default: Qwen3-8B's)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=2048)
     ap.add_argument("--page-size", type=int, default=16, help="tokens in a page of the cache (the engine's own default is 64)")
