@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch
 
-from .manager import CacheManager, PagedGroup, StateGroup
+from .manager import CacheManager, PagedGroup
 
 
 class CacheStorage:

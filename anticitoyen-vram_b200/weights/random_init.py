@@ -55,7 +55,7 @@ def write_random_model(config, folder: str | os.PathLike, seed: int = 0,
 
     ``config`` is a typed configuration of a registered architecture.  ``dtype``
     is the stored type; float32 files hold the same bfloat16-rounded values."""
-    from ..config import REGISTRY, family_of
+    from ..config import family_of
     from ..models import needs_of_plan
 
     folder = os.fspath(folder)
