@@ -171,7 +171,7 @@ def bench_decode(model, random_weights=False, seed=0, dtype="bfloat16", batches=
     need = max(batches) * (context + n_tokens + 64)
     eng = Engine(model, dtype, max_batch_size=max(batches), max_model_len=context + n_tokens + 64,
                  random_weights=random_weights, seed=seed, device=device, enable_cuda_graphs=cuda_graphs,
-                 page_size=64, num_pages=need // 64 + 2 * max(batches))
+                 page_size=64, num_pages=need // 64 + 2 * max(batches), enable_prefix_cache=False)
     out = {"model": str(model), "dtype": dtype, "context": context, "tokens": n_tokens}
     for b in batches:
         rates = []

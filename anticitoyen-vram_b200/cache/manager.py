@@ -21,14 +21,30 @@ code (acvram/memory/kvcache.py:37), here it is a parameter.
 
 The life of a request's pages follows the reference (pages reserved as the
 request grows, acvram/engine/runner.py:1762-1769; all given back at once when it
-ends, 1771-1803) plus the window rule above.  This file is host-side bookkeeping
-only and imports no torch at module level; ``CacheStorage`` holds the tensors.
+ends, 1771-1803) plus the window rule above.
+
+Prefix reuse, as the reference's allocator has it (reference counts, a chained
+hash over the tokens of each full page, freed-but-known pages kept until their
+room is needed; acvram/memory/kvcache.py:100-165): when a request ends, its full
+pages are *published* under the hash of all tokens up to and including theirs; a
+later request whose tokens begin the same way takes those pages into its block
+table instead of computing them again, and several requests may hold one page.
+Shared pages are never written: a request writes only at positions past what it
+holds.  Reuse is switched on by ``enable_prefix_cache`` and needs every group to
+keep all keys (a window gives pages back as it goes, and a state of fixed size
+has no page to take over).
+
+This file is host-side bookkeeping only and imports no torch at module level;
+``CacheStorage`` holds the tensors.
 """
 
 from __future__ import annotations
 
+import hashlib
+from array import array
+from collections import OrderedDict
 from dataclasses import dataclass, field
-from typing import Hashable
+from typing import Hashable, Sequence
 
 
 class OutOfPages(RuntimeError):
@@ -61,42 +77,100 @@ class StateNeed:
 
 
 class PagePool:
-    """Free list of page numbers ``0 .. num_pages-1``; last freed, first reused."""
+    """Page numbers ``0 .. num_pages-1``, each one free, held (by one or more block tables) or *kept*:
+    held by nobody, but still filled with published content that a later request may take over.
+    Free pages are given out first, last freed first reused; then kept pages, the longest unused first."""
 
     def __init__(self, num_pages: int) -> None:
         if num_pages < 0:
             raise ValueError("num_pages must be >= 0")
         self.num_pages = num_pages
         self._free = list(range(num_pages - 1, -1, -1))
-        self._held = [False] * num_pages
+        self._refs = [0] * num_pages
+        self._key: list[bytes | None] = [None] * num_pages      # the content a page is published under
+        self._index: dict[bytes, int] = {}                      # published content -> page
+        self._kept: OrderedDict[int, None] = OrderedDict()      # published pages that nobody holds, oldest first
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        """Pages that ``allocate`` can give: the free ones and the kept ones."""
+        return len(self._free) + len(self._kept)
+
+    @property
+    def num_kept(self) -> int:
+        return len(self._kept)
 
     def allocate(self, n: int) -> list[int]:
-        if n > len(self._free):
-            raise OutOfPages(f"{n} pages asked, {len(self._free)} free of {self.num_pages}")
-        out = [self._free.pop() for _ in range(n)]
-        for p in out:
-            self._held[p] = True
+        if n > self.num_free:
+            raise OutOfPages(f"{n} pages asked, {self.num_free} free of {self.num_pages}")
+        out = []
+        for _ in range(n):
+            if self._free:
+                p = self._free.pop()
+            else:                               # the room of the page that went unused longest
+                p, _ = self._kept.popitem(last=False)
+                del self._index[self._key[p]]
+                self._key[p] = None
+            self._refs[p] = 1
+            out.append(p)
         return out
 
     def release(self, pages) -> None:
         for p in pages:
-            if not 0 <= p < self.num_pages or not self._held[p]:
+            if not 0 <= p < self.num_pages or self._refs[p] <= 0:
                 raise CacheAccountingError(f"page {p} is released but not held")
-            self._held[p] = False
-            self._free.append(p)
+            self._refs[p] -= 1
+            if self._refs[p] == 0:
+                if self._key[p] is not None:
+                    self._kept[p] = None
+                else:
+                    self._free.append(p)
+
+    # ---- published content
+    def publish(self, page: int, key: bytes) -> None:
+        """``page`` (held) is full of the content named ``key``; a second page of the same content stays unnamed."""
+        if not 0 <= page < self.num_pages or self._refs[page] <= 0:
+            raise CacheAccountingError(f"page {page} is published but not held")
+        if self._key[page] is None and key not in self._index:
+            self._key[page] = key
+            self._index[key] = page
+
+    def lookup(self, key: bytes) -> int | None:
+        return self._index.get(key)
+
+    def is_kept(self, page: int) -> bool:
+        return page in self._kept
+
+    def share(self, page: int) -> None:
+        """One more holder of a published page (held by others, or kept)."""
+        if self._key[page] is None or (self._refs[page] == 0 and page not in self._kept):
+            raise CacheAccountingError(f"page {page} is shared but holds no published content")
+        self._kept.pop(page, None)
+        self._refs[page] += 1
+
+    def holders(self, page: int) -> int:
+        return self._refs[page]
 
     def check(self) -> None:
-        """Every page is either free or held, and none is both or twice free."""
+        """Every page is free, kept or held, and only one of them; the index names published pages only."""
         free = set(self._free)
         if len(free) != len(self._free):
             raise CacheAccountingError("a page is on the free list twice")
         for p in range(self.num_pages):
-            if self._held[p] == (p in free):
-                raise CacheAccountingError(f"page {p} is {'both held and free' if self._held[p] else 'lost'}")
+            states = (p in free) + (p in self._kept) + (self._refs[p] > 0)
+            if states != 1:
+                raise CacheAccountingError(f"page {p} is {'lost' if states == 0 else 'in two states at once'}")
+            if (p in free or p in self._kept) and self._refs[p] != 0:
+                raise CacheAccountingError(f"page {p} is counted as held and is not")
+            if p in self._kept and self._key[p] is None:
+                raise CacheAccountingError(f"page {p} is kept without content")
+            if p in free and self._key[p] is not None:
+                raise CacheAccountingError(f"page {p} is free and still published")
+        for key, p in self._index.items():
+            if self._key[p] != key:
+                raise CacheAccountingError(f"the index names page {p} under content it does not hold")
+        if sum(k is not None for k in self._key) != len(self._index):
+            raise CacheAccountingError("published pages and index entries do not add up")
 
 
 class PagedGroup:
@@ -141,7 +215,31 @@ class PagedGroup:
     def drop(self, request) -> None:
         table = self.tables.pop(request)
         self.first_live.pop(request)
-        self.pool.release([p for p in table if p >= 0])
+        # the last page first: of a chain of kept pages the deepest is then the first to lose its room,
+        # and the pages before it stay reachable
+        self.pool.release([p for p in reversed(table) if p >= 0])
+
+    # ---- prefix reuse
+    def matching(self, keys: Sequence[bytes]) -> list[int]:
+        """The pages published under the leading ``keys``, up to the first that is not there."""
+        pages = []
+        for key in keys:
+            p = self.pool.lookup(key)
+            if p is None:
+                break
+            pages.append(p)
+        return pages
+
+    def adopt(self, request, pages: Sequence[int]) -> None:
+        """A new request's block table begins with published pages."""
+        for p in pages:
+            self.pool.share(p)
+        self.tables[request] = list(pages)
+
+    def publish(self, request, keys: Sequence[bytes]) -> None:
+        for p, key in zip(self.tables[request], keys):
+            if p >= 0:
+                self.pool.publish(p, key)
 
 
 class StateGroup:
@@ -201,7 +299,8 @@ class CachePlan:
 class CacheManager:
     """Pages and state slots of all live requests, for all groups."""
 
-    def __init__(self, plan: CachePlan, page_size: int, num_pages: int | list[int], max_requests: int) -> None:
+    def __init__(self, plan: CachePlan, page_size: int, num_pages: int | list[int], max_requests: int,
+                 enable_prefix_cache: bool = False) -> None:
         if page_size < 1:
             raise ValueError("page_size must be >= 1")
         self.plan = plan
@@ -215,6 +314,42 @@ class CacheManager:
             else:
                 self.groups.append(StateGroup(need, n_slots, max_requests))
         self.lengths: dict[Hashable, int] = {}
+        # pages are taken over only where every group keeps all keys in pages
+        self.prefix_reuse = bool(enable_prefix_cache) and bool(self.groups) and all(
+            isinstance(g, PagedGroup) and g.need.window <= 0 for g in self.groups)
+        self.reused_tokens = 0          # tokens that requests took over instead of computing them
+
+    # ------------------------------------------------------------------ prefix reuse
+    def page_keys(self, tokens: Sequence[int], known: Sequence[bytes] = ()) -> list[bytes]:
+        """One key for each full page of ``tokens``: a hash of all tokens up to the page's end, chained
+        from page to page (the reference chains its hashes the same way, acvram/memory/kvcache.py:153-165).
+        ``known``: the keys of the first pages, from an earlier call with a beginning of the same tokens."""
+        ps = self.page_size
+        keys = list(known[:len(tokens) // ps])
+        parent = keys[-1] if keys else b""
+        for i in range(len(keys), len(tokens) // ps):
+            parent = hashlib.blake2b(parent + array("q", tokens[i * ps:(i + 1) * ps]).tobytes(), digest_size=16).digest()
+            keys.append(parent)
+        return keys
+
+    def reusable(self, keys: Sequence[bytes], num_tokens: int) -> tuple[int, list[int]]:
+        """(tokens, kept pages of each group among them) that a new request of ``num_tokens`` tokens, whose
+        full pages have the ``keys``, would take over.
+
+        At least the last token is left to be computed: its logits are what the request is admitted for."""
+        if not self.prefix_reuse or num_tokens < 2:
+            return 0, [0] * len(self.paged_groups)
+        keys = keys[:(num_tokens - 1) // self.page_size]
+        found = [g.matching(keys) for g in self.paged_groups]
+        n = min(len(f) for f in found)
+        return n * self.page_size, [sum(g.pool.is_kept(p) for p in f[:n]) for g, f in zip(self.paged_groups, found)]
+
+    def can_admit_with(self, keys: Sequence[bytes], num_tokens: int, first: int) -> bool:
+        """Whether the pools hold the first ``first`` new tokens of such a request beside the published
+        pages that it takes over (which leave the kept ones and stop counting as free)."""
+        reuse, kept = self.reusable(keys, num_tokens)
+        return all(g.pages_for(reuse + first) - reuse // self.page_size <= g.pool.num_free - k
+                   for g, k in zip(self.paged_groups, kept))
 
     # ------------------------------------------------------------------ queries
     @property
@@ -249,22 +384,30 @@ class CacheManager:
         return [g.pool.num_free for g in self.paged_groups]
 
     # ------------------------------------------------------------------ life of a request
-    def admit(self, request) -> dict[int, int]:
+    def admit(self, request, keys: Sequence[bytes] = (), num_tokens: int = 0) -> dict[int, int]:
         """Start a request: empty block tables, one state slot in each state group.
 
+        With the ``keys`` of the full pages of the ``num_tokens`` tokens that the request brings (as far
+        as known) and prefix reuse on, the block tables begin with the published pages of the longest
+        known beginning, and the request's length starts there (``lengths[request]``).
         Returns {group index: state slot}; the caller zeroes those slots."""
         if request in self.lengths:
             raise CacheAccountingError(f"request {request!r} is admitted twice")
         if not self.can_admit():
             raise OutOfPages("no room for another request")
         slots = {}
+        reuse, _ = self.reusable(keys, num_tokens)
+        keys = keys[:reuse // self.page_size]
         for gi, g in enumerate(self.groups):
             if isinstance(g, PagedGroup):
                 g.tables[request] = []
                 g.first_live[request] = 0
+                if keys:
+                    g.adopt(request, g.matching(keys))
             else:
                 slots[gi] = g.take(request)
-        self.lengths[request] = 0
+        self.lengths[request] = reuse
+        self.reused_tokens += reuse
         return slots
 
     def grow(self, request, length: int) -> None:
@@ -288,9 +431,15 @@ class CacheManager:
         """After a step: release what every window has passed.  Returns pages freed."""
         return sum(g.trim(request, self.lengths[request]) for g in self.paged_groups)
 
-    def release(self, request) -> None:
+    def release(self, request, keys: Sequence[bytes] = ()) -> None:
+        """Give back what the request holds.  With the ``keys`` of the full pages of its tokens (from
+        position 0) and prefix reuse on, the full pages that it holds are published first."""
         if request not in self.lengths:
             raise CacheAccountingError(f"request {request!r} is released but not live")
+        if keys and self.prefix_reuse:
+            keys = keys[:self.lengths[request] // self.page_size]
+            for g in self.paged_groups:
+                g.publish(request, keys)
         for g in self.groups:
             if isinstance(g, PagedGroup):
                 g.drop(request)
@@ -308,9 +457,18 @@ class CacheManager:
     def check(self) -> None:
         for g in self.paged_groups:
             g.pool.check()
-            held = [p for table in g.tables.values() for p in table if p >= 0]
-            if len(held) != len(set(held)):
-                raise CacheAccountingError("a page is in two block tables")
+            held: dict[int, int] = {}
+            for table in g.tables.values():
+                if len([p for p in table if p >= 0]) != len({p for p in table if p >= 0}):
+                    raise CacheAccountingError("a page is in one block table twice")
+                for p in table:
+                    if p >= 0:
+                        held[p] = held.get(p, 0) + 1
+            for p, n in held.items():
+                if g.pool.holders(p) != n:
+                    raise CacheAccountingError(f"page {p} is in {n} block tables and counted {g.pool.holders(p)} times")
+                if n > 1 and not self.prefix_reuse:
+                    raise CacheAccountingError("a page is in two block tables")
             if len(held) + g.pool.num_free != g.pool.num_pages:
                 raise CacheAccountingError("held + free pages do not add up to the pool")
         for g in self.state_groups:

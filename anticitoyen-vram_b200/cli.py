@@ -32,6 +32,8 @@ def _engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--token-budget", type=int, default=2048, help="most tokens that one step runs")
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--no-cuda-graphs", action="store_true")
+    p.add_argument("--no-prefix-cache", action="store_true",
+                   help="compute every prompt from its first token (default: full pages of finished requests are taken over)")
 
 
 def _make_engine(args):
@@ -39,7 +41,7 @@ def _make_engine(args):
     return Engine(args.model, args.dtype, max_batch_size=args.max_batch, max_model_len=args.max_model_len,
                   page_size=args.page_size, num_pages=args.num_pages, token_budget=args.token_budget,
                   random_weights=args.random_weights, seed=args.seed, device=args.device,
-                  enable_cuda_graphs=not args.no_cuda_graphs)
+                  enable_cuda_graphs=not args.no_cuda_graphs, enable_prefix_cache=not args.no_prefix_cache)
 
 
 def cmd_generate(args) -> int:

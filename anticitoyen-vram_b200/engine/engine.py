@@ -50,6 +50,7 @@ class EngineStats:
     preempted: int = 0
     refused: int = 0
     truncated: int = 0
+    reused_tokens: int = 0       # prompt tokens taken over from published pages instead of being computed
     extra: dict = field(default_factory=dict)
 
     def to_dict(self) -> dict:
@@ -80,9 +81,12 @@ class Engine:
     def __init__(self, model, dtype="bfloat16", *, max_batch_size: int = 16, max_model_len: int = 8192,
                  page_size: int = 64, num_pages: int | None = None, token_budget: int = 2048,
                  random_weights: bool = False, seed: int = 0, device: str = "cuda:0",
-                 enable_cuda_graphs: bool = True, run_ahead: bool = True, tokenizer=None) -> None:
+                 enable_cuda_graphs: bool = True, run_ahead: bool = True, enable_prefix_cache: bool = True,
+                 tokenizer=None) -> None:
         """``model``: a folder with config.json and model.safetensors, or (with
-        ``random_weights``) a typed configuration or a folder whose config.json alone is read."""
+        ``random_weights``) a typed configuration or a folder whose config.json alone is read.
+        ``enable_prefix_cache`` (the reference's name and default, acvram/engine/runner.py:689-694): the full
+        pages of a finished request stay known, and a later request that begins the same way takes them over."""
         from ..config import load_config
         from ..models import build_from_folder, build_random
 
@@ -102,7 +106,7 @@ class Engine:
         self.page_size = page_size
         if num_pages is None:
             num_pages = self._default_pages(max_batch_size, device)
-        self.runner = ModelRunner(self.model, page_size, num_pages, max_batch_size)
+        self.runner = ModelRunner(self.model, page_size, num_pages, max_batch_size, enable_prefix_cache)
         self.scheduler = Scheduler(self.runner.manager, max_batch_size, token_budget, self.max_model_len)
         self.sampler = Sampler(device)
         self.tokenizer = tokenizer
@@ -175,6 +179,7 @@ class Engine:
         self.stats.preempted += len(plan.preempted)
         self.stats.refused += len(plan.refused)
         self.stats.truncated += len(plan.truncated)
+        self.stats.reused_tokens = self.scheduler.counters["reused_tokens"]
         if not plan.entries:
             return outputs
         flight = self._launch(plan, None)

@@ -19,13 +19,14 @@ from .batch import BatchBuilder, StepContext, StepEntry
 
 
 class ModelRunner:
-    def __init__(self, model, page_size: int, num_pages: int, max_requests: int) -> None:
+    def __init__(self, model, page_size: int, num_pages: int, max_requests: int,
+                 enable_prefix_cache: bool = False) -> None:
         if model.rt is None:
             raise ValueError("the model has no weights loaded")
         rt: Runtime = model.rt
         self.model = model
         self.rt = rt
-        self.manager = CacheManager(model.cache_plan(), page_size, num_pages, max_requests)
+        self.manager = CacheManager(model.cache_plan(), page_size, num_pages, max_requests, enable_prefix_cache)
         self.storage = CacheStorage(self.manager, rt.device, rt.dtype)
         self.builder = BatchBuilder(self.manager, rt.device, model.plan.vocab_size, model.plan.max_positions)
         self.steps = 0

@@ -46,6 +46,8 @@ class Request:
     finish_reason: str | None = None
     preemptions: int = 0
     logprob_sum: float = 0.0
+    reused: int = 0              # tokens taken over from published pages at the last admission
+    page_keys: list = field(default_factory=list, repr=False)   # keys of the full pages of ``tokens``, as far as made
 
     @property
     def tokens(self) -> list[int]:
@@ -87,7 +89,7 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self._order = itertools.count()
-        self.counters = {"preempted": 0, "refused": 0, "truncated": 0, "admitted": 0}
+        self.counters = {"preempted": 0, "refused": 0, "truncated": 0, "admitted": 0, "reused_tokens": 0}
 
     # ------------------------------------------------------------------ queue
     def add(self, request: Request) -> None:
@@ -159,11 +161,16 @@ class Scheduler:
                 plan.refused.append(r)
                 self.counters["refused"] += 1
                 continue
-            first = min(r.remaining, budget)
-            if not self._pool_holds_new(first):
+            keys = self._keys(r)
+            n_tokens = len(r.prompt) + len(r.output)
+            reuse, _ = m.reusable(keys, n_tokens)
+            first = min(n_tokens - reuse, budget)
+            if not m.can_admit_with(keys, n_tokens, first):
                 break                                # stays waiting until pages come back
             self.waiting.popleft()
-            m.admit(r.request_id)
+            m.admit(r.request_id, keys, n_tokens)
+            r.computed = r.reused = m.lengths[r.request_id]     # published pages of the same beginning, taken over
+            self.counters["reused_tokens"] += r.reused
             r.admitted_at = next(self._order)
             self.running.append(r)
             self.counters["admitted"] += 1
@@ -231,8 +238,11 @@ class Scheduler:
         plan.truncated = earlier.truncated + plan.truncated
         return plan
 
-    def _pool_holds_new(self, count: int) -> bool:
-        return all(g.pages_for(count) <= g.pool.num_free for g in self.manager.paged_groups)
+    def _keys(self, r: Request) -> list:
+        """Keys of the full pages of the request's tokens (made once, continued as the tokens grow)."""
+        if self.manager.prefix_reuse:
+            r.page_keys = self.manager.page_keys(r.tokens, r.page_keys)
+        return r.page_keys
 
     def _plan_portion(self, r: Request, budget: int, plan: StepPlan) -> int:
         """Give ``r`` as many of its remaining tokens as budget and free pages allow."""
@@ -282,11 +292,11 @@ class Scheduler:
         r.finished, r.finish_reason = True, reason
         if r in self.running:
             self.running.remove(r)
-            self.manager.release(r.request_id)
+            self.manager.release(r.request_id, self._keys(r))
 
     def _preempt(self, r: Request, plan: StepPlan) -> None:
         self.running.remove(r)
-        self.manager.release(r.request_id)
+        self.manager.release(r.request_id, self._keys(r))
         plan.entries = [e for e in plan.entries if e.request is not r]
         r.computed = 0
         r.admitted_at = -1

@@ -83,7 +83,8 @@ def run_ours(args) -> int:
     max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
     num_pages = max_batch * ((per_request + page - 1) // page) + 8 + (2048 + page) // page
     engine = Engine(model, "bfloat16", max_batch_size=max_batch, max_model_len=8192, page_size=page,
-                    num_pages=num_pages, token_budget=4096, enable_cuda_graphs=not args.no_cuda_graphs)
+                    num_pages=num_pages, token_budget=4096, enable_cuda_graphs=not args.no_cuda_graphs,
+                    enable_prefix_cache=False)     # every prompt is computed: no number rests on pages taken over
     runner = engine.runner
     pk, pk_src = peaks()
 

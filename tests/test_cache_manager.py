@@ -151,3 +151,151 @@ def test_random_orders_of_requests(seed):
     m.check()
     assert all(g.pool.num_free == g.pool.num_pages for g in m.paged_groups)
     assert all(g.num_free == g.max_requests for g in m.state_groups)
+
+
+# --------------------------------------------------------------------------- prefix reuse
+def reuse_manager(num_pages=12, page=4, max_requests=4, layers=2):
+    return CacheManager(CachePlan([PagedNeed(2, 16, 0)] * layers), page, num_pages, max_requests, enable_prefix_cache=True)
+
+
+def run_request(m, name, tokens, upto=None):
+    """Admit ``name`` with ``tokens``, hold positions [0, upto); returns how many tokens it took over."""
+    keys = m.page_keys(tokens)
+    m.admit(name, keys, len(tokens))
+    reused = m.lengths[name]
+    upto = len(tokens) if upto is None else upto
+    m.grow(name, upto)
+    m.advance(name, upto)
+    return reused
+
+
+def test_a_finished_request_leaves_its_full_pages_to_the_next_with_the_same_beginning():
+    m = reuse_manager()
+    a = list(range(100, 111))                       # 11 tokens: two full pages and three tokens
+    assert run_request(m, "a", a) == 0
+    table_a = list(m.block_table("a", 0))
+    m.release("a", m.page_keys(a))
+    assert m.free_pages() == [12] and m.paged_groups[0].pool.num_kept == 2
+    m.check()
+    b = a[:9] + [7, 8, 9]                           # the same two pages, then something else
+    assert run_request(m, "b", b) == 8
+    assert m.block_table("b", 0)[:2] == table_a[:2] and m.block_table("b", 0)[2] not in table_a[:2]
+    assert m.reused_tokens == 8
+    m.check()
+    c = a[:4] + [1, 2, 3, 4, 5]                     # only the first page is the same
+    assert run_request(m, "c", c) == 4
+    assert m.block_table("c", 0)[0] == table_a[0] and m.paged_groups[0].pool.holders(table_a[0]) == 2
+    m.check()
+    m.release("b", m.page_keys(b))
+    assert m.paged_groups[0].pool.holders(table_a[0]) == 1, "c still holds the first page"
+    m.release("c", m.page_keys(c))
+    m.check()
+    assert m.free_pages() == [12]
+
+
+def test_the_last_token_of_a_known_prompt_is_still_computed():
+    m = reuse_manager()
+    a = list(range(8))                              # exactly two pages
+    run_request(m, "a", a)
+    m.release("a", m.page_keys(a))
+    assert run_request(m, "b", list(a)) == 4, "the second page holds the last token: it is computed again"
+    assert run_request(m, "c", a + [99]) == 8
+    m.check()
+
+
+def test_kept_pages_give_way_when_room_is_needed_the_deepest_first():
+    m = reuse_manager(num_pages=4)
+    a = list(range(12))
+    run_request(m, "a", a)
+    m.release("a", m.page_keys(a))
+    pool = m.paged_groups[0].pool
+    assert pool.num_kept == 3 and m.free_pages() == [4]
+    m.admit("x")
+    m.grow("x", 8)                                  # the free page, then the room of a's third page
+    m.advance("x", 8)
+    assert pool.num_kept == 2
+    keys = m.page_keys(a + [1])
+    assert m.reusable(keys, 13)[0] == 8, "the first two pages of a are still known"
+    m.grow("x", 16)
+    m.advance("x", 16)
+    assert pool.num_kept == 0 and m.reusable(keys, 13)[0] == 0
+    with pytest.raises(OutOfPages):
+        m.grow("x", 17)
+    m.check()
+    m.release("x")
+    assert m.free_pages() == [4] and pool.num_kept == 0, "pages released without tokens are not published"
+    m.check()
+
+
+def test_admission_counts_the_kept_pages_it_takes_over():
+    m = reuse_manager(num_pages=4)
+    a = list(range(12))
+    run_request(m, "a", a)
+    m.release("a", m.page_keys(a))                  # 3 kept, 1 free
+    keys = m.page_keys(a + [50, 51, 52, 53, 54])
+    # taking the three kept pages over leaves one page: room for up to 4 new tokens
+    assert m.can_admit_with(keys, 17, 4) and not m.can_admit_with(keys, 17, 5)
+    other = m.page_keys(list(range(200, 217)))
+    assert m.can_admit_with(other, 17, 16) and not m.can_admit_with(other, 17, 17)
+
+
+def test_reuse_is_off_for_windows_and_states_and_by_default():
+    assert not manager().prefix_reuse
+    plan = CachePlan([PagedNeed(2, 16, 0), PagedNeed(2, 16, 6)])
+    assert not CacheManager(plan, 4, 8, 2, enable_prefix_cache=True).prefix_reuse
+    plan = CachePlan([PagedNeed(2, 16, 0), StateNeed((3,))])
+    assert not CacheManager(plan, 4, 8, 2, enable_prefix_cache=True).prefix_reuse
+    m = manager()
+    a = list(range(9))
+    m.admit("a", m.page_keys(a), 9)
+    m.grow("a", 9); m.advance("a", 9)
+    m.release("a", m.page_keys(a))
+    assert m.paged_groups[0].pool.num_kept == 0
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_orders_with_shared_beginnings(seed):
+    """Requests whose tokens begin alike come and go at random; a page taken over always holds the
+    tokens of the request that takes it (checked against a shadow of what was written where)."""
+    rng = random.Random(seed)
+    page = 4
+    m = reuse_manager(num_pages=14, page=page, max_requests=4)
+    stems = [[rng.randrange(50) for _ in range(24)] for _ in range(3)]
+    written: dict[int, tuple] = {}                  # page -> the tokens from position 0 to the page's end
+    live: dict[int, tuple[list, int]] = {}
+    next_id = 0
+    for _ in range(500):
+        action = rng.random()
+        if action < 0.3 and m.can_admit():
+            stem = rng.choice(stems)
+            tokens = stem[:rng.randrange(1, 24)] + [rng.randrange(50, 99) for _ in range(rng.randrange(0, 9))]
+            keys = m.page_keys(tokens)
+            if m.can_admit_with(keys, len(tokens), 1):
+                m.admit(next_id, keys, len(tokens))
+                have = m.lengths[next_id]
+                assert have % page == 0 and have < len(tokens)
+                for i, p in enumerate(m.block_table(next_id, 0)):
+                    assert written[p] == tuple(tokens[:(i + 1) * page]), "a page taken over holds other tokens"
+                live[next_id] = (tokens, have)
+                next_id += 1
+        elif action < 0.8 and live:
+            r = rng.choice(list(live))
+            tokens, have = live[r]
+            n = min(len(tokens), have + rng.choice([1, 2, 5, 9]))
+            if n > have and m.can_grow(r, n):
+                m.grow(r, n)
+                m.advance(r, n)
+                table = m.block_table(r, 0)
+                for i in range(have // page, (n - 1) // page + 1):
+                    assert m.paged_groups[0].pool.holders(table[i]) == 1, "a shared page is written"
+                    written[table[i]] = tuple(tokens[:min(n, (i + 1) * page)])
+                live[r] = (tokens, n)
+        elif live:
+            r = rng.choice(list(live))
+            tokens, have = live.pop(r)
+            m.release(r, m.page_keys(tokens) if rng.random() < 0.8 else ())
+        m.check()
+    for r, (tokens, _) in live.items():
+        m.release(r, m.page_keys(tokens))
+    m.check()
+    assert m.free_pages() == [14] and m.reused_tokens > 0

@@ -236,3 +236,40 @@ def test_random_traffic_gives_the_same_tokens_one_step_ahead_or_not(tiny_folders
         assert all(reason is not None for _, reason in a.values())
         preempted += pa + pb
     assert preempted > 0       # the small pools did make requests give way
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pages_taken_over_change_no_token(tiny_folders, plain_models, dtype):
+    """Prefix reuse: a prompt seen before, prompts that begin like it (one of them cut inside a page), and a
+    pool so small that kept pages lose their room on the way.  What a request generates is what it would have
+    generated alone: in float32 the plain implementation's tokens, in bfloat16 near-best choices of its logits."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["B"]
+    vocab = cfg["vocab_size"]
+    base = random_ids(vocab, 50, 77)
+    prompts = [base, list(base), base[:40] + random_ids(vocab, 21, 78), base[:33], random_ids(vocab, 30, 79), list(base)]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    eng = engine_for(tiny_folders["B"], dtype, page_size=8, num_pages=14, max_model_len=128)
+    reused, outs = [], []
+    for p in prompts:                   # one after the other: each finds what the earlier ones left
+        outs.append(eng.generate_batch([p], sp)[0])
+        reused.append(eng.stats.reused_tokens - sum(reused))
+        eng.runner.manager.check()
+    assert reused[0] == 0 and reused[1] == 48 and reused[2] == 40 and reused[3] == 32 and reused[4] == 0
+    assert eng.runner.manager.free_pages() == [14] and eng.runner.manager.paged_groups[0].pool.num_kept > 0
+    for p, g in zip(prompts, outs):
+        if dtype == "float32":
+            assert g == plain_qwen3.greedy_generate(cfg, t, p, 10)
+        else:
+            logits = plain_qwen3.forward_logits(cfg, t, p + g)
+            yard = float((logits - plain_qwen3.forward_logits(cfg, t, p + g, torch.bfloat16)).abs().max())
+            for n, tok in enumerate(g):
+                row = logits[len(p) - 1 + n]
+                assert float(row.max() - row[tok]) <= 3 * yard, f"token {n} is not a near-best choice"
+    # the same requests all at once, and without reuse: the same tokens in float32
+    if dtype == "float32":
+        for cache in (True, False):
+            eng2 = engine_for(tiny_folders["B"], dtype, page_size=8, num_pages=64, max_model_len=128,
+                              enable_prefix_cache=cache)
+            assert eng2.generate_batch(prompts, sp) == outs
+            assert eng2.stats.reused_tokens == 0 or cache

@@ -253,3 +253,72 @@ def test_ahead_counts_the_pages_of_all_requests_together():
     assert free == [3]
     m.paged_groups[0].pool.allocate(2)          # somebody else's pages: one page left for two requests that both need one
     assert s.schedule_ahead(prev) is None and m.free_pages() == [1]
+
+
+# --------------------------------------------------------------------------- prefix reuse
+def make_reuse(num_pages=16, page=4, max_batch=4, budget=16, max_len=256):
+    m = CacheManager(CachePlan([PagedNeed(1, 8, 0)] * 2), page, num_pages, max_batch, enable_prefix_cache=True)
+    return m, Scheduler(m, max_batch, budget, max_len)
+
+
+def test_a_prompt_seen_before_starts_behind_its_known_pages():
+    m, s = make_reuse(budget=64, num_pages=32)
+    s.add(req(0, 22, max_tokens=3))
+    while not s.idle:
+        run_step(m, s)
+    # r0 held 22 prompt tokens and fed two of its three tokens: 24 tokens in six full pages
+    assert m.paged_groups[0].pool.num_kept == 6 and m.free_pages() == [32]
+    r1 = req(1, 22, max_tokens=2)
+    s.add(r1)
+    plan = run_step(m, s)
+    assert [(e.start, e.count, e.samples) for e in plan.entries] == [(20, 2, True)], "five pages taken over, two tokens run"
+    assert r1.reused == 20 and s.counters["reused_tokens"] == 20
+    r2 = Request("r2", list(range(1, 11)) + [90, 91, 92], SamplingParams(temperature=0.0, max_tokens=2))
+    s.add(r2)
+    plan = run_step(m, s)
+    assert [(e.request.request_id, e.start, e.count) for e in plan.entries] == [("r1", 22, 1), ("r2", 8, 5)]
+    while not s.idle:
+        run_step(m, s)
+    assert m.free_pages() == [32]
+
+
+def test_a_preempted_request_takes_its_own_pages_back():
+    m, s = make_reuse(num_pages=6, page=4, budget=32)
+    a, b = req(0, 7, max_tokens=12), req(1, 7, max_tokens=12)
+    s.add(a)
+    s.add(b)
+    run_step(m, s)                      # both prompts: 2 pages each
+    plan = None
+    for _ in range(8):
+        plan = run_step(m, s)
+        if plan.preempted:
+            break
+    assert plan is not None and plan.preempted == [b]
+    done = len(b.tokens)
+    while not a.finished:
+        run_step(m, s)
+    while b.admitted_at < 0:
+        run_step(m, s)
+    assert b.reused >= (done - 1) // 4 * 4 - 4 and b.reused > 0, "its published pages were still there"
+    while not s.idle:
+        run_step(m, s)
+    assert len(a.output) == 12 and len(b.output) == 12 and m.free_pages() == [6]
+
+
+def test_random_traffic_with_shared_beginnings_keeps_the_books():
+    rng = random.Random(3)
+    m, s = make_reuse(num_pages=20, page=4, max_batch=4, budget=12, max_len=64)
+    stems = [[rng.randrange(1, 40) for _ in range(20)] for _ in range(2)]
+    reqs = []
+    for i in range(60):
+        if rng.random() < 0.5 and len(s.waiting) < 3:
+            prompt = rng.choice(stems)[:rng.randrange(1, 20)] + [rng.randrange(40, 60) for _ in range(rng.randrange(0, 4))]
+            r = Request(f"q{i}", prompt, SamplingParams(temperature=0.0, max_tokens=rng.randrange(1, 9)))
+            reqs.append(r)
+            s.add(r)
+        run_step(m, s, token=rng.randrange(1, 40))
+    while not s.idle:
+        run_step(m, s, token=rng.randrange(1, 40))
+    assert all(r.finished for r in reqs) and m.free_pages() == [20]
+    assert all(len(r.output) == r.params.max_tokens for r in reqs if r.finish_reason == "length")
+    assert s.counters["reused_tokens"] > 0
