@@ -40,16 +40,30 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 
 
 def peaks() -> tuple[dict, str]:
+    """The roofline's denominators: MEASURED_PEAKS.json beside this file where it exists (its keys are looked
+    for at any depth), else the fallback figures."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    found: dict = {}
+
+    def walk(node) -> None:
+        if isinstance(node, dict):
+            for k, v in node.items():
+                if k in FALLBACK_PEAKS and isinstance(v, (int, float)) and not isinstance(v, bool) and v > 0:
+                    found.setdefault(k, float(v))
+                else:
+                    walk(v)
+        elif isinstance(node, list):
+            for v in node:
+                walk(v)
+
     if os.path.isfile(path):
         try:
             with open(path) as fh:
-                got = json.load(fh)
-            out = dict(FALLBACK_PEAKS)
-            out.update({k: float(v) for k, v in got.items() if k in out and isinstance(v, (int, float))})
-            return out, "measured"
+                walk(json.load(fh))
         except (OSError, ValueError):
-            pass
+            found = {}
+    if "hbm_gbs" in found and "bf16_tflops" in found:
+        return {**FALLBACK_PEAKS, **found}, "measured"
     return dict(FALLBACK_PEAKS), "fallback"
 
 
@@ -152,7 +166,7 @@ def run_ours(args) -> int:
                 "d2h_bytes_per_step": 4 * args.batch},
         "gpu_launches": main["launches"],
         "prefill": {"value": round(pre["tokens_per_s"], 1), "tokens": 2048, "ms": round(pre["ms"], 3),
-                    "frac": round(pre_frac, 4)},
+                    "frac": round(pre_frac, 4), "peak_tflops": pk["bf16_tflops"], "peaks": pk_src},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk_src},
         "points": points,
