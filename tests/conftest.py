@@ -56,11 +56,15 @@ def tiny_config(which: str):
         return Qwen3Config(vocab_size=512, hidden_size=256, intermediate_size=384, num_hidden_layers=2,
                            num_attention_heads=4, num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6,
                            rope_theta=1000000.0, max_position_embeddings=1024, tie_word_embeddings=False)
+    if which == "R":  # two layers of the real sizes of Qwen3-8B (the vocabulary alone is small): what serving tiles and splits
+        return Qwen3Config(vocab_size=2048, hidden_size=4096, intermediate_size=12288, num_hidden_layers=2,
+                           num_attention_heads=32, num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6,
+                           rope_theta=1000000.0, max_position_embeddings=2048, tie_word_embeddings=False)
     raise KeyError(which)
 
 
-TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5}
-TINY_PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16, "F": 64}
+TINY_SEEDS = {"A": 0, "B": 1, "C": 2, "D": 3, "E": 4, "F": 5, "R": 6}
+TINY_PAGE = {"A": 16, "B": 8, "C": 16, "D": 16, "E": 16, "F": 64, "R": 64}
 
 
 @pytest.fixture(scope="session")

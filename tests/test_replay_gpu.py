@@ -143,7 +143,7 @@ def run_trace(folder: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int,
 
 def requests_for(name: str, vocab: int) -> dict[str, list[int]]:
     lengths = {"A": [5, 17, 33, 70, 130], "B": [1, 9, 40, 130, 75], "C": [3, 64, 97, 250], "D": [2, 65, 129, 200, 31], "E": [4, 37, 90],
-               "F": [3, 66, 131, 300, 129]}[name]
+               "F": [3, 66, 131, 300, 129], "R": [3, 200, 513, 140, 66]}[name]
     return {str(i): random_ids(vocab, n, seed=100 + i) for i, n in enumerate(lengths)}
 
 
@@ -218,6 +218,36 @@ def test_replay_bfloat16(name, page, tiny_folders, plain_logits, tmp_path):
         if rid[0] != "w":
             d = float(np.abs(row - whole[rid[1:] + f":{pos}"]).max())
             assert d <= 2.5 * yard, f"{modes[rid[0]]} differs from whole by {d:.3e} at {rid[1:]}/{pos}"
+
+
+@pytest.fixture(scope="module")
+def real_size_model(tmp_path_factory):
+    """Two layers with the layer sizes of Qwen3-8B: (folder, config dict, float32 tensors of the plain implementation)."""
+    from acvram_b200.weights import write_random_model
+    from conftest import TINY_SEEDS, tiny_config
+    folder = str(tmp_path_factory.mktemp("real_sizes"))
+    write_random_model(tiny_config("R"), folder, TINY_SEEDS["R"])
+    return (folder, *plain_qwen3.read_folder(folder))
+
+
+@pytest.mark.parametrize("dtype,page", [("float32", None), ("bfloat16", None), ("bfloat16", 64)])
+def test_replay_at_real_layer_sizes(dtype, page, real_size_model, tmp_path):
+    """The four ways of cutting at the layer sizes that serving runs (hidden 4096, 32 query heads on 8 of 128,
+    intermediate 12288): the products' tile and split choices, the attention over several tiles of keys."""
+    folder, cfg, t = real_size_model
+    tr, reqs, modes = build_full_trace("R", cfg["vocab_size"])
+    got = run_trace(folder, dtype, tr, str(tmp_path), tr.live_peak, page)
+    ref = {rid: plain_qwen3.forward_logits(cfg, t, ids).numpy() for rid, ids in reqs.items()}
+    assert len(got) == 5 * sum(len(v) for v in reqs.values())
+    report = worst(got, ref, modes)
+    if dtype == "float32":
+        scale = max(float(np.abs(v).max()) for v in ref.values())
+        bound = 2e-5 * max(1.0, scale)
+    else:
+        ref16 = {rid: plain_qwen3.forward_logits(cfg, t, ids, torch.bfloat16).numpy() for rid, ids in reqs.items()}
+        bound = 2.5 * max(float(np.abs(ref16[r] - ref[r]).max()) for r in ref)
+    for mode, (d, where) in report.items():
+        assert d <= bound, f"{mode}: max |logit - plain| = {d:.3e} at request/position {where} (bound {bound:.3e})"
 
 
 def test_replay_pages_are_reused(tiny_folders):
