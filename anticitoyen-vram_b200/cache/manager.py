@@ -431,6 +431,15 @@ class CacheManager:
         """After a step: release what every window has passed.  Returns pages freed."""
         return sum(g.trim(request, self.lengths[request]) for g in self.paged_groups)
 
+    def publish(self, request, keys: Sequence[bytes], num_tokens: int) -> None:
+        """The request's pages that positions [0, num_tokens) fill become known under ``keys`` while the
+        request goes on (it never writes them again), so that requests admitted meanwhile can take them over."""
+        if not self.prefix_reuse:
+            return
+        keys = keys[:min(num_tokens, self.lengths[request]) // self.page_size]
+        for g in self.paged_groups:
+            g.publish(request, keys)
+
     def release(self, request, keys: Sequence[bytes] = ()) -> None:
         """Give back what the request holds.  With the ``keys`` of the full pages of its tokens (from
         position 0) and prefix reuse on, the full pages that it holds are published first."""

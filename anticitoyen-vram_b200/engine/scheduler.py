@@ -48,6 +48,7 @@ class Request:
     logprob_sum: float = 0.0
     reused: int = 0              # tokens taken over from published pages at the last admission
     page_keys: list = field(default_factory=list, repr=False)   # keys of the full pages of ``tokens``, as far as made
+    published: int = 0           # pages of this admission that are already known to later requests
 
     @property
     def tokens(self) -> list[int]:
@@ -170,6 +171,7 @@ class Scheduler:
             self.waiting.popleft()
             m.admit(r.request_id, keys, n_tokens)
             r.computed = r.reused = m.lengths[r.request_id]     # published pages of the same beginning, taken over
+            r.published = r.reused // m.page_size
             self.counters["reused_tokens"] += r.reused
             r.admitted_at = next(self._order)
             self.running.append(r)
@@ -264,6 +266,7 @@ class Scheduler:
         in order.  Returns the requests that got a token (finished ones included)."""
         it = iter(sampled)
         touched = []
+        m = self.manager
         for e in plan.entries:
             r = e.request
             if r.finished:          # stopped (or aborted) after this step was planned ahead: its token is dropped
@@ -271,6 +274,10 @@ class Scheduler:
                     next(it, None)
                 continue
             r.computed = e.start + e.count
+            if m.prefix_reuse and r.computed // m.page_size > r.published:
+                # a page of this request has become full: it is known from now on, not only when the request ends
+                m.publish(r.request_id, self._keys(r), r.computed)
+                r.published = r.computed // m.page_size
             if not e.samples:
                 continue
             tok = int(next(it))

@@ -322,3 +322,19 @@ def test_random_traffic_with_shared_beginnings_keeps_the_books():
     assert all(r.finished for r in reqs) and m.free_pages() == [20]
     assert all(len(r.output) == r.params.max_tokens for r in reqs if r.finish_reason == "length")
     assert s.counters["reused_tokens"] > 0
+
+
+def test_full_pages_are_known_while_their_request_still_runs():
+    m, s = make_reuse(budget=12, num_pages=32)
+    a = req(0, 21, max_tokens=8)
+    s.add(a)
+    run_step(m, s)                                  # 12 of a's 21 prompt tokens: three pages, known at once
+    b = req(1, 21, max_tokens=2)
+    s.add(b)
+    plan = run_step(m, s)                           # a's last 9 tokens; b takes a's three pages and runs 3 tokens
+    assert [(e.request.request_id, e.start, e.count) for e in plan.entries] == [("r0", 12, 9), ("r1", 12, 3)]
+    assert b.reused == 12 and m.block_table("r1", 0)[:3] == m.block_table("r0", 0)[:3]
+    assert m.paged_groups[0].pool.holders(m.block_table("r0", 0)[0]) == 2
+    while not s.idle:
+        run_step(m, s)
+    assert len(a.output) == 8 and len(b.output) == 2 and m.free_pages() == [32]
