@@ -216,7 +216,7 @@ class Engine:
                     a = b
             entries = [StepEntry(e.request.request_id, [0], (0,)) for e in plan.entries]
         else:
-            entries = [StepEntry(e.request.request_id, e.request.tokens[e.start:e.start + e.count],
+            entries = [StepEntry(e.request.request_id, e.request.token_slice(e.start, e.count),
                                  (e.count - 1,) if e.samples else ()) for e in plan.entries]
         logits = self.runner.step(entries, device_tokens=device_tokens)
         rows = [e.request for e in plan.entries if e.samples]

@@ -55,8 +55,21 @@ class Request:
         return self.prompt + self.output
 
     @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output)
+
+    @property
     def remaining(self) -> int:
         return len(self.prompt) + len(self.output) - self.computed
+
+    def token_slice(self, start: int, count: int) -> list[int]:
+        """tokens[start : start + count] without putting prompt and output together first."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output[:start + count - n]
 
 
 @dataclass
@@ -156,14 +169,14 @@ class Scheduler:
         # 3. new requests, first come first served
         while self.waiting and budget > 0 and len(self.running) < self.max_batch_size and m.can_admit():
             r = self.waiting[0]
-            if not m.fits_empty_pool(len(r.tokens) + 1):
+            if not m.fits_empty_pool(r.num_tokens + 1):
                 self.waiting.popleft()
                 r.finished, r.finish_reason = True, "refused"
                 plan.refused.append(r)
                 self.counters["refused"] += 1
                 continue
             keys = self._keys(r)
-            n_tokens = len(r.prompt) + len(r.output)
+            n_tokens = r.num_tokens
             reuse, _ = m.reusable(keys, n_tokens)
             first = min(n_tokens - reuse, budget)
             if not m.can_admit_with(keys, n_tokens, first):
