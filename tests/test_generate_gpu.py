@@ -273,3 +273,33 @@ def test_pages_taken_over_change_no_token(tiny_folders, plain_models, dtype):
                               enable_prefix_cache=cache)
             assert eng2.generate_batch(prompts, sp) == outs
             assert eng2.stats.reused_tokens == 0 or cache
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_abort_between_steps_frees_everything_and_leaves_the_others_alone(tiny_folders, plain_models, ahead):
+    """A request is aborted while it decodes (with the engine one step ahead: while a step that holds its token is
+    unread), another while it still waits: their pages come back at once, nothing more is delivered for them, and
+    the requests beside them get the tokens they would have got alone."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["A"]
+    prompts = [random_ids(cfg["vocab_size"], n, 400 + n) for n in (20, 33, 7, 50, 12)]
+    sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True)
+    eng = engine_for(tiny_folders["A"], run_ahead=ahead, max_batch_size=3, num_pages=24)
+    ids = [eng.add_request(p, sp, request_id=f"q{i}") for i, p in enumerate(prompts)]
+    got = {i: [] for i in ids}
+    after_abort = {}
+    step = 0
+    while not eng.idle:
+        if step == 6:
+            eng.abort("q1")                     # decoding
+            eng.abort("q4")                     # still waiting: three requests are live at most
+            after_abort = {k: len(v) for k, v in got.items()}
+        for o in eng.step():
+            got[o.request_id].extend(o.token_ids)
+        step += 1
+        assert step < 500
+    assert len(got["q1"]) == after_abort["q1"] < 24 and got["q4"] == []
+    for i in (0, 2, 3):
+        assert got[f"q{i}"] == plain_qwen3.greedy_generate(cfg, t, prompts[i], 24)
+    eng.runner.manager.check()
+    assert eng.runner.manager.free_pages() == [24]
