@@ -33,7 +33,7 @@ def _engine_args(p: argparse.ArgumentParser) -> None:
     p.add_argument("--device", default="cuda:0")
     p.add_argument("--no-cuda-graphs", action="store_true")
     p.add_argument("--no-prefix-cache", action="store_true",
-                   help="compute every prompt from its first token (default: full pages of finished requests are taken over)")
+                   help="compute every prompt from its first token (default: full pages of earlier requests are taken over)")
 
 
 def _make_engine(args):
