@@ -313,6 +313,8 @@ class CacheManager:
                 self.groups.append(PagedGroup(need, n_slots, page_size, n_pages))
             else:
                 self.groups.append(StateGroup(need, n_slots, max_requests))
+        self._paged = [g for g in self.groups if isinstance(g, PagedGroup)]      # the groups never change
+        self._state = [g for g in self.groups if isinstance(g, StateGroup)]
         self.lengths: dict[Hashable, int] = {}
         # pages are taken over only where every group keeps all keys in pages
         self.prefix_reuse = bool(enable_prefix_cache) and bool(self.groups) and all(
@@ -354,11 +356,11 @@ class CacheManager:
     # ------------------------------------------------------------------ queries
     @property
     def paged_groups(self) -> list[PagedGroup]:
-        return [g for g in self.groups if isinstance(g, PagedGroup)]
+        return self._paged
 
     @property
     def state_groups(self) -> list[StateGroup]:
-        return [g for g in self.groups if isinstance(g, StateGroup)]
+        return self._state
 
     def live(self) -> list:
         return list(self.lengths)
@@ -371,8 +373,9 @@ class CacheManager:
         return [g.missing(request, length) for g in self.paged_groups]
 
     def can_grow(self, request, length: int, reserve: list[int] | None = None) -> bool:
-        reserve = reserve or [0] * len(self.paged_groups)
-        return all(g.missing(request, length) + r <= g.pool.num_free for g, r in zip(self.paged_groups, reserve))
+        if reserve is None:
+            return all(g.missing(request, length) <= g.pool.num_free for g in self._paged)
+        return all(g.missing(request, length) + r <= g.pool.num_free for g, r in zip(self._paged, reserve))
 
     def fits_empty_pool(self, length: int) -> bool:
         """Could a request of ``length`` tokens ever be held, with every page free?

@@ -93,11 +93,13 @@ def run_ours(args) -> int:
 
     K, W = args.steps, args.warmup
     page = args.page_size
-    per_request = args.context + 2 * (K + W) + 3 * page
+    budget = 4096
+    fill_steps = -(-args.batch * args.context // budget)        # steps in which the end-to-end run's prompts are computed
+    per_request = args.context + 2 * (K + W) + fill_steps + 3 * page
     max_batch = max(args.batch, 64 if not args.skip_points else args.batch)
     num_pages = max_batch * ((per_request + page - 1) // page) + 8 + (2048 + page) // page
     engine = Engine(model, "bfloat16", max_batch_size=max_batch, max_model_len=8192, page_size=page,
-                    num_pages=num_pages, token_budget=4096, enable_cuda_graphs=not args.no_cuda_graphs,
+                    num_pages=num_pages, token_budget=budget, enable_cuda_graphs=not args.no_cuda_graphs,
                     enable_prefix_cache=False)     # every prompt is computed: no number rests on pages taken over
     runner = engine.runner
     pk, pk_src = peaks()
@@ -131,7 +133,8 @@ def run_ours(args) -> int:
     pre_frac = flops / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12)
 
     # end to end through the public entry point: host ids in, host ids out, every step
-    sp = SamplingParams(temperature=0.0, max_tokens=K + W + 4, ignore_eos=True)
+    # requests whose prompts are done decode while the others' prompts are computed: enough tokens for those steps too
+    sp = SamplingParams(temperature=0.0, max_tokens=K + W + 4 + fill_steps, ignore_eos=True)
     for i in range(args.batch):
         engine.add_request(B.synthetic_ids(cfg.vocab_size, args.context, 50 + i), sp)
     while any(r.remaining > 1 or r.computed == 0 for r in engine.scheduler.running) or engine.scheduler.waiting:
