@@ -418,10 +418,12 @@ class CacheManager:
 
         Reserving does not move the request's length: ``advance`` does, once the
         tokens have run.  Growing to a length already reserved takes nothing."""
-        if not self.can_grow(request, length):
+        need = [g.missing(request, length) for g in self._paged]
+        if any(n > g.pool.num_free for n, g in zip(need, self._paged)):
             raise OutOfPages(f"request {request!r} cannot grow to {length} tokens: free {self.free_pages()}")
-        for g in self.paged_groups:
-            g.grow(request, length)
+        for n, g in zip(need, self._paged):
+            if n:
+                g.tables[request].extend(g.pool.allocate(n))
 
     def advance(self, request, length: int) -> None:
         """The request now holds ``length`` tokens in its pages."""

@@ -33,7 +33,7 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
 
-@dataclass
+@dataclass(eq=False)        # a request is itself: membership in the queues is by identity, not by comparing token lists
 class Request:
     request_id: Hashable
     prompt: list[int]
@@ -242,7 +242,8 @@ class Scheduler:
             return None
         plan = StepPlan()
         for e in keep:
-            m.grow(e.request.request_id, e.start + 2)
+            for g in m.paged_groups:                       # the pools hold them all: counted above
+                g.grow(e.request.request_id, e.start + 2)
             plan.entries.append(PlannedEntry(e.request, e.start + 1, 1, True))
         return plan
 
