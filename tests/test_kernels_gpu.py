@@ -64,7 +64,7 @@ def test_add_rmsnorm(ops, dtype, T, H, eps):
 
 
 def test_rmsnorm_breaking_arm(ops):
-    """The judge can see a fault: a wrong eps moves the result beyond the tolerance."""
+    """The comparison can see a fault: a wrong eps moves the result beyond the tolerance."""
     x = rnd(4, 96, scale=0.01, seed=4)
     w = torch.ones(96, device="cuda")
     good = ops.add_rmsnorm(x.clone(), None, w, 1e-6, torch.empty_like(x))
