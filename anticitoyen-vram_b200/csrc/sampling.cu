@@ -372,4 +372,73 @@ ACV_API int acv_sample(const float* logits, int ld, int rows, int V, const float
     return acv_launch_status();
 }
 
+// ----------------------------------------------------------------------------- the k most probable tokens
+// For each row the k largest logits in falling order (equal values: the lower index first) with their log
+// probabilities logit - logsumexp(row), the normalisation of the chosen token's log probability
+// (acvram/engine/sampler.py:103-117).  One block per row: a pass for the maximum and the sum of exponentials,
+// then k passes, each finding the largest entry that comes after the one found before it.
+#define TOPLP_MAX_K 64
+__global__ void __launch_bounds__(SMP_THREADS)
+top_logprobs_kernel(const float* __restrict__ logits, int ld, int V, int k, int* __restrict__ out_ids,
+                    float* __restrict__ out_lp) {
+    __shared__ float redf[32];
+    __shared__ int redi[32];
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) mx = fmaxf(mx, row[i]);
+    mx = block_reduce_max(mx, redf);
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) sum += __expf(row[i] - mx);
+    sum = block_reduce_sum(sum, redf);
+    const float lse = mx + logf(sum);
+    float prev_v = INFINITY;
+    int prev_i = -1;
+    for (int n = 0; n < k; ++n) {
+        float best = -INFINITY;
+        int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float v = row[i];
+            const bool after = v < prev_v || (v == prev_v && i > prev_i);      // not yet given out
+            if (after && v > -INFINITY && (v > best || (v == best && i < bi))) { best = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+        __syncthreads();
+        if (lane == 0) { redf[warp] = best; redi[warp] = bi; }
+        __syncthreads();
+        best = lane < nwarp ? redf[lane] : -INFINITY;
+        bi = lane < nwarp ? redi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        }
+        if (bi == 0x7fffffff) {              // fewer than k finite entries are left (k > V, or a row of -inf)
+            if (threadIdx.x == 0) { out_ids[(size_t)blockIdx.x * k + n] = -1; out_lp[(size_t)blockIdx.x * k + n] = -INFINITY; }
+            continue;
+        }
+        if (threadIdx.x == 0) {
+            out_ids[(size_t)blockIdx.x * k + n] = bi;
+            out_lp[(size_t)blockIdx.x * k + n] = best - lse;
+        }
+        prev_v = best;
+        prev_i = bi;
+    }
+}
+
+// logits float [rows, V] (row stride ld); out_ids int [rows, k], out_lp float [rows, k]; 1 <= k <= 64.
+ACV_API int acv_top_logprobs(const float* logits, int ld, int rows, int V, int k, int* out_ids, float* out_lp,
+                             cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0 || k < 1 || k > TOPLP_MAX_K) return ACV_ERR_SIZE;
+    top_logprobs_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, ld, V, k, out_ids, out_lp);
+    return acv_launch_status();
+}
+
 ACV_TL_EXPORT(sampling)

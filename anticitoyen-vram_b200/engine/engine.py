@@ -16,6 +16,7 @@ from typing import Hashable, Iterator, Optional, Sequence
 
 import torch
 
+from ..kernels import ops
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner
@@ -34,8 +35,9 @@ class GenerationOutput:
     finish_reason: Optional[str] = None
     prompt_tokens: int = 0
     completion_tokens: int = 0
-    logprob: float = 0.0
-    top_logprobs: Optional[list] = None
+    logprob: Optional[float] = None          # of the delivered token, for requests with ``logprobs`` set
+    top_logprobs: Optional[list] = None      # [(token id, log probability)], most probable first, ``logprobs`` of them
+    cumulative_logprob: Optional[float] = None
 
 
 @dataclass
@@ -70,6 +72,7 @@ class _Flight:
     rows: list                 # the requests that get a token, in the order of ``tokens``
     tokens: torch.Tensor | None
     logprobs: torch.Tensor | None
+    top: tuple | None          # (ids [rows, k], log probabilities [rows, k]) on the device, when a request asks for them
     host: torch.Tensor | None  # pinned copy of ``tokens``, valid after ``event``
     event: torch.cuda.Event
     t0: float
@@ -220,10 +223,16 @@ class Engine:
                                  (e.count - 1,) if e.samples else ()) for e in plan.entries]
         logits = self.runner.step(entries, device_tokens=device_tokens)
         rows = [e.request for e in plan.entries if e.samples]
-        tokens = logprobs = host = None
+        tokens = logprobs = host = top = None
         event = torch.cuda.Event()
         if rows:
             want_lp = any(r.params.logprobs is not None for r in rows)
+            # the k most probable tokens are read from the logits as the model gave them, before penalties and
+            # temperature, one k for the whole step (the largest asked for), as the reference does
+            # (acvram/engine/runner.py:2625-2640)
+            k = max((int(r.params.logprobs or 0) for r in rows), default=0)
+            if k > 0:
+                top = ops.top_logprobs(logits, min(k, 64, logits.shape[1]))
             tokens, logprobs = self.sampler(
                 logits, [r.params for r in rows], [r.tokens if r.params.penalised else () for r in rows],
                 [r.seed for r in rows], [len(r.output) + lag for r in rows], want_lp)
@@ -232,13 +241,14 @@ class Engine:
             host.copy_(tokens, non_blocking=True)
         event.record()
         decode = sum(1 for e in plan.entries if e.count == 1 and e.start > 0)
-        return _Flight(plan, rows, tokens, logprobs, host, event, t0, decode, plan.num_tokens - decode)
+        return _Flight(plan, rows, tokens, logprobs, top, host, event, t0, decode, plan.num_tokens - decode)
 
     def _complete(self, f: "_Flight") -> list[GenerationOutput]:
         """Wait for the step's tokens (the step's one wait for the device), record them, make the outputs."""
         f.event.synchronize()
         sampled = f.host.tolist() if f.host is not None else []
         logprobs = f.logprobs.tolist() if f.logprobs is not None else None
+        top = (f.top[0].tolist(), f.top[1].tolist()) if f.top is not None else None
         dt = time.perf_counter() - f.t0
         before = {id(r): len(r.output) for r in f.rows}
         touched = self.scheduler.commit(f.plan, sampled, self.model.plan.eos_token_ids)
@@ -246,9 +256,14 @@ class Engine:
         outputs = []
         for r in touched:
             new = r.output[before[id(r)]:]
-            if logprobs is not None and new:
-                r.logprob_sum += logprobs[row_of[id(r)]]
-            outputs.append(self._output(r, new))
+            lp = tops = None
+            if logprobs is not None and new and r.params.logprobs is not None:
+                lp = logprobs[row_of[id(r)]]
+                r.logprob_sum += lp
+                if top is not None and r.params.logprobs > 0:
+                    i, n = row_of[id(r)], int(r.params.logprobs)
+                    tops = [(t, p) for t, p in zip(top[0][i][:n], top[1][i][:n]) if t >= 0]
+            outputs.append(self._output(r, new, lp, tops))
         self.stats.steps += 1
         self.stats.decode_tokens += f.decode
         self.stats.prefill_tokens += f.prefill
@@ -258,11 +273,12 @@ class Engine:
             self.stats.decode_seconds += dt
         return outputs
 
-    def _output(self, r: Request, new: list[int]) -> GenerationOutput:
+    def _output(self, r: Request, new: list[int], logprob: float | None = None, top: list | None = None) -> GenerationOutput:
         if r.finished:
             self._requests.pop(r.request_id, None)
         return GenerationOutput(self._seq_ids.get(r.request_id, -1), r.request_id, list(new), "", r.finished,
-                                r.finish_reason, len(r.prompt), len(r.output), r.logprob_sum)
+                                r.finish_reason, len(r.prompt), len(r.output), logprob, top,
+                                r.logprob_sum if r.params.logprobs is not None else None)
 
     # ------------------------------------------------------------------ generation
     def generate(self, prompt_ids: Sequence[int], params: SamplingParams | None = None) -> Iterator[GenerationOutput]:

@@ -81,6 +81,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
         "acv_sample": [P, I, I, I, P, P, P, P, P, P, P, P, P],
+        "acv_top_logprobs": [P, I, I, I, I, P, P, P],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)
@@ -379,6 +380,20 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _check(library().acv_sample(_p(logits), logits.stride(0), R, V, _p(temperature), _p(top_k), _p(top_p), _p(min_p),
                                 _p(seed), _p(counter), _p(out_token), _p(out_logprob), _stream()), "sample")
     return out_token
+
+
+def top_logprobs(logits: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """(ids int32 [R, k], log probabilities float32 [R, k]) of each row's k most probable tokens, most probable
+    first (equal logits: the lower id first); log probability = logit - logsumexp(row).  1 <= k <= 64; where a row
+    has fewer than k entries above -inf the rest is id -1 with -inf."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("top_logprobs: float32 rows wanted")
+    R, V = logits.shape
+    ids = torch.empty((R, k), device=logits.device, dtype=torch.int32)
+    lp = torch.empty((R, k), device=logits.device, dtype=torch.float32)
+    _check(library().acv_top_logprobs(_p(logits), logits.stride(0), R, V, k, _p(ids), _p(lp), _stream()), "top_logprobs")
+    return ids, lp
 
 
 # ----------------------------------------------------------------------------- tensor-core attention (bfloat16)

@@ -303,3 +303,33 @@ def test_abort_between_steps_frees_everything_and_leaves_the_others_alone(tiny_f
         assert got[f"q{i}"] == plain_qwen3.greedy_generate(cfg, t, prompts[i], 24)
     eng.runner.manager.check()
     assert eng.runner.manager.free_pages() == [24]
+
+
+def test_log_probabilities_of_the_chosen_and_of_the_most_probable_tokens(tiny_folders, plain_models):
+    """``logprobs=k``: every delivered token comes with its own log probability and with the k most probable tokens
+    of its step, normalised over the whole vocabulary of the plain implementation's logits; a request beside it
+    that asked for none gets none."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["B"]
+    prompts = [random_ids(cfg["vocab_size"], n, 500 + n) for n in (11, 23)]
+    eng = engine_for(tiny_folders["B"], page_size=8)
+    a = eng.add_request(prompts[0], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, logprobs=3))
+    b = eng.add_request(prompts[1], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))
+    outs = {a: [], b: []}
+    while not eng.idle:
+        for o in eng.step():
+            outs[o.request_id].append(o)
+    assert all(o.logprob is None and o.top_logprobs is None and o.cumulative_logprob is None for o in outs[b])
+    toks = [x for o in outs[a] for x in o.token_ids]
+    assert toks == plain_qwen3.greedy_generate(cfg, t, prompts[0], 6)
+    ref = torch.log_softmax(plain_qwen3.forward_logits(cfg, t, prompts[0] + toks).double(), dim=-1)
+    total = 0.0
+    for n, o in enumerate(outs[a]):
+        row = ref[len(prompts[0]) - 1 + n]
+        want = torch.topk(row, 3)
+        assert [i for i, _ in o.top_logprobs] == want.indices.tolist()
+        assert o.top_logprobs[0][0] == o.token_ids[0], "greedy: the chosen token is the most probable one"
+        torch.testing.assert_close(torch.tensor([p for _, p in o.top_logprobs]).double(), want.values, rtol=1e-4, atol=1e-4)
+        assert abs(o.logprob - float(row[o.token_ids[0]])) < 1e-4
+        total += o.logprob
+        assert abs(o.cumulative_logprob - total) < 1e-4

@@ -91,3 +91,25 @@ def test_sampler_object_mixes_greedy_and_sampled_rows():
     scaled = plain_qwen3.filtered_distribution(logits[1].cpu(), 0.8, 20, 0.0, 1.0)
     assert toks[1] == plain_qwen3.draw(scaled, plain_qwen3.philox_uniform(4, 6))
     assert toks[2] != best, "the repetition penalty moved the greedy choice"
+
+
+@pytest.mark.parametrize("V,k", [(331, 5), (4097, 1), (151936, 20), (7, 7), (5, 8)])
+def test_top_logprobs_kernel(V, k):
+    """The k most probable tokens of each row with logit - logsumexp, against a sort in float64; equal logits
+    come lowest id first; a row shorter than k ends with id -1 and -inf."""
+    from acvram_b200.kernels import ops
+    g = torch.Generator().manual_seed(V + k)
+    logits = (torch.randn(6, V, generator=g) * 3.0)
+    logits[1, : min(V, 4)] = 2.5                    # equal values among the largest
+    logits[2, V // 2] = float("-inf")
+    if V > 100:
+        logits[3] = torch.round(logits[3])          # many equal values
+    ids, lp = ops.top_logprobs(logits.cuda(), k)
+    ids, lp = ids.cpu(), lp.cpu()
+    ref = torch.log_softmax(logits.double(), dim=-1)
+    for r in range(6):
+        order = sorted(range(V), key=lambda i: (-float(logits[r, i]), i))
+        order = [i for i in order if logits[r, i] != float("-inf")][:k]
+        assert ids[r, :len(order)].tolist() == order
+        torch.testing.assert_close(lp[r, :len(order)].double(), ref[r, order], rtol=1e-5, atol=1e-5)
+        assert all(int(i) == -1 for i in ids[r, len(order):]) and all(v == float("-inf") for v in lp[r, len(order):])
