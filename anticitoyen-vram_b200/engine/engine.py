@@ -21,6 +21,7 @@ from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner
 from .scheduler import Request, Scheduler, StepPlan
+from .text import cut_at_stop, text_delta
 
 
 @dataclass
@@ -88,6 +89,8 @@ class Engine:
                  tokenizer=None) -> None:
         """``model``: a folder with config.json and model.safetensors, or (with
         ``random_weights``) a typed configuration or a folder whose config.json alone is read.
+        ``tokenizer``: anything with ``decode(ids) -> str``; with one, outputs carry the text that their tokens
+        add (``text_delta``) and ``SamplingParams.stop`` strings end a request.
         ``enable_prefix_cache`` (the reference's name and default, acvram/engine/runner.py:689-694): the full
         pages of a finished request stay known, and a later request that begins the same way takes them over."""
         from ..config import load_config
@@ -263,7 +266,7 @@ class Engine:
                 if top is not None and r.params.logprobs > 0:
                     i, n = row_of[id(r)], int(r.params.logprobs)
                     tops = [(t, p) for t, p in zip(top[0][i][:n], top[1][i][:n]) if t >= 0]
-            outputs.append(self._output(r, new, lp, tops))
+            outputs.append(self._output(r, new, lp, tops, self._text(r) if self.tokenizer is not None else ""))
         self.stats.steps += 1
         self.stats.decode_tokens += f.decode
         self.stats.prefill_tokens += f.prefill
@@ -273,10 +276,27 @@ class Engine:
             self.stats.decode_seconds += dt
         return outputs
 
-    def _output(self, r: Request, new: list[int], logprob: float | None = None, top: list | None = None) -> GenerationOutput:
+    def _text(self, r: Request) -> str:
+        """The text that the request's new tokens add; ends the request where a stop string begins
+        (acvram/engine/runner.py:2550-2557: the string itself is not delivered)."""
+        delta, r.text_tokens = text_delta(self.tokenizer, r.output, r.text_tokens, final=r.finished)
+        r.text += delta
+        if delta and r.params.stop and (not r.finished or r.finish_reason == "length"):
+            kept, hit = cut_at_stop(r.text, delta, r.params.stop)
+            if hit:
+                r.text = r.text[:len(r.text) - len(delta) + len(kept)]
+                delta = kept
+                if r.finished:
+                    r.finish_reason = "stop"
+                else:
+                    self.scheduler.finish(r, "stop")
+        return delta
+
+    def _output(self, r: Request, new: list[int], logprob: float | None = None, top: list | None = None,
+                text: str = "") -> GenerationOutput:
         if r.finished:
             self._requests.pop(r.request_id, None)
-        return GenerationOutput(self._seq_ids.get(r.request_id, -1), r.request_id, list(new), "", r.finished,
+        return GenerationOutput(self._seq_ids.get(r.request_id, -1), r.request_id, list(new), text, r.finished,
                                 r.finish_reason, len(r.prompt), len(r.output), logprob, top,
                                 r.logprob_sum if r.params.logprobs is not None else None)
 

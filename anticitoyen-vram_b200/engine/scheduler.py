@@ -49,6 +49,8 @@ class Request:
     reused: int = 0              # tokens taken over from published pages at the last admission
     page_keys: list = field(default_factory=list, repr=False)   # keys of the full pages of ``tokens``, as far as made
     published: int = 0           # pages of this admission that are already known to later requests
+    text: str = ""               # the output's text so far (when the engine has a tokenizer)
+    text_tokens: int = 0         # output tokens that ``text`` covers
 
     @property
     def tokens(self) -> list[int]:
@@ -307,6 +309,11 @@ class Scheduler:
             elif len(r.prompt) + len(r.output) >= self.max_model_len:
                 self._finish(r, "length")
         return touched
+
+    def finish(self, r: Request, reason: str) -> None:
+        """End a request for a reason that the engine finds (a stop string in its text)."""
+        if not r.finished:
+            self._finish(r, reason)
 
     # ------------------------------------------------------------------ internals
     def _finish(self, r: Request, reason: str) -> None:

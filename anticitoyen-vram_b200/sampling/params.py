@@ -17,7 +17,7 @@ class SamplingParams:
     presence_penalty: float = 0.0
     frequency_penalty: float = 0.0
     max_tokens: int = 512
-    stop: list[str] = field(default_factory=list)          # needs a tokenizer; none is attached here
+    stop: list[str] = field(default_factory=list)          # strings that end the request; need the engine's tokenizer
     stop_token_ids: list[int] = field(default_factory=list)
     seed: Optional[int] = None        # the reference stores it and never uses it; here it keys the request's generator
     n: int = 1

@@ -333,3 +333,33 @@ def test_log_probabilities_of_the_chosen_and_of_the_most_probable_tokens(tiny_fo
         assert abs(o.logprob - float(row[o.token_ids[0]])) < 1e-4
         total += o.logprob
         assert abs(o.cumulative_logprob - total) < 1e-4
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_text_deltas_and_stop_strings_with_a_tokenizer(tiny_folders, plain_models, ahead):
+    """With a tokenizer the outputs carry their text, and a stop string ends its request where it begins: the
+    string is not delivered, the pages come back, the request beside it is not touched."""
+    from acvram_b200 import SamplingParams
+
+    class Tok:
+        def decode(self, ids):
+            return "".join(f"<{i}>" for i in ids)
+
+    cfg, t = plain_models["A"]
+    prompts = [random_ids(cfg["vocab_size"], n, 600 + n) for n in (9, 14)]
+    want = [plain_qwen3.greedy_generate(cfg, t, p, 12) for p in prompts]
+    j = next(i for i in range(3, 12) if want[0][i] not in want[0][:i])
+    eng = engine_for(tiny_folders["A"], run_ahead=ahead, tokenizer=Tok())
+    a = eng.add_request(prompts[0], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True, stop=[f"<{want[0][j]}>"]))
+    b = eng.add_request(prompts[1], SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    outs = {a: [], b: []}
+    while not eng.idle:
+        for o in eng.step():
+            outs[o.request_id].append(o)
+    assert "".join(o.text_delta for o in outs[b]) == "".join(f"<{i}>" for i in want[1])
+    assert outs[b][-1].finish_reason == "length"
+    assert "".join(o.text_delta for o in outs[a]) == "".join(f"<{i}>" for i in want[0][:j])
+    assert outs[a][-1].finished and outs[a][-1].finish_reason == "stop"
+    assert [x for o in outs[a] for x in o.token_ids] == want[0][:j + 1], "the token that completed the string is the last"
+    assert eng.runner.manager.free_pages() == [64]
+    eng.runner.manager.check()
