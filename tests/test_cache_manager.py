@@ -290,6 +290,8 @@ def test_random_orders_with_shared_beginnings(seed):
                     assert m.paged_groups[0].pool.holders(table[i]) == 1, "a shared page is written"
                     written[table[i]] = tuple(tokens[:min(n, (i + 1) * page)])
                 live[r] = (tokens, n)
+                if rng.random() < 0.5:              # full pages become known while the request still runs
+                    m.publish(r, m.page_keys(tokens), n)
         elif live:
             r = rng.choice(list(live))
             tokens, have = live.pop(r)
