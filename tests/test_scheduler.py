@@ -306,22 +306,60 @@ def test_a_preempted_request_takes_its_own_pages_back():
 
 
 def test_random_traffic_with_shared_beginnings_keeps_the_books():
-    rng = random.Random(3)
-    m, s = make_reuse(num_pages=20, page=4, max_batch=4, budget=12, max_len=64)
-    stems = [[rng.randrange(1, 40) for _ in range(20)] for _ in range(2)]
-    reqs = []
-    for i in range(60):
-        if rng.random() < 0.5 and len(s.waiting) < 3:
-            prompt = rng.choice(stems)[:rng.randrange(1, 20)] + [rng.randrange(40, 60) for _ in range(rng.randrange(0, 4))]
-            r = Request(f"q{i}", prompt, SamplingParams(temperature=0.0, max_tokens=rng.randrange(1, 9)))
-            reqs.append(r)
-            s.add(r)
-        run_step(m, s, token=rng.randrange(1, 40))
-    while not s.idle:
-        run_step(m, s, token=rng.randrange(1, 40))
-    assert all(r.finished for r in reqs) and m.free_pages() == [20]
-    assert all(len(r.output) == r.params.max_tokens for r in reqs if r.finish_reason == "length")
-    assert s.counters["reused_tokens"] > 0
+    """Random requests with shared beginnings, stops, aborts and a pool that preempts.  A shadow of what each page
+    holds (written as the runner would write it) shows that a step never writes a page that two requests hold, that
+    every position a step reads holds the tokens of the request that reads it, and the budget is kept."""
+    reused = preempted = 0
+    for seed in range(6):
+        rng = random.Random(seed)
+        page = 4
+        m, s = make_reuse(num_pages=rng.choice([12, 20, 40]), page=page, max_batch=4, budget=rng.choice([5, 12, 30]), max_len=64)
+        stems = [[rng.randrange(1, 40) for _ in range(20)] for _ in range(2)]
+        shadow: dict[int, list] = {}                    # page -> the token whose keys each of its rows holds
+        reqs = []
+        for i in range(120):
+            if rng.random() < 0.4 and len(s.waiting) < 3:
+                prompt = rng.choice(stems)[:rng.randrange(1, 20)] + [rng.randrange(40, 60) for _ in range(rng.randrange(0, 4))]
+                r = Request(f"q{seed}-{i}", prompt, SamplingParams(temperature=0.0, max_tokens=rng.randrange(1, 9),
+                                                                   stop_token_ids=[7] if rng.random() < 0.3 else []))
+                reqs.append(r)
+                s.add(r)
+            if rng.random() < 0.05 and s.running:
+                s.abort(rng.choice(s.running).request_id)
+            plan = s.schedule()
+            assert plan.num_tokens <= s.token_budget and len(s.running) <= 4
+            for e in plan.entries:
+                r, table = e.request, m.block_table(e.request.request_id, 0)
+                tokens = r.tokens
+                for pos in range(e.start):              # what the step reads was written with this request's tokens
+                    assert shadow[table[pos // page]][pos % page] == tokens[pos], (seed, i, r.request_id, pos)
+                for pos in range(e.start, e.start + e.count):
+                    p = table[pos // page]
+                    assert m.paged_groups[0].pool.holders(p) == 1, "a page that two requests hold is written"
+                    shadow.setdefault(p, [None] * page)[pos % page] = tokens[pos]
+                m.advance(r.request_id, e.start + e.count)
+            s.commit(plan, [rng.randrange(1, 40) for e in plan.entries if e.samples])
+            m.check()
+        steps = 0
+        while not s.idle:
+            plan = s.schedule()
+            for e in plan.entries:
+                table, tokens = m.block_table(e.request.request_id, 0), e.request.tokens
+                for pos in range(e.start):
+                    assert shadow[table[pos // page]][pos % page] == tokens[pos]
+                for pos in range(e.start, e.start + e.count):
+                    assert m.paged_groups[0].pool.holders(table[pos // page]) == 1
+                    shadow.setdefault(table[pos // page], [None] * page)[pos % page] = tokens[pos]
+                m.advance(e.request.request_id, e.start + e.count)
+            s.commit(plan, [rng.randrange(1, 40) for e in plan.entries if e.samples])
+            m.check()
+            steps += 1
+            assert steps < 2000
+        assert all(r.finished for r in reqs) and m.free_pages() == [m.paged_groups[0].pool.num_pages]
+        assert all(len(r.output) == r.params.max_tokens for r in reqs if r.finish_reason == "length")
+        reused += s.counters["reused_tokens"]
+        preempted += s.counters["preempted"]
+    assert reused > 100 and preempted > 0
 
 
 def test_full_pages_are_known_while_their_request_still_runs():
