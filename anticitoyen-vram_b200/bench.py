@@ -165,11 +165,12 @@ def time_prefill(runner, tokens: int, reps: int = 3, warmup: int = 1) -> dict:
 
 
 def bench_decode(model, random_weights=False, seed=0, dtype="bfloat16", batches=(1,), context=128, n_tokens=256,
-                 device="cuda:0", cuda_graphs=True, repetitions=3) -> dict:
-    """``acvram bench --what decode``: median decode tokens/s for each batch size, with the spread."""
+                 device="cuda:0", cuda_graphs=True, repetitions=3, prefill=0) -> dict:
+    """``acvram bench --what decode``: median decode tokens/s for each batch size, with the spread; with
+    ``prefill`` > 0 also the tokens/s of one prompt of that many tokens computed in one step."""
     from .engine import Engine
-    need = max(batches) * (context + n_tokens + 64)
-    eng = Engine(model, dtype, max_batch_size=max(batches), max_model_len=context + n_tokens + 64,
+    need = max(max(batches) * (context + n_tokens + 64), prefill + 64)
+    eng = Engine(model, dtype, max_batch_size=max(batches), max_model_len=max(context + n_tokens, prefill) + 64,
                  random_weights=random_weights, seed=seed, device=device, enable_cuda_graphs=cuda_graphs,
                  page_size=64, num_pages=need // 64 + 2 * max(batches), enable_prefix_cache=False)
     out = {"model": str(model), "dtype": dtype, "context": context, "tokens": n_tokens}
@@ -184,4 +185,8 @@ def bench_decode(model, random_weights=False, seed=0, dtype="bfloat16", batches=
                 eng.runner.release(n)
         out[f"decode_b{b}"] = {"tokens_per_s": statistics.median(rates), "spread": max(rates) - min(rates),
                                "runs": rates}
+    if prefill > 0:
+        if prefill > eng.max_model_len:
+            raise ValueError(f"a prefill of {prefill} tokens does not fit the model's {eng.max_model_len} positions")
+        out["prefill"] = time_prefill(eng.runner, prefill, reps=3, warmup=1)
     return out

@@ -76,7 +76,8 @@ def cmd_bench(args) -> int:
         return 2
     res = bench_decode(args.model, random_weights=args.random_weights, seed=args.seed, dtype=args.dtype,
                        batches=[int(b) for b in args.batch.split(",")], context=args.context,
-                       n_tokens=args.tokens, device=args.device, cuda_graphs=not args.no_cuda_graphs)
+                       n_tokens=args.tokens, device=args.device, cuda_graphs=not args.no_cuda_graphs,
+                       prefill=args.prefill)
     if args.json:
         print(json.dumps(res))
     else:
@@ -129,6 +130,7 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--batch", default="1", help="batch sizes, comma separated")
     b.add_argument("--context", type=int, default=128, help="tokens of context before decoding (reference: 128)")
     b.add_argument("--tokens", type=int, default=256, help="tokens decoded per request (reference: 256)")
+    b.add_argument("--prefill", type=int, default=0, help="also time one prompt of this many tokens, computed in one step")
     b.add_argument("--json", action="store_true")
     b.set_defaults(func=cmd_bench)
 

@@ -152,11 +152,12 @@ def test_command_line_generate_and_random_model(tiny_folders, plain_models, tmp_
     assert all(torch.equal(a[k], b[k]) for k in a)
     # `bench --what decode` (the reference's name): a rate for each batch size asked for
     out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "acvram"), "bench", tiny_folders["A"], "--what", "decode",
-                          "--batch", "1,3", "--context", "20", "--tokens", "8", "--json"],
+                          "--batch", "1,3", "--context", "20", "--tokens", "8", "--prefill", "40", "--json"],
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr
     res = json.loads(out.stdout.strip().splitlines()[-1])
     assert res["decode_b1"]["tokens_per_s"] > 0 and res["decode_b3"]["tokens_per_s"] > res["decode_b1"]["tokens_per_s"] * 0.5
+    assert res["prefill"]["tokens"] == 40 and res["prefill"]["tokens_per_s"] > 0
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
