@@ -25,6 +25,34 @@ def read_config_json(path: str | os.PathLike) -> dict[str, Any]:
             raise ConfigError(f"{path} is not valid JSON: {exc}") from None
     if not isinstance(cfg, dict):
         raise ConfigError(f"{path} does not hold a JSON object")
+    return merge_generation_stops(cfg, os.path.join(os.path.dirname(os.path.abspath(path)), "generation_config.json"))
+
+
+def _id_list(value: Any) -> list[int]:
+    if isinstance(value, bool):
+        return []
+    if isinstance(value, int):
+        return [value]
+    if isinstance(value, (list, tuple)):
+        return [v for v in value if isinstance(v, int) and not isinstance(v, bool)]
+    return []
+
+
+def merge_generation_stops(cfg: dict[str, Any], generation_config_path: str) -> dict[str, Any]:
+    """The end-of-sequence ids of ``generation_config.json`` beside the model's config.json join those of
+    config.json itself: some checkpoints name their end-of-turn token only there, and the reference lets that file
+    have its say on the stop tokens (acvram/engine/config.py:816-835).  A file that is absent or unreadable
+    changes nothing."""
+    if not os.path.isfile(generation_config_path):
+        return cfg
+    try:
+        with open(generation_config_path, "r", encoding="utf-8") as fh:
+            gen = json.load(fh)
+    except (OSError, json.JSONDecodeError):
+        return cfg
+    merged = _id_list(cfg.get("eos_token_id")) + (_id_list(gen.get("eos_token_id")) if isinstance(gen, dict) else [])
+    if merged:
+        cfg = {**cfg, "eos_token_id": sorted(set(merged))}
     return cfg
 
 

@@ -84,3 +84,20 @@ def test_another_architecture_registers_without_touching_the_package(tmp_path):
         assert cfg.width == 7
     finally:
         REGISTRY.pop("ToyForTests")
+
+
+def test_generation_config_adds_its_end_of_sequence_ids(tmp_path):
+    """generation_config.json beside config.json: its eos ids join config.json's (int or list in either file)."""
+    import json
+    from acvram_b200.config import load_config
+    base = {"architectures": ["Qwen3ForCausalLM"], "vocab_size": 300, "hidden_size": 64, "intermediate_size": 128,
+            "num_hidden_layers": 2, "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16, "eos_token_id": 45}
+    (tmp_path / "config.json").write_text(json.dumps(base))
+    assert load_config(tmp_path).eos_token_id == (45,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [45, 43], "temperature": 0.6}))
+    assert load_config(tmp_path).eos_token_id == (43, 45)
+    assert load_config(tmp_path / "config.json").eos_token_id == (43, 45)
+    (tmp_path / "generation_config.json").write_text("{ not json")
+    assert load_config(tmp_path).eos_token_id == (45,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 299}))
+    assert load_config(tmp_path).eos_token_id == (45, 299)
