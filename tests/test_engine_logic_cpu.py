@@ -146,3 +146,40 @@ def test_bad_inputs_are_refused(tiny_folders):
         r.step([StepEntry("b", [1, 2], (5,))])
     with pytest.raises(ValueError):
         r.step([StepEntry("c", [], ())])
+
+
+def test_requests_that_take_pages_over_get_the_plain_logits(tiny_folders, plain_models):
+    """Scheduler and step function together, with prefix reuse and a pool small enough to preempt: requests whose
+    prompts begin alike run behind the pages of earlier ones, and the logits that choose each of their tokens are
+    the plain implementation's for the tokens they hold (greedy, so the tokens are the plain ones too)."""
+    from acvram_b200.engine.scheduler import Request, Scheduler
+    from acvram_b200.sampling import SamplingParams
+    cfg, t = plain_models["A"]
+    model = build(tiny_folders["A"])
+    page = 8
+    r = ModelRunner(model, page, 14, 3, enable_prefix_cache=True)
+    s = Scheduler(r.manager, 3, 24, 128)
+    stem = random_ids(cfg["vocab_size"], 40, 31)
+    prompts = [stem[:33], stem[:40], stem[:21] + random_ids(cfg["vocab_size"], 9, 32), stem[:33], stem[:9]]
+    reqs = [Request(f"r{i}", list(p), SamplingParams(temperature=0.0, max_tokens=7, ignore_eos=True)) for i, p in enumerate(prompts)]
+    pending = list(reqs)
+    step = 0
+    while pending or not s.idle:
+        if pending and step % 3 == 0:
+            s.add(pending.pop(0))
+        plan = s.schedule()
+        if plan.entries:
+            entries = [StepEntry(e.request.request_id, e.request.token_slice(e.start, e.count),
+                                 (e.count - 1,) if e.samples else ()) for e in plan.entries]
+            logits = r.step(entries)
+            rows = [e.request for e in plan.entries if e.samples]
+            for req, row in zip(rows, logits):
+                want = plain_qwen3.forward_logits(cfg, t, req.tokens)[-1]
+                assert (row - want).abs().max() < 5e-6, f"{req.request_id} at {len(req.tokens)} tokens (took over {req.reused})"
+            s.commit(plan, [int(row.argmax()) for row in logits])
+        r.manager.check()
+        step += 1
+        assert step < 400
+    for req, p in zip(reqs, prompts):
+        assert req.output == plain_qwen3.greedy_generate(cfg, t, p, 7)
+    assert s.counters["reused_tokens"] >= 32 + 16 + 32 and r.manager.free_pages() == [14]
