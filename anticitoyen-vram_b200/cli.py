@@ -98,7 +98,10 @@ def cmd_random_model(args) -> int:
 
 def cmd_replay(args) -> int:
     from .engine.replay import replay
-    return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout, args.device)
+    if args.page_size < 1 or 64 % args.page_size:
+        raise SystemExit("--page-size must divide 64")
+    return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout, args.device,
+                  args.page_size, args.max_requests)
 
 
 def build_parser() -> argparse.ArgumentParser:
@@ -147,6 +150,8 @@ def build_parser() -> argparse.ArgumentParser:
     t.add_argument("--out", required=True)
     t.add_argument("--max-tokens", type=int, required=True)
     t.add_argument("--device", default="cuda:0")
+    t.add_argument("--page-size", type=int, default=16, help="tokens per cache page (a divisor of 64)")
+    t.add_argument("--max-requests", type=int, default=16, help="most requests live at a time")
     t.set_defaults(func=cmd_replay)
     return p
 

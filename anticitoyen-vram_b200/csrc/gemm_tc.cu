@@ -65,6 +65,10 @@ struct GemmParams {
     float* workspace;       // [tiles][splits][BN][128] floats when splits > 1
     int* counters;          // [tiles], zero before and after
     int* status;            // 0, or the code of the wait that ran out
+    // for the test of the bounded waits only (acv_gemm_tc_test_fault): polls before a wait gives up, and a k-block
+    // whose loads the producer leaves out, so that the wait for it must run out (-1: none)
+    unsigned int wait_limit;
+    int skip_kb;
 };
 
 // SiLU(gate) * up with the roundings of the unfused path: the product's outputs are rounded to
@@ -461,9 +465,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (half_done) {
                         --early;
                     } else {
-                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 1); break; }
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 1); break; }
                         mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
                     }
+                    if (kb == p.skip_kb) continue;          // test of the bounded waits: the bytes announced never come
                     if (!(half_done && p.swap)) tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * GT_BK, ta * GT_BM);
                     if (!(half_done && !p.swap)) tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * s, kb * GT_BK, tb * BN);
                 }
@@ -479,12 +484,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const int split = item % p.splits;
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
                 const uint32_t buf = local & 1, use = local >> 1;
-                if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 2); break; }
+                if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 2); break; }
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BN;
                 bool failed = false;
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
-                    if (!mbar_wait(full0 + 8 * s, ph, &abort_s)) { abort_s = 1; atomicExch(p.status, 3); failed = true; break; }
+                    if (!mbar_wait(full0 + 8 * s, ph, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 3); failed = true; break; }
                     tc_fence_after();
                     if (local == 0 && kb == kb0) ACV_TL_MARK(TL_M_FIRST_FULL);
                     const uint32_t a_addr = tiles_addr + s * S::STAGE_BYTES, b_addr = a_addr + GT_BM * GT_BK * 2;
@@ -538,7 +543,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int split = item % p.splits, tile = item / p.splits;
             const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
             const uint32_t buf = local & 1, use = local >> 1;
-            if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 4); break; }
+            if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 4); break; }
             tc_fence_after();
             if (et == 0 && item + (int)gridDim.x >= n_items) ACV_TL_MARK(TL_M_ACC_DONE);
             const int row_a = ta * GT_BM + wq * 32 + lane;          // row of the A operand this thread holds
@@ -718,6 +723,18 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     return acv_launch_status();
 }
 
+// Test of the bounded waits, without a fault: the next product launched from this process (and only that one)
+// polls each mbarrier at most `wait_limit` times and its producer leaves out the loads of k-block `skip_kb`, so the
+// wait for that block runs out, the CTA's roles leave their loops, tensor memory is freed, and `status` holds the
+// code of the wait (1 producer, 2 accumulator buffer, 3 operand stage, 4 epilogue).  The output of that launch is
+// unspecified; the counters of a split-K workspace may be left non-zero and have to be cleared by the caller.
+static unsigned int g_test_wait_limit = 0;
+static int g_test_skip_kb = -1;
+ACV_API void acv_gemm_tc_test_fault(int wait_limit, int skip_kb) {
+    g_test_wait_limit = wait_limit > 0 ? (unsigned int)wait_limit : 0u;
+    g_test_skip_kb = skip_kb;
+}
+
 // x [M,K] (row stride ldx), w [N,K] (row stride ldw), C [M,N] (row stride ldc) bf16 or float.
 // bn: rows of the B operand per tile (16, 32, 64, 128 or 256); swap: the weight is the A operand.
 // splits > 1 needs workspace of tiles*splits*bn*128 floats and `tiles` zeroed counters.
@@ -742,6 +759,9 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
     p.kb_per_split = (p.n_kb + splits - 1) / splits;
     p.splits = (p.n_kb + p.kb_per_split - 1) / p.kb_per_split;
     p.C = C; p.workspace = workspace; p.counters = counters; p.status = status;
+    p.wait_limit = g_test_wait_limit ? g_test_wait_limit : GT_WAIT_LIMIT;
+    p.skip_kb = g_test_skip_kb;
+    g_test_wait_limit = 0; g_test_skip_kb = -1;      // one launch only
     const long long tiles = (long long)p.tiles_a * p.tiles_b;
     if (p.splits > 1 && (tiles * p.splits * bn * GT_BM > workspace_floats || tiles > n_counters)) return ACV_ERR_SCRATCH;
     if (tiles * p.splits > 0x7fffffff) return ACV_ERR_SIZE;

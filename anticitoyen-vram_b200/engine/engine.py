@@ -39,6 +39,7 @@ class GenerationOutput:
     logprob: Optional[float] = None          # of the delivered token, for requests with ``logprobs`` set
     top_logprobs: Optional[list] = None      # [(token id, log probability)], most probable first, ``logprobs`` of them
     cumulative_logprob: Optional[float] = None
+    error: Optional[str] = None              # with finish_reason "error": what went wrong in the request's step
 
 
 @dataclass
@@ -54,6 +55,8 @@ class EngineStats:
     refused: int = 0
     truncated: int = 0
     reused_tokens: int = 0       # prompt tokens taken over from published pages instead of being computed
+    failed_steps: int = 0        # steps that raised or whose kernels reported a wait that ran out
+    failed_requests: int = 0     # requests ended with finish_reason "error" by such steps
     extra: dict = field(default_factory=dict)
 
     def to_dict(self) -> dict:
@@ -75,6 +78,7 @@ class _Flight:
     logprobs: torch.Tensor | None
     top: tuple | None          # (ids [rows, k], log probabilities [rows, k]) on the device, when a request asks for them
     host: torch.Tensor | None  # pinned copy of ``tokens``, valid after ``event``
+    status: torch.Tensor       # pinned copy of the kernels' status word after the step, valid after ``event``
     event: torch.cuda.Event
     t0: float
     decode: int
@@ -126,7 +130,12 @@ class Engine:
         self.pipeline = run_ahead
         self._flight: _Flight | None = None
         self._pinned = [torch.empty(max_batch_size, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self._pinned_status = [torch.zeros(1, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self._pinned_turn = 0
+        self._status = ops.status_word(self.model.rt.device)
+        self._open: list[StepPlan] = []      # plans whose steps are launched or being launched, not yet committed
+        self._early: list[GenerationOutput] = []
+        self.last_error: str | None = None
         self._requests: dict[Hashable, Request] = {}
         self._seq_ids: dict[Hashable, int] = {}
 
@@ -173,20 +182,36 @@ class Engine:
         step k+1 (whose tokens it feeds on the device) before it reads step k's tokens, so that the host's
         share of a step (planning, the batch's tables, the launch, reading the tokens) falls into the time
         the device computes.  A call then delivers the tokens of the step launched one call earlier; the
-        first such call delivers nothing.  ``idle`` stays false until the last launched step is delivered."""
+        first such call delivers nothing.  ``idle`` stays false until the last launched step is delivered.
+
+        A step that raises, or whose kernels report a bounded wait that ran out (their status word, read
+        with the step's tokens), does not stop the engine: the requests of that step end with
+        ``finish_reason="error"``, their pages go back without becoming known to later requests, and
+        requests that wait or were not part of the step are served as before
+        (acvram/engine/runner.py:1329-1338)."""
+        self._early = []
+        try:
+            return self._step()
+        except Exception as exc:          # not BaseException: an interrupt still ends the caller's loop
+            return self._fail(exc)
+
+    def _step(self) -> list[GenerationOutput]:
         flight, self._flight = self._flight, None
         if flight is not None:
             ahead = self.scheduler.schedule_ahead(flight.plan) if self._can_run_ahead(flight) else None
             if ahead is not None:
+                self._open.append(ahead)
                 self._flight = self._launch(ahead, flight)
             return self._complete(flight)
         plan = self.scheduler.schedule()
-        outputs = [self._output(r, []) for r in plan.refused + plan.truncated]
+        self._open.append(plan)
+        outputs = self._early = [self._output(r, []) for r in plan.refused + plan.truncated]
         self.stats.preempted += len(plan.preempted)
         self.stats.refused += len(plan.refused)
         self.stats.truncated += len(plan.truncated)
         self.stats.reused_tokens = self.scheduler.counters["reused_tokens"]
         if not plan.entries:
+            self._open.remove(plan)
             return outputs
         flight = self._launch(plan, None)
         if self.pipeline and self._can_run_ahead(flight) and self.scheduler.schedule_ahead_possible(plan):
@@ -240,21 +265,27 @@ class Engine:
                 logits, [r.params for r in rows], [r.tokens if r.params.penalised else () for r in rows],
                 [r.seed for r in rows], [len(r.output) + lag for r in rows], want_lp)
             host = self._pinned[self._pinned_turn][:len(rows)]
-            self._pinned_turn ^= 1
             host.copy_(tokens, non_blocking=True)
+        status = self._pinned_status[self._pinned_turn]
+        status.copy_(self._status, non_blocking=True)
+        self._pinned_turn ^= 1
         event.record()
         decode = sum(1 for e in plan.entries if e.count == 1 and e.start > 0)
-        return _Flight(plan, rows, tokens, logprobs, top, host, event, t0, decode, plan.num_tokens - decode)
+        return _Flight(plan, rows, tokens, logprobs, top, host, status, event, t0, decode, plan.num_tokens - decode)
 
     def _complete(self, f: "_Flight") -> list[GenerationOutput]:
         """Wait for the step's tokens (the step's one wait for the device), record them, make the outputs."""
         f.event.synchronize()
+        code = int(f.status[0])
+        if code:
+            raise ops.KernelError(f"a kernel of the step gave up a bounded wait (status {code}): its results are not used")
         sampled = f.host.tolist() if f.host is not None else []
         logprobs = f.logprobs.tolist() if f.logprobs is not None else None
         top = (f.top[0].tolist(), f.top[1].tolist()) if f.top is not None else None
         dt = time.perf_counter() - f.t0
         before = {id(r): len(r.output) for r in f.rows}
         touched = self.scheduler.commit(f.plan, sampled, self.model.plan.eos_token_ids)
+        self._open.remove(f.plan)
         row_of = {id(r): i for i, r in enumerate(f.rows)}
         outputs = []
         for r in touched:
@@ -275,6 +306,40 @@ class Engine:
         else:
             self.stats.decode_seconds += dt
         return outputs
+
+    def _fail(self, exc: Exception, always: bool = False) -> list[GenerationOutput]:
+        """End the requests of every step that is launched or was being launched and not committed.
+
+        The device is waited for first (a step launched ahead may still run and write pages that are about to go
+        back); if that wait fails too, the CUDA context is lost and the first exception is raised again.  An
+        exception from outside a step (every plan is committed: a tokenizer that raised, say) is not the
+        engine's to absorb and is raised again as well."""
+        plans, self._open = self._open, []
+        self._flight = None
+        if not plans and not always:
+            raise exc
+        try:
+            torch.cuda.synchronize(self.model.rt.device)
+            ops.reset_after_failure()
+        except Exception:
+            raise exc
+        text = f"{type(exc).__name__}: {exc}"
+        self.last_error = text
+        failed = self.scheduler.fail([e.request for plan in plans for e in plan.entries])
+        self.stats.failed_steps += 1
+        self.stats.failed_requests += len(failed)
+        outputs = list(self._early)
+        for r in failed:
+            out = self._output(r, [])
+            out.error = text
+            outputs.append(out)
+        return outputs
+
+    def fail_step(self, reason: str = "a caller gave the step up") -> list[Hashable]:
+        """What the reference's ``echec_du_pas`` does for its server (acvram/engine/runner.py:1329-1338): end the
+        requests of the steps in flight with ``"error"``, give their pages back unpublished; returns their ids."""
+        self._early = []
+        return [o.request_id for o in self._fail(RuntimeError(reason), always=True) if o.finish_reason == "error"]
 
     def _text(self, r: Request) -> str:
         """The text that the request's new tokens add; ends the request where a stop string begins

@@ -30,7 +30,7 @@ MAX_LIVE_REQUESTS = 16  # traces hold up to four
 
 
 def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[str], echo: IO[str],
-           device: str = "cuda:0", page_size: int = PAGE_SIZE) -> int:
+           device: str = "cuda:0", page_size: int = PAGE_SIZE, max_requests: int = MAX_LIVE_REQUESTS) -> int:
     from ..models import build_from_folder
 
     run_dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[dtype]
@@ -41,7 +41,7 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
     # every live request's count is rounded up to a multiple of 64 by the caller, and 64 is a
     # multiple of the page, so max_tokens / page_size pages always hold the live requests
     num_pages = (max_tokens + page_size - 1) // page_size
-    runner = ModelRunner(model, page_size, num_pages, MAX_LIVE_REQUESTS)
+    runner = ModelRunner(model, page_size, num_pages, max_requests)
     if run_dtype == torch.bfloat16:
         runner.enable_graphs()      # as serving does: steps of single tokens replay a captured graph
     for line in lines:
@@ -52,10 +52,10 @@ def replay(model_dir: str, dtype: str, out_dir: str, max_tokens: int, lines: IO[
         step = rec["step"]
         entries = [StepEntry(e["id"], e["tokens"], e.get("want", ())) for e in rec.get("entries", ())]
         logits = runner.step(entries)
-        if logits.shape[0]:
-            logits.to("cpu").numpy().astype("<f4").tofile(os.path.join(out_dir, f"{step}.f32"))
-        else:
-            torch.cuda.synchronize()
+        host = logits.to("cpu") if logits.shape[0] else None
+        runner.check_status()       # waits for the device; a step whose kernels gave up a wait writes nothing
+        if host is not None:
+            host.numpy().astype("<f4").tofile(os.path.join(out_dir, f"{step}.f32"))
         for request in rec.get("end", ()):
             if request in runner.manager.lengths:
                 runner.release(request)
@@ -75,7 +75,9 @@ def main(argv=None) -> int:
     ap.add_argument("--device", default="cuda:0")
     ap.add_argument("--page-size", type=int, default=PAGE_SIZE,
                     help="tokens per cache page (a divisor of 64, so that the rounding of --max-tokens holds)")
+    ap.add_argument("--max-requests", type=int, default=MAX_LIVE_REQUESTS, help="most requests live at a time")
     args = ap.parse_args(argv)
     if args.page_size < 1 or 64 % args.page_size:
         ap.error("--page-size must divide 64")
-    return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout, args.device, args.page_size)
+    return replay(args.model, args.dtype, args.out, args.max_tokens, sys.stdin, sys.stdout, args.device, args.page_size,
+                  args.max_requests)

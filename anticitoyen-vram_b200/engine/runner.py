@@ -14,6 +14,7 @@ from typing import Hashable, Sequence
 import torch
 
 from ..cache import CacheManager, CacheStorage
+from ..kernels import ops
 from ..parts import Runtime
 from .batch import BatchBuilder, StepContext, StepEntry
 
@@ -41,6 +42,16 @@ class ModelRunner:
     @property
     def graph_launches(self) -> int:
         return self.graphs.launches if self.graphs is not None else 0
+
+    def check_status(self) -> None:
+        """Wait for the device and raise if a kernel gave up one of its bounded waits since the last check: the
+        logits of such a step are not to be used.  (``Engine`` reads the same word with every step's tokens.)"""
+        if self.rt.device.type != "cuda":
+            return
+        code = int(ops.status_word(self.rt.device).item())
+        if code:
+            ops.reset_after_failure()
+            raise ops.KernelError(f"a kernel gave up a bounded wait (status {code}); the step's results are not used")
 
     # ------------------------------------------------------------------ requests
     def admit(self, request: Hashable) -> None:

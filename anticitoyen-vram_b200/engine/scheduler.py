@@ -105,7 +105,7 @@ class Scheduler:
         self.waiting: deque[Request] = deque()
         self.running: list[Request] = []
         self._order = itertools.count()
-        self.counters = {"preempted": 0, "refused": 0, "truncated": 0, "admitted": 0, "reused_tokens": 0}
+        self.counters = {"preempted": 0, "refused": 0, "truncated": 0, "admitted": 0, "reused_tokens": 0, "failed": 0}
 
     # ------------------------------------------------------------------ queue
     def add(self, request: Request) -> None:
@@ -314,6 +314,25 @@ class Scheduler:
         """End a request for a reason that the engine finds (a stop string in its text)."""
         if not r.finished:
             self._finish(r, reason)
+
+    def fail(self, requests: Sequence[Request], reason: str = "error") -> list[Request]:
+        """End the requests of a step that failed.  Their pages go back *unpublished*: what the step wrote may be
+        incomplete, so none of it may become known to later requests (pages that earlier, good steps of the same
+        request published stay known).  Requests that wait, and running ones that are not named, are untouched
+        (acvram/engine/runner.py:1329-1338).  Returns the requests it ended."""
+        ended = []
+        for r in requests:
+            if r.finished or r in ended:
+                continue
+            r.finished, r.finish_reason = True, reason
+            if r in self.running:
+                self.running.remove(r)
+                self.manager.release(r.request_id)          # no keys: nothing is published on the way out
+            elif r in self.waiting:
+                self.waiting.remove(r)
+            ended.append(r)
+        self.counters["failed"] += len(ended)
+        return ended
 
     # ------------------------------------------------------------------ internals
     def _finish(self, r: Request, reason: str) -> None:

@@ -89,6 +89,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.restype = c_int
     lib.acv_set_pdl.argtypes = [c_int]
     lib.acv_set_pdl.restype = None
+    lib.acv_gemm_tc_test_fault.argtypes = [c_int, c_int]
+    lib.acv_gemm_tc_test_fault.restype = None
 
 
 LAUNCHES = 0   # kernels of this package launched so far (library matrix products are not counted)
@@ -344,6 +346,32 @@ def gemm_tc_takes(x: torch.Tensor, w: torch.Tensor) -> bool:
     """The tensor-core kernel needs 16-byte aligned rows: K and the row strides multiples of 8."""
     return (x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
             and w.data_ptr() % 16 == 0 and x.stride(1) == 1 and w.stride(1) == 1)
+
+
+def status_word(device) -> torch.Tensor:
+    """The int32 word (on ``device``) into which the tensor-core kernels write a code when one of their bounded
+    waits runs out (0 otherwise).  The engine copies it to the host with every step's tokens."""
+    device = torch.device(device)
+    if device.type == "cuda" and device.index is None:
+        device = torch.device("cuda", torch.cuda.current_device())
+    return _gemm_buffers(device, 0, 0)[2]
+
+
+def reset_after_failure() -> None:
+    """After a step whose kernels gave up a wait: the status word back to 0, and the arrival counters of the
+    split products and of the split attention back to 0 (a CTA that gave up never arrived at its tile)."""
+    for _, cnt, status in _gemm_scratch.values():
+        status.zero_()
+        cnt.zero_()
+    for _, _, cnt in _scratch.values():
+        cnt.zero_()
+
+
+def gemm_tc_test_fault(wait_limit: int, skip_k_block: int) -> None:
+    """For the test of the bounded waits: the next tensor-core product of this process polls each barrier at most
+    ``wait_limit`` times and never loads k-block ``skip_k_block``, so it gives up, frees what it holds, returns,
+    and leaves the wait's code in the status word.  Nothing faults, traps or hangs."""
+    library().acv_gemm_tc_test_fault(int(wait_limit), int(skip_k_block))
 
 
 def gemm_status(device=None) -> int:

@@ -314,6 +314,56 @@ def test_decode_kernel_twice_leaves_its_counters_clean(ops):
         torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
 
 
+def _decode_direct(ops, NH, NKV, D, page, lens, n_splits, cluster_merge, seed, spike=None):
+    """The split-KV kernel called by itself (every page filled at random), against the float32 reference."""
+    dtype = torch.bfloat16
+    B = len(lens)
+    n_pages = sum((l + page - 1) // page for l in lens) + 3
+    kp, vp, table = _paged_setup(B, lens, NKV, D, page, dtype, n_pages, seed)
+    kp.copy_(rnd(*kp.shape, dtype=dtype, seed=seed + 1))
+    vp.copy_(rnd(*vp.shape, dtype=dtype, seed=seed + 2))
+    q = rnd(B, (NH + 2 * NKV) * D, dtype=dtype, seed=seed + 3)
+    if spike is not None:
+        b, j = spike
+        pg = int(table[b, j // page])
+        for h in range(NH):
+            q[b, h * D:(h + 1) * D] = (kp[pg, h // (NH // NKV), j % page].float() * 3.0).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    kv_len, ar = i32(lens), i32(list(range(B)))
+    out1 = torch.full((B, NH * D), 7.0, device="cuda", dtype=dtype)
+    out2 = torch.zeros_like(out1)
+    splits = n_splits or ops.decode_splits(B, NKV, max(lens))
+    ops.attention_decode(q, out1, kp, vp, ar, ar, B, kv_len, table, NH, NKV, D, D ** -0.5, 0, splits, max(lens),
+                         cluster_merge=cluster_merge)
+    ref.attention_generic(q, out2, kp, vp, i32([l - 1 for l in lens]), ar, table, NH, NKV, D, D ** -0.5, 0)
+    return out1, out2, splits
+
+
+@pytest.mark.parametrize("n_splits", [3, 9, 16])
+def test_decode_attention_merge_through_scratch_memory(ops, n_splits):
+    """Partial results in scratch memory and the merge by the CTA that arrives last (what more than 8 splits, i.e.
+    long contexts, use; up to 8 splits ordinarily merge inside a cluster): twice in a row with different shapes,
+    so that a counter that did not return to zero or a partial result left over from the first call would show."""
+    for seed, NH, NKV, D, page, lens in ((82, 8, 2, 128, 16, [700, 300, 1, 2100]), (83, 6, 2, 64, 8, [129, 1500, 90]),
+                                         (84, 8, 2, 128, 16, [640, 33])):
+        o1, o2, _ = _decode_direct(ops, NH, NKV, D, page, lens, n_splits, cluster_merge=False, seed=seed)
+        torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+def test_decode_attention_long_context_chooses_many_splits(ops):
+    """About 10 000 keys: the split count that serving computes is above 8, the merge goes through scratch memory
+    and block-table entries beyond the part cached in shared memory are read; one far key at a split's edge carries
+    the answer for request 0."""
+    lens = [10000, 517]
+    assert ops.decode_splits(len(lens), 2, max(lens)) > 8
+    n = ops.decode_splits(len(lens), 2, max(lens))
+    per = -(-max(lens) // n)
+    for j in (per - 1, per, 5 * per, 9999, 0):
+        o1, o2, splits = _decode_direct(ops, 8, 2, 128, 16, lens, None, cluster_merge=True, seed=85 + j % 7, spike=(0, j))
+        assert splits == n
+        torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
 # ----------------------------------------------------------------------------- tcgen05 matrix product
 GEMM_SHAPES = [
     # (M, N, K): decode-like (swapped roles) and prefill-like, with edges that fill no tile
@@ -335,6 +385,20 @@ def test_gemm_tc(ops, M, N, K, out_dtype):
     torch.testing.assert_close(out.double(), want, **t)
 
 
+@pytest.mark.parametrize("M,K", [(8, 512), (1, 4096), (300, 256)])
+def test_gemm_tc_at_the_real_vocabulary(ops, M, K):
+    """The output head of the real models: 151 936 rows of weights, float32 logits (1187 tiles of 128 rows)."""
+    N = 151936
+    x = rnd(M, K, dtype=torch.bfloat16, seed=98)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=99)
+    out = torch.full((M, N), 3.0, device="cuda", dtype=torch.float32)
+    ops.gemm_tc(x, w, out, static_weights=True)
+    assert ops.gemm_status() == 0
+    for n0 in range(0, N, 32768):        # the reference in pieces: a double copy of the whole weight is not needed
+        want = x.double() @ w[n0:n0 + 32768].double().T
+        torch.testing.assert_close(out[:, n0:n0 + 32768].double(), want, rtol=1e-4, atol=1e-4)
+
+
 @pytest.mark.parametrize("plan", [(1, 16, 1), (1, 16, 4), (1, 32, 3), (1, 64, 2), (1, 128, 5), (0, 64, 1), (0, 128, 2),
                                   (0, 256, 1), (0, 256, 3)])
 def test_gemm_tc_every_tile_shape_and_split(ops, plan):
@@ -349,6 +413,30 @@ def test_gemm_tc_every_tile_shape_and_split(ops, plan):
         assert ops.gemm_status() == 0
         t = dict(rtol=1e-4, atol=1e-4) if out_dtype == torch.float32 else tol(torch.bfloat16)
         torch.testing.assert_close(out.double(), x.double() @ w.double().T, **t)
+
+
+@pytest.mark.parametrize("M,plan", [(8, None), (8, (1, 16, 4, 4, 0)), (300, None)])
+def test_gemm_tc_wait_that_runs_out_leaves_its_code_and_returns(ops, M, plan):
+    """A bounded wait made to run out, without a fault: the product is told to poll each barrier a few thousand
+    times at most and never to load one k-block.  It has to give up, free what it holds and return, with the
+    wait's code in the status word; after the counters are cleared the next launch of the same shape is right.
+    M = 8: swapped roles, the splits of K as a cluster / through the work space; M = 300: tokens on the rows."""
+    N, K = 512, 4096
+    x = rnd(M, K, dtype=torch.bfloat16, seed=190)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=191)
+    want = x.double() @ w.double().T
+    assert ops.gemm_status() == 0
+    ops.gemm_tc_test_fault(1 << 12, 5)
+    ops.gemm_tc(x, w, torch.zeros(M, N, device="cuda", dtype=torch.float32), plan)
+    torch.cuda.synchronize()                 # returns: the kernel ended by itself
+    assert ops.gemm_status() in (1, 2, 3, 4)
+    ops.reset_after_failure()
+    assert ops.gemm_status() == 0
+    for _ in range(2):
+        out = torch.zeros(M, N, device="cuda", dtype=torch.float32)
+        ops.gemm_tc(x, w, out, plan)
+        torch.testing.assert_close(out.double(), want, rtol=1e-4, atol=1e-4)
+    assert ops.gemm_status() == 0
 
 
 def test_gemm_tc_strided_rows_and_repeat(ops):

@@ -115,9 +115,12 @@ def play_mixed(tr: Trace, reqs, tag: str, seed: int, max_live: int = 4, tail: in
 
 
 # --------------------------------------------------------------------------- running
-def run_trace(folder: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int, page_size: int | None = None) -> dict:
+def run_trace(folder: str, dtype: str, tr: Trace, out_dir: str, max_tokens: int, page_size: int | None = None,
+              max_requests: int | None = None) -> dict:
     env = dict(os.environ)
     extra = ["--page-size", str(page_size)] if page_size else []
+    if max_requests:
+        extra += ["--max-requests", str(max_requests)]
     proc = subprocess.Popen([sys.executable, TRACE_RUN, "--model", folder, "--dtype", dtype, "--out", out_dir,
                              "--max-tokens", str(max_tokens), *extra], stdin=subprocess.PIPE, stdout=subprocess.PIPE,
                             text=True, env=env)
@@ -184,7 +187,7 @@ def worst(got, ref, modes):
     return {modes[m]: v for m, v in out.items()}
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C", "E", "F"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "F"])
 def test_replay_float32(name, tiny_folders, plain_logits, tmp_path):
     cfg = json.load(open(os.path.join(tiny_folders[name], "config.json")))
     tr, reqs, modes = build_full_trace(name, cfg["vocab_size"])
@@ -256,3 +259,114 @@ def test_replay_pages_are_reused(tiny_folders):
     tr, reqs, _ = build_full_trace("A", cfg["vocab_size"])
     total = sum((len(v) + 15) // 16 for v in reqs.values())
     assert total * 5 > tr.live_peak // 16
+
+
+# --------------------------------------------------------------------------- the steps that serving runs
+def play_serving_steps(tr: Trace, decoders: dict[str, list[int]], bigs: list[tuple[str, list[int], list[int]]]):
+    """What a scheduler with a budget of a thousand tokens or two makes: requests that decode, one token each, beside
+    a long portion of another request's prompt, in one step.  The decoders' prompts run first, all in one step
+    (several portions of a hundred tokens or more side by side); then every portion of every big request runs beside
+    one token of each decoder; a big request that ends gives its pages to the next."""
+    n_steps = sum(len(portions) for _, _, portions in bigs)
+    tr.step({name: ids[:len(ids) - n_steps] for name, ids in decoders.items()})
+    at = {name: len(ids) - n_steps for name, ids in decoders.items()}
+    k = 0
+    for name, ids, portions in bigs:
+        assert sum(portions) == len(ids)
+        pos = 0
+        for n in portions:
+            k += 1
+            parts = {d: decoders[d][at[d]:at[d] + 1] for d in decoders}
+            parts[name] = ids[pos:pos + n]
+            pos += n
+            end = [name] if pos == len(ids) else []
+            if k == n_steps:
+                end += list(decoders)
+            tr.step(parts, end=end)
+            for d in decoders:
+                at[d] += 1
+
+
+SERVING = {   # decoders' lengths; big requests as lists of portions
+    "F": ([150, 301, 97], [[600, 129, 171], [257, 443]]),
+    "R": ([150, 301, 97], [[1024, 129, 147], [257, 443]]),
+}
+
+
+def bound_for(dtype: str, ref: dict, ref16: dict | None) -> float:
+    if dtype == "float32":
+        return 2e-5 * max(1.0, max(float(np.abs(v).max()) for v in ref.values()))
+    return 2.5 * max(float(np.abs(ref16[r] - ref[r]).max()) for r in ref)
+
+
+_PLAIN: dict = {}     # the plain implementation's logits, kept between the parametrisations of a test
+
+
+def plain_cached(cfg, t, ids, dtype=torch.float32):
+    key = (json.dumps(cfg, sort_keys=True), tuple(ids), dtype)
+    if key not in _PLAIN:
+        _PLAIN[key] = plain_qwen3.forward_logits(cfg, t, ids, dtype).numpy()
+    return _PLAIN[key]
+
+
+def check_against_plain(got: dict, reqs: dict[str, list[int]], cfg, t, dtype: str, what: str):
+    ref = {rid: plain_cached(cfg, t, ids) for rid, ids in reqs.items()}
+    ref16 = None
+    if dtype == "bfloat16":
+        ref16 = {rid: plain_cached(cfg, t, ids, torch.bfloat16) for rid, ids in reqs.items()}
+    bound = bound_for(dtype, ref, ref16)
+    assert len(got) == sum(len(v) for v in reqs.values())
+    worst_d, where = 0.0, None
+    for (rid, pos), row in got.items():
+        d = float(np.abs(row - ref[rid][pos]).max())
+        if d > worst_d:
+            worst_d, where = d, (rid, pos)
+    assert worst_d <= bound, f"{what}: max |logit - plain| = {worst_d:.3e} at request/position {where} (bound {bound:.3e})"
+
+
+@pytest.mark.parametrize("name,dtype,page", [("F", "float32", None), ("F", "bfloat16", None), ("F", "bfloat16", 64),
+                                             ("R", "float32", None), ("R", "bfloat16", None), ("R", "bfloat16", 64)])
+def test_replay_long_portions_beside_decoding_requests(name, dtype, page, tiny_folders, plain_models, real_size_model,
+                                                      tmp_path):
+    """Portions of 129 to 1024 tokens beside three requests that decode, in one step: the products with tokens on
+    the tile's rows and the q,k,v epilogue over rows of different requests, the prompt attention and the decode
+    attention in the same step."""
+    if name == "R":
+        folder, cfg, t = real_size_model
+    else:
+        folder, (cfg, t) = tiny_folders[name], plain_models[name]
+    dec_lens, big_portions = SERVING[name]
+    decoders = {f"d{i}": random_ids(cfg["vocab_size"], n, 300 + i) for i, n in enumerate(dec_lens)}
+    bigs = [(f"big{i}", random_ids(cfg["vocab_size"], sum(por), 400 + i), por) for i, por in enumerate(big_portions)]
+    tr = Trace()
+    play_serving_steps(tr, decoders, bigs)
+    got = run_trace(folder, dtype, tr, str(tmp_path), tr.live_peak, page)
+    reqs = {**decoders, **{n: ids for n, ids, _ in bigs}}
+    check_against_plain(got, reqs, cfg, t, dtype, "long portions beside decoding")
+
+
+def play_many_decoding(tr: Trace, reqs: dict[str, list[int]], n_decode: int, per_step: int = 8):
+    names = list(reqs)
+    for i in range(0, len(names), per_step):
+        tr.step({n: reqs[n][:len(reqs[n]) - n_decode] for n in names[i:i + per_step]})
+    for k in range(n_decode, 0, -1):
+        tr.step({n: reqs[n][len(reqs[n]) - k:len(reqs[n]) - k + 1] for n in names}, end=names if k == 1 else [])
+
+
+@pytest.mark.parametrize("name,dtype,live", [("F", "bfloat16", 9), ("F", "bfloat16", 33), ("F", "bfloat16", 65),
+                                             ("F", "float32", 33), ("D", "bfloat16", 65), ("R", "bfloat16", 9),
+                                             ("R", "bfloat16", 65)])
+def test_replay_many_requests_decoding_together(name, dtype, live, tiny_folders, plain_models, real_size_model, tmp_path):
+    """Decode steps of 9, 33 and 65 live requests (the captured graphs' buckets of 16, 64 and 128 rows, the
+    products' tiles of 16 to 128 tokens, the attention with and without a split of the context)."""
+    if name == "R":
+        folder, cfg, t = real_size_model
+    else:
+        folder, (cfg, t) = tiny_folders[name], plain_models[name]
+    rng = random.Random(live)
+    reqs = {f"q{i}": random_ids(cfg["vocab_size"], rng.choice([7, 12, 20, 33, 49, 64, 65, 90]) if name != "R"
+                                else rng.choice([6, 9, 17, 30]), 500 + i) for i in range(live)}
+    tr = Trace()
+    play_many_decoding(tr, reqs, n_decode=4)
+    got = run_trace(folder, dtype, tr, str(tmp_path), tr.live_peak, None, max_requests=live)
+    check_against_plain(got, reqs, cfg, t, dtype, f"{live} requests decoding")

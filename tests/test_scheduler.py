@@ -376,3 +376,38 @@ def test_full_pages_are_known_while_their_request_still_runs():
     while not s.idle:
         run_step(m, s)
     assert len(a.output) == 8 and len(b.output) == 2 and m.free_pages() == [32]
+
+
+def test_a_failed_step_gives_its_pages_back_unpublished_and_leaves_the_others():
+    """Scheduler.fail: the named requests end with "error", their pages are free again and not known to later
+    requests; a running request that is not named and a waiting one go on (acvram/engine/runner.py:1329-1338)."""
+    m = CacheManager(CachePlan([PagedNeed(1, 8, 0)] * 2), 4, 16, 4, enable_prefix_cache=True)
+    s = Scheduler(m, 2, 8, 256)
+    a, b, c = req(0, 11), Request("rb", list(range(50, 56)), SamplingParams(temperature=0.0, max_tokens=3), 1), req(2, 5)
+    for r in (a, b, c):
+        s.add(r)
+    run_step(m, s)                                   # a's first 8 tokens: two full pages, published as they fill
+    plan = s.schedule()                              # a's last 3 tokens and b's first 5
+    assert {e.request.request_id for e in plan.entries} == {"r0", "rb"}
+    free_before = m.free_pages()[0]
+    ended = s.fail([e.request for e in plan.entries if e.request is a])
+    assert ended == [a] and a.finished and a.finish_reason == "error" and a not in s.running
+    assert b in s.running and c in s.waiting and s.counters["failed"] == 1
+    m.check()
+    assert m.free_pages()[0] == free_before + 3      # all three pages of a are back
+    keys = m.page_keys(a.tokens)
+    pool = m.paged_groups[0].pool
+    assert pool.lookup(keys[0]) is not None and pool.lookup(keys[1]) is not None     # from the good step
+    assert len(keys) == 2                             # the third page never filled: nothing of the failed step is known
+    assert s.fail([a]) == []                          # ending it twice does nothing
+    # b and c run to their ends
+    for e in plan.entries:
+        if e.request is b:
+            m.advance("rb", e.start + e.count)
+    s.commit(type(plan)([e for e in plan.entries if e.request is b]), [7], ())
+    for _ in range(20):
+        if s.idle:
+            break
+        run_step(m, s)
+    assert s.idle and b.finish_reason == "length" and c.finish_reason == "length"
+    m.check()
