@@ -212,6 +212,11 @@ class PagedGroup:
             self.first_live[request] = releasable
         return len(freed)
 
+    def set_page(self, request, index: int, page: int) -> None:
+        """Put ``page`` at ``index`` of the request's block table (the books of the pool are the caller's to keep:
+        tests use it to make a table wrong on purpose)."""
+        self.tables[request][index] = page
+
     def drop(self, request) -> None:
         table = self.tables.pop(request)
         self.first_live.pop(request)

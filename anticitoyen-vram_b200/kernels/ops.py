@@ -89,6 +89,10 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.restype = c_int
     lib.acv_set_pdl.argtypes = [c_int]
     lib.acv_set_pdl.restype = None
+    lib.acv_random_normal.argtypes = [P, LL, ctypes.c_ulonglong, F, F, P, P, I, P]
+    lib.acv_random_normal.restype = c_int
+    lib.acv_random_int.argtypes = [P, LL, ctypes.c_ulonglong, ctypes.c_uint, P]
+    lib.acv_random_int.restype = c_int
     lib.acv_gemm_tc_test_fault.argtypes = [c_int, c_int]
     lib.acv_gemm_tc_test_fault.restype = None
 
@@ -166,6 +170,26 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     _need_cuda(gate_up, out)
     T, I = out.shape
     _check(library().acv_swiglu(_p(gate_up), _p(out), T, I, dtype_code(out.dtype), _stream()), "swiglu")
+    return out
+
+
+def random_normal(out: torch.Tensor, key: int, mean: float, std: float, t1: torch.Tensor, t2: torch.Tensor) -> torch.Tensor:
+    """out (float32 or bfloat16, contiguous) = mean + std * z, z the normal deviates of the Philox stream keyed by
+    ``key``; t1, t2: the quantile tables (weights/random_init.py).  Bit-equal to the host's arithmetic."""
+    _need_cuda(out, t1, t2)
+    if not out.is_contiguous() or t1.numel() != 1024 or t2.numel() != 1025:
+        raise KernelError("random_normal: a contiguous output and tables of 1024 and 1025 floats are wanted")
+    with torch.cuda.device(out.device):
+        _check(library().acv_random_normal(_p(out), out.numel(), key, mean, std, _p(t1), _p(t2), dtype_code(out.dtype),
+                                           _stream()), "random_normal")
+    return out
+
+
+def random_int(out: torch.Tensor, key: int, mask: int) -> torch.Tensor:
+    """out (int32, contiguous) = words of the Philox stream keyed by ``key``, and-ed with ``mask``."""
+    _need_cuda(out)
+    with torch.cuda.device(out.device):
+        _check(library().acv_random_int(_p(out), out.numel(), key, mask, _stream()), "random_int")
     return out
 
 

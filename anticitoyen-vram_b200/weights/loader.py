@@ -7,17 +7,23 @@ acvram/engine/loader.py:403-406, 1013-1033).  The reference reports a missing
 name with a KeyError at first use and never checks shapes
 (acvram/engine/loader.py:506-508); here the whole file is checked against the
 model's needs first and one error lists everything that is missing, unexpected
-or of the wrong shape.
+or of the wrong shape.  Tensors that the model does not use are no fault by
+themselves (the reference ignores them): alone they are listed once in a warning
+and skipped, unless ``strict`` asks for the error; beside another fault they are
+listed in the error with it.
 
-Storage rule: floating tensors stored in 16 bits are kept as bfloat16, tensors
-stored in 32-bit floating point stay float32, integer tables become int32.  The
-parts cast what they compute with.
+Storage rule: bfloat16 stays bfloat16, float32 stays float32, integer tables
+become int32.  float16 becomes float32, which holds every float16 value exactly
+(bfloat16 would drop three bits of its mantissa): a float32 run then computes
+with the file's own values, and a bfloat16 run rounds them once, where the parts
+cast what they compute with.
 """
 
 from __future__ import annotations
 
 import json
 import os
+import warnings
 from typing import Mapping
 
 import torch
@@ -25,7 +31,7 @@ from safetensors import safe_open
 
 from .needs import TensorNeed, WeightError
 
-_KEEP = {torch.bfloat16: torch.bfloat16, torch.float16: torch.bfloat16, torch.float32: torch.float32,
+_KEEP = {torch.bfloat16: torch.bfloat16, torch.float16: torch.float32, torch.float32: torch.float32,
          torch.int32: torch.int32, torch.int64: torch.int32, torch.int16: torch.int32, torch.int8: torch.int32,
          torch.uint8: torch.int32}
 
@@ -46,9 +52,15 @@ def _files_of(folder: str) -> dict[str, list[str] | None]:
     raise FileNotFoundError(f"no model.safetensors or model.safetensors.index.json in {folder}")
 
 
+class UnusedTensorsWarning(UserWarning):
+    """The weight file holds tensors that the model does not read."""
+
+
 def load_tensors(folder: str | os.PathLike, needs: Mapping[str, TensorNeed],
-                 device: str | torch.device = "cpu") -> dict[str, torch.Tensor]:
-    """Return ``{name: tensor}`` for every needed tensor that the folder holds."""
+                 device: str | torch.device = "cpu", strict: bool = False) -> dict[str, torch.Tensor]:
+    """Return ``{name: tensor}`` for every needed tensor that the folder holds.
+
+    ``strict``: tensors that the model does not use are an error even when nothing else is wrong."""
     folder = os.fspath(folder)
     files = _files_of(folder)
     present: dict[str, tuple[str, tuple[int, ...]]] = {}
@@ -65,8 +77,12 @@ def load_tensors(folder: str | os.PathLike, needs: Mapping[str, TensorNeed],
         unexpected = sorted(n for n in present if n not in needs)
         wrong_shape = [(n, present[n][1], need.shape) for n, need in needs.items()
                        if n in present and present[n][1] != tuple(need.shape)]
-        if missing or unexpected or wrong_shape:
+        if missing or wrong_shape or (unexpected and strict):
             raise WeightError(folder, missing, unexpected, wrong_shape)
+        if unexpected:
+            shown = ", ".join(unexpected[:8]) + (f" and {len(unexpected) - 8} more" if len(unexpected) > 8 else "")
+            warnings.warn(f"weights in {folder}: {len(unexpected)} tensors that the model does not use are skipped: {shown}",
+                          UnusedTensorsWarning, stacklevel=2)
         out: dict[str, torch.Tensor] = {}
         wrong_dtype = []
         for name in needs:

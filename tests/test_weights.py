@@ -71,6 +71,58 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
         assert word in msg
 
 
+def test_tensors_the_model_does_not_use_are_a_warning_not_an_error(tmp_path):
+    """The reference ignores what it does not read (acvram/engine/loader.py:506-508 fails on a missing name only);
+    here such tensors are named once in a warning, or refused with ``strict``."""
+    from acvram_b200.weights.loader import UnusedTensorsWarning
+    write_random_model(tiny_config("A"), tmp_path, seed=0)
+    path = os.path.join(tmp_path, "model.safetensors")
+    t = load_file(path)
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    save_file(t, path)
+    _, plan = plan_of_folder(tmp_path)
+    with pytest.warns(UnusedTensorsWarning, match="rotary_emb.inv_freq"):
+        got = load_tensors(tmp_path, needs_of_plan(plan))
+    assert "model.layers.0.self_attn.rotary_emb.inv_freq" not in got and len(got) == len(t) - 1
+    with pytest.raises(WeightError) as err:
+        load_tensors(tmp_path, needs_of_plan(plan), strict=True)
+    assert err.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and not err.value.missing
+
+
+def test_float16_files_keep_their_values(tmp_path):
+    """float16 has three bits of mantissa more than bfloat16: it is kept as float32 (exact), not rounded on reading."""
+    write_random_model(tiny_config("A"), tmp_path, seed=0)
+    path = os.path.join(tmp_path, "model.safetensors")
+    t = load_file(path)
+    half = {k: (v.float() * 1.001).to(torch.float16) for k, v in t.items()}      # values that bfloat16 cannot hold
+    save_file(half, path)
+    _, plan = plan_of_folder(tmp_path)
+    got = load_tensors(tmp_path, needs_of_plan(plan))
+    assert all(v.dtype == torch.float32 for v in got.values())
+    assert all(torch.equal(got[k], half[k].float()) for k in half)
+    assert any(not torch.equal(got[k], got[k].bfloat16().float()) for k in half)
+
+
+def test_random_values_are_normal_and_counter_based():
+    """The generator behind the random weights: Philox words (known-answer vectors of Random123), normal deviates
+    from tabulated quantiles; a tensor's values depend on (seed, name) alone, element by element."""
+    import numpy as np
+    from acvram_b200.weights import TensorNeed, random_tensor
+    from acvram_b200.weights.random_init import normal_of_words, philox_words
+    # Random123's known answers for philox4x32-10: zero counter and key; all bits set
+    assert philox_words(0, 0, 1).tolist() == [0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8]
+    z = normal_of_words(philox_words(12345, 0, 1 << 18))
+    assert abs(float(z.mean())) < 5e-3 and abs(float(z.std()) - 1.0) < 5e-3
+    assert abs(float((np.abs(z) > 1.959964).mean()) - 0.05) < 2e-3 and abs(float((np.abs(z) > 3.290527).mean()) - 0.001) < 3e-4
+    assert float(np.abs(z).max()) < 6.3
+    big = random_tensor("w", TensorNeed((50, 30)), 7, "cpu", torch.float32)
+    small = random_tensor("w", TensorNeed((10, 30)), 7, "cpu", torch.float32)
+    assert torch.equal(big[:10], small), "element i depends on (seed, name, i) only"
+    assert not torch.equal(small, random_tensor("v", TensorNeed((10, 30)), 7, "cpu", torch.float32))
+    table = random_tensor("t", TensorNeed((9,), "table"), 7)
+    assert table.dtype == torch.int32 and int(table.min()) >= 0 and int(table.max()) < 2 ** 15
+
+
 def test_untied_model_needs_its_head(tmp_path):
     write_random_model(tiny_config("B"), tmp_path, seed=0)
     path = os.path.join(tmp_path, "model.safetensors")
