@@ -34,6 +34,14 @@ holds.  Reuse is switched on by ``enable_prefix_cache`` and needs every group to
 keep all keys (a window gives pages back as it goes, and a state of fixed size
 has no page to take over).
 
+The block tables also live on the device, one row for each live request, and
+stay there between steps (the reference rebuilds a padded table on the host and
+copies it every step, acvram/engine/lot.py:98-118).  The manager gives every
+request a *row* when it is admitted and notes each entry that changes (a page
+reserved, taken over, or given back by a window); ``take_updates`` hands those
+(row, column, page) triples to the step that is being built, which sends them
+along with its tokens.
+
 This file is host-side bookkeeping only and imports no torch at module level;
 ``CacheStorage`` holds the tensors.
 """
@@ -183,6 +191,13 @@ class PagedGroup:
         self.pool = PagePool(num_pages)
         self.tables: dict[Hashable, list[int]] = {}
         self.first_live: dict[Hashable, int] = {}  # first page index not yet released by the window
+        self.rows: dict[Hashable, int] = {}        # request -> its row of the device table (the manager's dict)
+        self.dirty: list[tuple[int, int, int]] = []   # (row, column, page) entries that the device table lacks
+
+    def _note(self, request, first_col: int, pages) -> None:
+        row = self.rows.get(request)
+        if row is not None:
+            self.dirty.extend((row, first_col + i, p) for i, p in enumerate(pages))
 
     def pages_for(self, length: int) -> int:
         return (length + self.page_size - 1) // self.page_size
@@ -193,7 +208,12 @@ class PagedGroup:
     def grow(self, request, length: int) -> None:
         n = self.missing(request, length)
         if n:
-            self.tables[request].extend(self.pool.allocate(n))
+            self.extend(request, self.pool.allocate(n))
+
+    def extend(self, request, pages: Sequence[int]) -> None:
+        table = self.tables[request]
+        self._note(request, len(table), pages)
+        table.extend(pages)
 
     def trim(self, request, kv_len: int) -> int:
         """Give back the pages whose every key is out of the window of any later query."""
@@ -208,6 +228,7 @@ class PagedGroup:
         for i in range(start, releasable):
             table[i] = -1
         if freed:
+            self._note(request, start, [-1] * len(freed))
             self.pool.release(freed)
             self.first_live[request] = releasable
         return len(freed)
@@ -216,6 +237,7 @@ class PagedGroup:
         """Put ``page`` at ``index`` of the request's block table (the books of the pool are the caller's to keep:
         tests use it to make a table wrong on purpose)."""
         self.tables[request][index] = page
+        self._note(request, index, [page])
 
     def drop(self, request) -> None:
         table = self.tables.pop(request)
@@ -240,6 +262,7 @@ class PagedGroup:
         for p in pages:
             self.pool.share(p)
         self.tables[request] = list(pages)
+        self._note(request, 0, pages)
 
     def publish(self, request, keys: Sequence[bytes]) -> None:
         for p, key in zip(self.tables[request], keys):
@@ -321,6 +344,12 @@ class CacheManager:
         self._paged = [g for g in self.groups if isinstance(g, PagedGroup)]      # the groups never change
         self._state = [g for g in self.groups if isinstance(g, StateGroup)]
         self.lengths: dict[Hashable, int] = {}
+        # rows of the device block tables: one for each live request, the same in every group; row
+        # ``max_requests`` belongs to nobody and stays at -1 (padding rows of a fixed-shape batch point there)
+        self.rows: dict[Hashable, int] = {}
+        self._free_rows = list(range(max_requests - 1, -1, -1))
+        for g in self._paged:
+            g.rows = self.rows
         # pages are taken over only where every group keeps all keys in pages
         self.prefix_reuse = bool(enable_prefix_cache) and bool(self.groups) and all(
             isinstance(g, PagedGroup) and g.need.window <= 0 for g in self.groups)
@@ -406,6 +435,7 @@ class CacheManager:
         slots = {}
         reuse, _ = self.reusable(keys, num_tokens)
         keys = keys[:reuse // self.page_size]
+        self.rows[request] = self._free_rows.pop()
         for gi, g in enumerate(self.groups):
             if isinstance(g, PagedGroup):
                 g.tables[request] = []
@@ -428,7 +458,7 @@ class CacheManager:
             raise OutOfPages(f"request {request!r} cannot grow to {length} tokens: free {self.free_pages()}")
         for n, g in zip(need, self._paged):
             if n:
-                g.tables[request].extend(g.pool.allocate(n))
+                g.extend(request, g.pool.allocate(n))
 
     def advance(self, request, length: int) -> None:
         """The request now holds ``length`` tokens in its pages."""
@@ -465,6 +495,26 @@ class CacheManager:
             else:
                 g.give_back(request)
         del self.lengths[request]
+        self._free_rows.append(self.rows.pop(request))
+
+    # ------------------------------------------------------------------ the device's copy of the block tables
+    @property
+    def null_row(self) -> int:
+        return self.max_requests
+
+    def take_updates(self) -> list[list[tuple[int, int, int]]]:
+        """For each paged group the (row, column, page) entries that changed since the last call, oldest first."""
+        out = []
+        for g in self._paged:
+            out.append(g.dirty)
+            g.dirty = []
+        return out
+
+    def resync(self) -> None:
+        """Note every entry of every live request again (after a step failed somewhere between taking the
+        updates and sending them, the device's tables cannot be trusted)."""
+        for g in self._paged:
+            g.dirty = [(self.rows[r], c, p) for r, table in g.tables.items() for c, p in enumerate(table)]
 
     # ------------------------------------------------------------------ views
     def block_table(self, request, group: int) -> list[int]:
@@ -493,3 +543,6 @@ class CacheManager:
         for g in self.state_groups:
             if len(set(g.slot_of.values())) != len(g.slot_of) or len(g.slot_of) + g.num_free != g.max_requests:
                 raise CacheAccountingError("state slots do not add up")
+        if (set(self.rows) != set(self.lengths) or len(set(self.rows.values())) != len(self.rows)
+                or sorted(list(self.rows.values()) + self._free_rows) != list(range(self.max_requests))):
+            raise CacheAccountingError("rows of the block tables do not add up")

@@ -16,17 +16,28 @@ class CacheStorage:
     reference keeps ``[num_blocks, 16, kv_heads, head_dim]`` per layer
     (acvram/memory/kvcache.py:463-469).  State group:
     ``[slots, max_requests, *shape]``.  Everything starts at zero, so that a key
-    that is masked out never brings a NaN into a product."""
+    that is masked out never brings a NaN into a product.
 
-    def __init__(self, manager: CacheManager, device, dtype: torch.dtype) -> None:
+    Beside its pages a paged group has its block table on the device, int32
+    ``[max_requests + 1, width]``: row r belongs to the request that the manager gave row r, the last row to
+    nobody; all entries start at -1 ("no page").  ``max_len`` (tokens) decides the width."""
+
+    def __init__(self, manager: CacheManager, device, dtype: torch.dtype, max_len: int | None = None) -> None:
         self.manager = manager
         self.device = torch.device(device)
         self.dtype = dtype
         self.tensors: list[torch.Tensor] = []
-        for g in manager.groups:
+        self.tables: dict[int, torch.Tensor] = {}       # group index -> the group's block table on the device
+        for gi, g in enumerate(manager.groups):
             if isinstance(g, PagedGroup):
                 shape = (g.num_slots, 2, max(g.pool.num_pages, 1), g.need.num_kv_heads, g.page_size, g.need.head_dim)
                 self.tensors.append(torch.zeros(shape, device=self.device, dtype=dtype))
+                # a request that keeps all its keys can never hold more pages than the pool has
+                tokens = max_len if max_len else g.pool.num_pages * g.page_size
+                if g.need.window <= 0:
+                    tokens = min(tokens, g.pool.num_pages * g.page_size)
+                width = max(1, g.pages_for(tokens))
+                self.tables[gi] = torch.full((manager.max_requests + 1, width), -1, device=self.device, dtype=torch.int32)
             else:
                 sdtype = getattr(torch, g.need.dtype)
                 self.tensors.append(torch.zeros((g.num_slots, g.max_requests, *g.need.shape), device=self.device,
@@ -34,6 +45,11 @@ class CacheStorage:
 
     def bytes(self) -> int:
         return sum(t.numel() * t.element_size() for t in self.tensors)
+
+    @property
+    def max_tokens(self) -> int:
+        """The longest request that every block table has columns for."""
+        return min((t.shape[1] * self.manager.page_size for t in self.tables.values()), default=1 << 30)
 
     def pages(self, cache_slot: int) -> tuple[torch.Tensor, torch.Tensor]:
         """(keys, values) of a cache slot, each ``[num_pages, kv_heads, page_size, head_dim]``."""

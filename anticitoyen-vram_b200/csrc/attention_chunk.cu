@@ -24,7 +24,7 @@ __global__ void __launch_bounds__(AC_THREADS)
 attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                   const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages, const int* __restrict__ tile_seq,
                   const int* __restrict__ tile_q0, const int* __restrict__ cu_q, const int* __restrict__ kv_len,
-                  const int* __restrict__ block_table, int bt_stride, int NH, int NKV, int page_size, int page_shift,
+                  const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift,
                   int pg_cap, int num_pages, float scale, int window) {
     constexpr int CH = D / 8;
     constexpr int TILE_BYTES = AC_BN * D * 2;
@@ -44,7 +44,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
     const int q_len = cu_q[seq + 1] - cu_q[seq];
     const int rows = min(AC_BM, q_len - q0);
     const int pos0 = kv_len[seq] - q_len + q0;          // absolute position of the tile's first query
-    const int* bt = block_table + (size_t)seq * bt_stride;
+    const int* bt = block_table + (size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride;
     const int hi = pos0 + rows - 1;                     // last key any row of the tile sees
     const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
     const int j_first = lo & ~(AC_BN - 1);
@@ -245,7 +245,7 @@ attn_chunk_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ o
 template <int D>
 static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                         const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
-                        const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int page_size,
+                        const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
                         int num_pages, float scale, int window, int max_kv, cudaStream_t stream) {
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
@@ -253,16 +253,12 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
     int pg_cap = max_kv / page_size + 2;
     if (pg_cap > 16384) pg_cap = 16384;
     const int smem = AC_BM * D * 2 + 4 * AC_BN * D * 2 + pg_cap * 4;
-    static int configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_chunk_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
+    static AcvSmemConfig smem_config;          // per kernel instance and device
+    if (int rc = acv_ensure_smem(smem_config, attn_chunk_kernel<D>, smem)) return rc;
     dim3 grid(n_tiles, NH);
     acv_launch(PDL_MISC, attn_chunk_kernel<D>, grid, AC_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, tile_seq,
-        tile_q0, cu_q, kv_len, block_table, bt_stride, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window);
+        tile_q0, cu_q, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window);
     return acv_launch_status();
 }
 
@@ -270,7 +266,7 @@ static int launch_chunk(const void* q, int q_stride, void* out, int out_stride, 
 // the tile's first token among the request's tokens of this step.
 ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                 const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles,
-                                const int* cu_q, const int* kv_len, const int* block_table, int bt_stride, int NH,
+                                const int* cu_q, const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
                                 int NKV, int D, int page_size, int num_pages, float scale, int window, int max_kv,
                                 cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
@@ -279,7 +275,7 @@ ACV_API int acv_attention_chunk(const void* q, int q_stride, void* out, int out_
         ((uintptr_t)out & 3) || (out_stride & 1))
         return ACV_ERR_ALIGN;
 #define AC_ARGS q, q_stride, out, out_stride, k_pages, v_pages, tile_seq, tile_q0, n_tiles, cu_q, kv_len, block_table, \
-                bt_stride, NH, NKV, page_size, num_pages, scale, window, max_kv, stream
+                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, max_kv, stream
     switch (D) {
         case 64: return launch_chunk<64>(AC_ARGS);
         case 128: return launch_chunk<128>(AC_ARGS);

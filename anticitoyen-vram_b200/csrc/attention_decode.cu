@@ -29,8 +29,8 @@ __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                    const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    const int* __restrict__ dec_tokens, const int* __restrict__ dec_seqs,
-                   const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride, int NH, int NKV,
-                   int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
+                   const int* __restrict__ kv_len, const int* __restrict__ block_table, int bt_stride,
+                   const int* __restrict__ bt_rows, int NH, int NKV, int page_size, int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
                    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
                    int cluster_merge) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
@@ -45,11 +45,15 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     ACV_TL(TL_ATTN_DECODE, 0);
     pdl_launch_dependents();
     pdl_wait();
+    // the splits of one cluster write their partial results into rank 0's shared memory at the end: a CTA may do so
+    // only when it knows that rank 0 has started, which is what the first phase of the cluster's barrier tells it
+    const bool in_cluster = cluster_merge && n_splits > 1;
+    if (in_cluster) cluster_arrive();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tok = dec_tokens[item], seq = dec_seqs[item];
     const int n_rep = NH / NKV;
-    const int* bt = block_table + (size_t)seq * bt_stride;
+    const int* bt = block_table + (size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride;   // the request's row of the table
     const int p = kv_len[seq] - 1;
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int n_keys = p + 1 - lo;
@@ -256,6 +260,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     __syncthreads();
 
     const size_t part = ((size_t)item * NKV + kvh) * n_splits + split;
+    if (in_cluster) cluster_wait();          // long passed: the peers arrived when they began
     for (int idx = tid; idx < n_rep * D; idx += AD_THREADS) {
         const int r = idx / D, d = idx % D;
         float M = -INFINITY;
@@ -342,8 +347,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
 template <int D>
 static int launch_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                          const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
-                         const int* block_table, int bt_stride, int NH, int NKV, int page_size, int num_pages,
-                         float scale, int window, int n_splits, float* part_acc, float* part_ml, int* counters,
+                         const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
+                         int num_pages, float scale, int window, int n_splits, float* part_acc, float* part_ml, int* counters,
                          int max_kv, int cluster_merge, cudaStream_t stream) {
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
@@ -356,27 +361,24 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     const int n_rep = NH / NKV;
     const int smem = 16 * D * 2 + 4 * AD_STAGES * 2 * 16 * D * 2 + ((pg_cap + 3) & ~3) * 4 +
                      (cluster_merge ? n_splits * n_rep * (D + 2) * 4 : 0);
-    static int configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
+    static AcvSmemConfig smem_config;          // per kernel instance and device
+    if (int rc = acv_ensure_smem(smem_config, attn_decode_kernel<D>, smem)) return rc;
     dim3 grid(n_dec, NKV, n_splits);
     acv_launch_cluster(PDL_ATTN, dim3(1, 1, cluster_merge ? n_splits : 1), attn_decode_kernel<D>, grid, AD_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
-        dec_seqs, kv_len, block_table, bt_stride, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
+        dec_seqs, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
         n_splits, part_acc, part_ml, counters, cluster_merge);
     return acv_launch_status();
 }
 
+// bt_rows (may be null): the row of block_table that belongs to each request of the batch (null: row = its index).
 // Scratch, given by the caller: part_acc holds n_dec*NKV*n_splits*(NH/NKV)*D floats, part_ml
 // n_dec*NKV*n_splits*(NH/NKV)*2 floats, counters n_dec*NKV ints that are zero before the first call
 // (the kernel leaves them zero).  scratch_floats / scratch_counters say how much the caller gave.
 ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                  const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec,
-                                 const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int D,
-                                 int page_size, int num_pages, float scale, int window, int n_splits, float* part_acc,
+                                 const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH,
+                                 int NKV, int D, int page_size, int num_pages, float scale, int window, int n_splits, float* part_acc,
                                  float* part_ml, int* counters, long long scratch_floats, long long scratch_ml_floats,
                                  long long scratch_counters, int max_kv, int cluster_merge, cudaStream_t stream) {
     if (n_dec <= 0) return 0;
@@ -391,7 +393,7 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
             return ACV_ERR_SCRATCH;
     }
 #define AD_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
-                bt_stride, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, max_kv, \
+                bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, max_kv, \
                 cluster_merge, stream
     switch (D) {
         case 64: return launch_decode<64>(AD_ARGS);
@@ -413,6 +415,8 @@ static __device__ __align__(256) float ad_static_scratch[AD_STATIC_FLOATS];
 // asked for, once per device, with that device current.
 static float* ad_static_address(int* error) {
     static float* address[64] = {nullptr};
+    static std::mutex lock;                     // host threads may make their first calls side by side
+    std::lock_guard<std::mutex> guard(lock);
     int device = 0;
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess || device < 0 || device >= 64) {
@@ -459,7 +463,7 @@ ACV_API int acv_attention_decode_static(const void* q, int q_stride, void* out, 
     cudaError_t e = cudaMemsetAsync(cnt, 0, (size_t)counters * sizeof(int), stream);
     if (e != cudaSuccess) return (int)e;
     return acv_attention_decode(q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len,
-                                block_table, bt_stride, NH, NKV, D, page_size, num_pages, scale, window, n_splits,
+                                block_table, bt_stride, nullptr, NH, NKV, D, page_size, num_pages, scale, window, n_splits,
                                 part_acc, part_ml, cnt, acc_floats, ml_floats, counters, max_kv, 0, stream);
 }
 

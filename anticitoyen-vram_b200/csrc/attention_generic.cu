@@ -17,7 +17,7 @@ template <typename T, int NR>
 __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride,
                                     const T* __restrict__ k_pages, const T* __restrict__ v_pages,
                                     const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                    const int* __restrict__ block_table, int bt_stride, int NH, int NKV, int D,
+                                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, int NH, int NKV, int D,
                                     int page_size, int num_pages, float scale, int window) {
     extern __shared__ float sm_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -28,7 +28,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
     const int kvh = h / (NH / NKV);
     const int p = positions[t];
     const int seq = seq_of_token[t];
-    const int* bt = block_table + (size_t)seq * bt_stride;
+    const int* bt = block_table + (size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride;
     const T* qrow = q + (size_t)t * q_stride + (size_t)h * D;
     for (int e = lane; e < D; e += 32) qs[e] = to_f32(qrow[e]) * scale;
     __syncwarp();
@@ -89,7 +89,7 @@ __global__ void attn_generic_kernel(const T* __restrict__ q, int q_stride, T* __
 template <typename T>
 static int launch_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                           const void* v_pages, const int* positions, const int* seq_of_token, const int* block_table,
-                          int bt_stride, int T_tokens, int NH, int NKV, int D, int page_size, int num_pages,
+                          int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D, int page_size, int num_pages,
                           float scale, int window, cudaStream_t stream) {
     dim3 grid(T_tokens, (NH + AG_WARPS - 1) / AG_WARPS);
     const size_t smem = (size_t)AG_WARPS * D * sizeof(float);
@@ -98,7 +98,7 @@ static int launch_generic(const void* q, int q_stride, void* out, int out_stride
     case N:                                                                                                          \
         attn_generic_kernel<T, N><<<grid, AG_WARPS * 32, smem, stream>>>(                                            \
             (const T*)q, q_stride, (T*)out, out_stride, (const T*)k_pages, (const T*)v_pages, positions,             \
-            seq_of_token, block_table, bt_stride, NH, NKV, D, page_size, num_pages, scale, window);                  \
+            seq_of_token, block_table, bt_stride, bt_rows, NH, NKV, D, page_size, num_pages, scale, window);                  \
         break;
     switch (nr) {
         AG_CASE(1) AG_CASE(2) AG_CASE(3) AG_CASE(4) AG_CASE(5) AG_CASE(6) AG_CASE(7) AG_CASE(8)
@@ -110,18 +110,18 @@ static int launch_generic(const void* q, int q_stride, void* out, int out_stride
 
 ACV_API int acv_attention_generic(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
                                   const void* v_pages, const int* positions, const int* seq_of_token,
-                                  const int* block_table, int bt_stride, int T_tokens, int NH, int NKV, int D,
+                                  const int* block_table, int bt_stride, const int* bt_rows, int T_tokens, int NH, int NKV, int D,
                                   int page_size, int num_pages, float scale, int window, int dtype,
                                   cudaStream_t stream) {
     if (T_tokens <= 0) return 0;
     if (D <= 0 || D > 256 || NKV <= 0 || NH % NKV) return ACV_ERR_SIZE;
     if (dtype == ACV_F32)
         return launch_generic<float>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
-                                     block_table, bt_stride, T_tokens, NH, NKV, D, page_size, num_pages, scale, window,
+                                     block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, page_size, num_pages, scale, window,
                                      stream);
     if (dtype == ACV_BF16)
         return launch_generic<bf16>(q, q_stride, out, out_stride, k_pages, v_pages, positions, seq_of_token,
-                                    block_table, bt_stride, T_tokens, NH, NKV, D, page_size, num_pages, scale, window,
+                                    block_table, bt_stride, bt_rows, T_tokens, NH, NKV, D, page_size, num_pages, scale, window,
                                     stream);
     return ACV_ERR_DTYPE;
 }

@@ -42,6 +42,7 @@ struct AttnTcParams {
     const int* kv_len;
     const int* block_table;
     int bt_stride;
+    const int* bt_rows;         // the row of block_table of each request of the batch (null: its index)
     int NH, NKV, page_size, page_shift, num_pages, window;
     float scale;
     int* status;
@@ -109,7 +110,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int lo = p.window > 0 ? max(0, pos0 - p.window + 1) : 0;
     const int j_first = lo & ~(AT_BN - 1);
     const int n_tiles = (hi - j_first) / AT_BN + 1;
-    const int* bt = p.block_table + (size_t)seq * p.bt_stride;
+    const int* bt = p.block_table + (size_t)(p.bt_rows ? p.bt_rows[seq] : seq) * p.bt_stride;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -339,12 +340,8 @@ template <int D>
 static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p,
                           int n_tiles, cudaStream_t stream) {
     constexpr int SMEM = 2 * (D / 64) * AT_ATOM /*Q of two heads*/ + 4 * (D / 64) * AT_ATOM /*K,V x2*/ + 1024 + 128;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static AcvSmemConfig smem_config;          // per kernel instance and device
+    if (int rc = acv_ensure_smem(smem_config, attn_tc_kernel<D>, SMEM)) return rc;
     const int n_rep = p.NH / p.NKV;
     acv_launch(PDL_MISC, attn_tc_kernel<D>, dim3((unsigned)(n_tiles * (p.NKV * ((n_rep + 1) / 2)))), AT_THREADS, SMEM, stream, mq, mk, mv, p);
     return acv_launch_status();
@@ -355,8 +352,8 @@ static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CU
 // Takes head sizes 64 and 128 and page sizes that are powers of two from 8 to 128.
 ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int out_stride, const void* k_pages,
                              const void* v_pages, const int* tile_seq, const int* tile_q0, int n_tiles, const int* cu_q,
-                             const int* kv_len, const int* block_table, int bt_stride, int NH, int NKV, int D,
-                             int page_size, int num_pages, float scale, int window, int* status, cudaStream_t stream) {
+                             const int* kv_len, const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV,
+                             int D, int page_size, int num_pages, float scale, int window, int* status, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     if (NKV <= 0 || NH % NKV || NH > 65535 || (D != 64 && D != 128)) return ACV_ERR_SIZE;
     if ((long long)n_tiles * NH > 0x7fffffffLL) return ACV_ERR_SIZE;
@@ -378,7 +375,7 @@ ACV_API int acv_attention_tc(const void* q, int q_stride, int T, void* out, int 
     if (rc) return rc;
     AttnTcParams p;
     p.out = (bf16*)out; p.out_stride = out_stride; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.cu_q = cu_q;
-    p.kv_len = kv_len; p.block_table = block_table; p.bt_stride = bt_stride; p.NH = NH; p.NKV = NKV;
+    p.kv_len = kv_len; p.block_table = block_table; p.bt_stride = bt_stride; p.bt_rows = bt_rows; p.NH = NH; p.NKV = NKV;
     p.page_size = page_size; p.page_shift = page_shift; p.num_pages = num_pages; p.window = window; p.scale = scale;
     p.status = status;
     if (D == 64) return launch_attn_tc<64>(mq, mk, mv, p, n_tiles, stream);

@@ -68,6 +68,29 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 
 static inline int acv_launch_status() { return (int)cudaGetLastError(); }
 
+// A kernel's cudaFuncAttributeMaxDynamicSharedMemorySize is a setting of the device that is current: one record
+// of the largest size asked so far for each device (a function-local static per kernel instance), guarded so that
+// host threads may launch side by side.  Returns 0 or the cudaError_t.
+#include <mutex>
+struct AcvSmemConfig {
+    int bytes[64];
+    std::mutex lock;
+};
+template <typename Kernel>
+static inline int acv_ensure_smem(AcvSmemConfig& cfg, Kernel kernel, int smem) {
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= 64) return ACV_ERR_SIZE;
+    std::lock_guard<std::mutex> guard(cfg.lock);
+    if (smem > cfg.bytes[device]) {
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        cfg.bytes[device] = smem;
+    }
+    return 0;
+}
+
 // ----------------------------------------------------------------------------- programmatic dependent launch
 // Kernels of the serving path may be launched so that a kernel begins while the one before it in
 // the stream is still finishing: it lets its successor start at once (pdl_launch_dependents) and
@@ -150,6 +173,11 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
 __device__ __forceinline__ void cluster_store_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
+// The two halves of a cluster barrier, for a CTA that has to know that its peers have started before it
+// writes into their shared memory: arrive early, wait just before the first remote store.  Every thread of
+// every CTA of the cluster executes each half once per phase.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
 // every thread of every CTA of the cluster passes here once (release before, acquire after)
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");

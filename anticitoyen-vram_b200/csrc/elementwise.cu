@@ -247,3 +247,47 @@ ACV_API int acv_swiglu(const void* gu, void* out, int T, int I, int dtype, cudaS
 ACV_API void acv_set_pdl(int classes) { acv_pdl_flag = classes; }
 
 ACV_TL_EXPORT(elementwise)
+
+// ----------------------------------------------------------------------------- block tables kept on the device
+// The block tables of all live requests stay on the device between steps ([rows][stride] page numbers, a row for
+// each request slot); a step sends only the entries that changed since the step before, as (row, column, page)
+// triples, and this kernel writes them.  An entry outside the table is skipped (the host never makes one).
+__global__ void table_update_kernel(int* __restrict__ table, int rows, int stride, const int* __restrict__ updates, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int row = updates[3 * i], col = updates[3 * i + 1], page = updates[3 * i + 2];
+    if (row >= 0 && row < rows && col >= 0 && col < stride) table[(size_t)row * stride + col] = page;
+}
+
+ACV_API int acv_table_update(int* table, int rows, int stride, const int* updates, int n, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    table_update_kernel<<<(n + 255) / 256, 256, 0, stream>>>(table, rows, stride, updates, n);
+    return acv_launch_status();
+}
+
+// ----------------------------------------------------------------------------- bias of a projection
+// out[t][n] += bias[n], the sum in float and rounded once to the element type.  The reference adds a bias where the
+// weight file holds one (acvram/engine/loader.py:269-270); Qwen3's files hold none.
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ out, int ld, const float* __restrict__ bias, int rows, int N) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * N) return;
+    const int t = (int)(i / N), n = (int)(i - (long long)t * N);
+    T* p = out + (size_t)t * ld + n;
+    *p = from_f32<T>(to_f32(*p) + bias[n]);
+}
+
+ACV_API int acv_add_bias(void* out, int ld, const float* bias, int rows, int N, int dtype, cudaStream_t stream) {
+    if (rows <= 0 || N <= 0) return 0;
+    const long long total = (long long)rows * N;
+    const unsigned grid = (unsigned)((total + 255) / 256);
+    if (dtype == ACV_F32)
+        acv_launch(PDL_MISC, add_bias_kernel<float>, grid, 256, 0, stream, (float*)out, ld, bias, rows, N);
+    else if (dtype == ACV_BF16)
+        acv_launch(PDL_MISC, add_bias_kernel<bf16>, grid, 256, 0, stream, (bf16*)out, ld, bias, rows, N);
+    else
+        return ACV_ERR_DTYPE;
+    return acv_launch_status();
+}

@@ -58,6 +58,7 @@ struct GemmParams {
     const int* seq_of_token;
     const int* block_table;
     int bt_stride;
+    const int* bt_rows;                         // the row of block_table of each request of the batch (null: its index)
     bf16* k_pages;
     bf16* v_pages;
     int page_size, num_pages;
@@ -280,7 +281,10 @@ __device__ __forceinline__ void gt_store_qkv_rows(const GemmParams& p, uint32_t 
     int pos = 0, pg = -1;
     if (live) {
         pos = p.positions[token];
-        pg = p.block_table[(size_t)p.seq_of_token[token] * p.bt_stride + pos / p.page_size];
+        {
+            const int sq = p.seq_of_token[token];
+            pg = p.block_table[(size_t)(p.bt_rows ? p.bt_rows[sq] : sq) * p.bt_stride + pos / p.page_size];
+        }
         if (pg >= p.num_pages) pg = -1;
     }
     const bool in_table = pos >= 0 && pos < p.table_rows;
@@ -429,6 +433,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // only now may the next kernel's CTAs come: one that took tensor memory before this CTA had its own
     // could wait for this grid to end while this CTA waits for its columns
     pdl_launch_dependents();
+    // split K inside a cluster: ranks 1.. write their partial tiles into rank 0's shared memory at the end.  They may
+    // do so only when they know that rank 0 has started: every thread arrives at the cluster's barrier now and
+    // waits for its first phase before the remote stores (or, for threads that make none, before the second phase)
+    if (cluster_split) cluster_arrive();
+    bool cluster_waited = false;
 
     const int n_items = p.tiles_a * p.tiles_b * p.splits;
     const uint32_t tiles_addr = gt_smem(tiles);
@@ -521,7 +530,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 int pos = 0, pg = -1;
                 if (t < p.M) {
                     pos = p.positions[t];
-                    pg = p.block_table[(size_t)p.seq_of_token[t] * p.bt_stride + pos / p.page_size];
+                    {
+                        const int sq = p.seq_of_token[t];
+                        pg = p.block_table[(size_t)(p.bt_rows ? p.bt_rows[sq] : sq) * p.bt_stride + pos / p.page_size];
+                    }
                     if (pg >= p.num_pages) pg = -1;
                 }
                 pos_s[r] = pos;
@@ -587,6 +599,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 // ---- split K inside a cluster: ranks 1.. put their partial tile into rank 0's shared memory;
                 // rank 0 adds them to its own after the cluster barrier below (one item per CTA in this mode)
                 const uint32_t rank = cluster_ctarank();
+                cluster_wait();
+                cluster_waited = true;
                 if (rank != 0) {
                     const uint32_t remote = cluster_map(part0, 0) + (rank - 1) * S::PART_BYTES + (wq * 32 + lane) * 4;
 #pragma unroll 1
@@ -642,6 +656,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (cluster_split) {
         if (threadIdx.x == 64) ACV_TL_MARK(TL_M_PART_SENT);
+        if (!cluster_waited) cluster_wait();
         cluster_sync_all();         // every partial tile lies in rank 0's shared memory
         if (threadIdx.x == 64) ACV_TL_MARK(TL_M_CLUSTER_MET);
         if (warp >= 2 && cluster_ctarank() == 0 && !abort_s) {
@@ -696,12 +711,8 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     while ((parts || aux_bytes) && stages > 2 && S::smem_bytes(stages, parts, aux_bytes) > 226 * 1024) --stages;
     p.stages = stages;
     const int smem = S::smem_bytes(stages, parts, aux_bytes);
-    static int configured = 0;
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = smem;
-    }
+    static AcvSmemConfig smem_config;          // per kernel instance and device
+    if (int rc = acv_ensure_smem(smem_config, gemm_tc_kernel<BN>, smem)) return rc;
     // CTAs that fit one SM: by shared memory and by tensor-memory columns (512 in all)
     int per_sm = (227 * 1024) / (smem + 1024);
     if (per_sm > 512 / S::TMEM_COLS) per_sm = 512 / S::TMEM_COLS;
@@ -802,7 +813,7 @@ ACV_API int acv_gemm_tc_qkv(const void* x, int ldx, const void* w, int ldw, void
                             long long n_counters, int* status, int sm_count, int stages, int flags, int NH, int NKV, int D,
                             const float* q_w, const float* k_w, float eps, const float* cos_sin, int table_rows,
                             const int* positions, const int* seq_of_token, const int* block_table, int bt_stride,
-                            void* k_pages, void* v_pages, int page_size, int num_pages, cudaStream_t stream) {
+                            const int* bt_rows, void* k_pages, void* v_pages, int page_size, int num_pages, cudaStream_t stream) {
     if ((D != 64 && D != 128) || NH <= 0 || NKV <= 0 || N != (NH + 2 * NKV) * D || (swap && bn > 32) || !k_pages || !v_pages ||
         !positions || !seq_of_token || !block_table || page_size <= 0 || ((uintptr_t)k_pages & 15) || ((uintptr_t)v_pages & 15) ||
         (cos_sin && ((uintptr_t)cos_sin & 15)))
@@ -810,7 +821,7 @@ ACV_API int acv_gemm_tc_qkv(const void* x, int ldx, const void* w, int ldw, void
     GemmParams p;
     p.qkv = 1; p.q_heads = NH; p.kv_heads = NKV; p.head_dim = D; p.q_w = q_w; p.k_w = k_w; p.qk_eps = eps;
     p.cos_sin = cos_sin; p.table_rows = table_rows; p.positions = positions; p.seq_of_token = seq_of_token;
-    p.block_table = block_table; p.bt_stride = bt_stride; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages;
+    p.block_table = block_table; p.bt_stride = bt_stride; p.bt_rows = bt_rows; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages;
     p.page_size = page_size; p.num_pages = num_pages;
     return gemm_tc_run(p, x, ldx, w, ldw, C, ldc, M, N, K, 0, 0, swap, bn, splits, workspace, workspace_floats, counters,
                        n_counters, status, sm_count, stages, flags, stream);

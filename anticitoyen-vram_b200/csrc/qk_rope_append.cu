@@ -24,7 +24,7 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, int row_stride, 
                                            const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                                            const float* __restrict__ cos_sin, int rot, int table_rows,
                                            const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                           const int* __restrict__ block_table, int bt_stride, T* __restrict__ k_pages,
+                                           const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows, T* __restrict__ k_pages,
                                            T* __restrict__ v_pages, int page_size, int num_pages) {
     extern __shared__ float sm_all[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -58,7 +58,7 @@ __global__ void qk_norm_rope_append_kernel(T* __restrict__ qkv, int row_stride, 
         dst = src;
     } else if (k_pages) {
         const int seq = seq_of_token[t];
-        const int pg = block_table[(size_t)seq * bt_stride + pos / page_size];
+        const int pg = block_table[(size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride + pos / page_size];
         if (pg >= 0 && pg < num_pages) {
             const int kvh = is_k ? head - NH : head - NH - NKV;
             T* base = is_k ? k_pages : v_pages;
@@ -92,7 +92,7 @@ __global__ void qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, int row_stri
                                                const float* __restrict__ q_w, const float* __restrict__ k_w, float eps,
                                                const float* __restrict__ cos_sin, int table_rows,
                                                const int* __restrict__ positions, const int* __restrict__ seq_of_token,
-                                               const int* __restrict__ block_table, int bt_stride,
+                                               const int* __restrict__ block_table, int bt_stride, const int* __restrict__ bt_rows,
                                                T* __restrict__ k_pages, T* __restrict__ v_pages, int page_size,
                                                int num_pages) {
     constexpr int D = VEC * 32;
@@ -116,7 +116,7 @@ __global__ void qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, int row_stri
         dst = src;
     } else if (k_pages) {
         const int seq = seq_of_token[t];
-        const int pg = block_table[(size_t)seq * bt_stride + pos / page_size];
+        const int pg = block_table[(size_t)(bt_rows ? bt_rows[seq] : seq) * bt_stride + pos / page_size];
         if (pg >= 0 && pg < num_pages) {
             const int kvh = is_k ? head - NH : head - NH - NKV;
             dst = (is_k ? k_pages : v_pages) + (((size_t)pg * NKV + kvh) * page_size + (pos % page_size)) * D;
@@ -162,17 +162,17 @@ __global__ void qk_norm_rope_append_vec_kernel(T* __restrict__ qkv, int row_stri
 template <typename T, int VEC>
 static void launch_qra_vec(dim3 grid, cudaStream_t stream, void* qkv, int row_stride, int NH, int NKV, const float* q_w,
                            const float* k_w, float eps, const float* cos_sin, int table_rows, const int* positions,
-                           const int* seq_of_token, const int* block_table, int bt_stride, void* k_pages, void* v_pages,
+                           const int* seq_of_token, const int* block_table, int bt_stride, const int* bt_rows, void* k_pages, void* v_pages,
                            int page_size, int num_pages) {
     acv_launch(PDL_ROPE, qk_norm_rope_append_vec_kernel<T, VEC>, grid, QRA_WARPS * 32, 0, stream,
         (T*)qkv, row_stride, NH, NKV, q_w, k_w, eps, cos_sin, table_rows, positions, seq_of_token, block_table,
-        bt_stride, (T*)k_pages, (T*)v_pages, page_size, num_pages);
+        bt_stride, bt_rows, (T*)k_pages, (T*)v_pages, page_size, num_pages);
 }
 
 ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, int NKV, int D, const float* q_w,
                                     const float* k_w, float eps, const float* cos_sin, int rot, int table_rows,
                                     const int* positions, const int* seq_of_token, const int* block_table,
-                                    int bt_stride, void* k_pages, void* v_pages, int page_size, int num_pages,
+                                    int bt_stride, const int* bt_rows, void* k_pages, void* v_pages, int page_size, int num_pages,
                                     int dtype, cudaStream_t stream) {
     if (T <= 0) return 0;
     if (D <= 0 || D > 1024 || (cos_sin && (rot <= 0 || rot > D || (rot & 1)))) return ACV_ERR_SIZE;
@@ -188,7 +188,7 @@ ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, in
     if (vec_ok) {
 #define QRA_VEC(TT, VV)                                                                                                 \
     launch_qra_vec<TT, VV>(grid, stream, qkv, row_stride, NH, NKV, q_w, k_w, eps, cos_sin, table_rows, positions,       \
-                           seq_of_token, block_table, bt_stride, k_pages, v_pages, page_size, num_pages)
+                           seq_of_token, block_table, bt_stride, bt_rows, k_pages, v_pages, page_size, num_pages)
         if (dtype == ACV_F32) {
             if (vec == 1) QRA_VEC(float, 1); else if (vec == 2) QRA_VEC(float, 2); else if (vec == 4) QRA_VEC(float, 4);
             else return ACV_ERR_SIZE;
@@ -203,11 +203,11 @@ ACV_API int acv_qk_norm_rope_append(void* qkv, int row_stride, int T, int NH, in
     if (dtype == ACV_F32)
         qk_norm_rope_append_kernel<float><<<grid, QRA_WARPS * 32, smem, stream>>>(
             (float*)qkv, row_stride, NH, NKV, D, q_w, k_w, eps, cos_sin, rot, table_rows, positions, seq_of_token,
-            block_table, bt_stride, (float*)k_pages, (float*)v_pages, page_size, num_pages);
+            block_table, bt_stride, bt_rows, (float*)k_pages, (float*)v_pages, page_size, num_pages);
     else if (dtype == ACV_BF16)
         qk_norm_rope_append_kernel<bf16><<<grid, QRA_WARPS * 32, smem, stream>>>(
             (bf16*)qkv, row_stride, NH, NKV, D, q_w, k_w, eps, cos_sin, rot, table_rows, positions, seq_of_token,
-            block_table, bt_stride, (bf16*)k_pages, (bf16*)v_pages, page_size, num_pages);
+            block_table, bt_stride, bt_rows, (bf16*)k_pages, (bf16*)v_pages, page_size, num_pages);
     else
         return ACV_ERR_DTYPE;
     return acv_launch_status();

@@ -99,7 +99,7 @@ argmax_kernel(const float* __restrict__ logits, int ld, int V, int* __restrict__
     __shared__ float redf[32];
     __shared__ int redi[32];
     const int bi = block_argmax(logits + (size_t)blockIdx.x * ld, V, 1.f, redf, redi);
-    if (threadIdx.x == 0) out[blockIdx.x] = bi;
+    if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;     // a row without a value above -inf (all NaN): token 0
 }
 
 // Wide rows: each row is cut into ARG_PARTS slices, one block per slice leaves (value, index) in
@@ -248,7 +248,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     const float temp = temperature[r];
 
     if (temp <= 0.f) {  // greedy row
-        const int bi = block_argmax(row, V, 1.f, redf, redi);
+        int bi = block_argmax(row, V, 1.f, redf, redi);
+        if (bi == 0x7fffffff) bi = 0;           // a row without a value above -inf (all NaN): token 0, as argmax_split_kernel
         float z = 0.f;
         if (out_logprob) {
             const float mx = row[bi];

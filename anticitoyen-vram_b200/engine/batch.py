@@ -5,24 +5,35 @@ positions, sequence lengths, query lengths, block tables and a slot mapping, and
 is either all-prefill or all-decode.  Here a batch mixes portions of prompts and
 single decoded tokens freely; per token it gives the token id, its absolute
 position and the index of its request in the batch, per request the start of its
-tokens, the length of its context after the step, its row of each group's block
-table and its state slots.  The slot of a token's key and value is computed in
-the kernel from the block table (page = table[pos // page_size], row = pos %
-page_size; acvram/engine/runner.py:1853-1854 has the same arithmetic on the host).
+tokens, the length of its context after the step, its row of the block tables
+and its state slots.  The slot of a token's key and value is computed in the
+kernel from the block table (page = table[row][pos // page_size], row in the page
+= pos % page_size; acvram/engine/runner.py:1853-1854 has the same arithmetic on
+the host).
 
-Everything is packed into one pinned int32 buffer and reaches the device with one
-copy per step.
+The block tables themselves stay on the device (``CacheStorage.tables``); a step
+brings only the entries that changed since the step before (the reference
+rebuilds and copies a padded table every step, acvram/engine/lot.py:98-118).
+Everything a step brings is packed into one pinned int32 buffer and reaches the
+device with one copy.
+
+What a particular kind of mixer needs beside this (work lists of its kernels,
+say) is not made here: a mixer class may offer ``step_metadata`` and
+``decode_metadata`` (``parts.base.Mixer``); the builder calls each distinct
+provider once a step, packs its arrays into the same buffer and hands the device
+views back under the provider's key in ``StepContext.work``.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable, Sequence
+from typing import Hashable, Mapping, Sequence
 
 import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, PagedGroup
+from ..kernels import ops
 
 
 @dataclass
@@ -43,19 +54,17 @@ class StepContext:
     cu_q: torch.Tensor            # int32 [B+1] start of each request's tokens in the flat batch
     kv_len: torch.Tensor          # int32 [B] length of each request's context after this step
     logit_rows: torch.Tensor      # int32 [R] rows of the flat batch whose logits are wanted
-    block_tables: dict[int, torch.Tensor] = field(default_factory=dict)   # group -> int32 [B, W]
+    table_rows: torch.Tensor | None = None    # int32 [B] each request's row of the block tables (None: its index)
+    block_tables: dict[int, torch.Tensor] = field(default_factory=dict)   # group -> int32 [rows, W], kept on the device
     state_slots: dict[int, torch.Tensor] = field(default_factory=dict)    # group -> int32 [B]
     requests: list = field(default_factory=list)
     q_lens: list[int] = field(default_factory=list)
     kv_lens: list[int] = field(default_factory=list)
-    work: dict = field(default_factory=dict)   # per-step work lists of the attention kernels (device views)
+    work: dict = field(default_factory=dict)   # provider key -> what that kind of mixer asked for (device views, counts)
 
     @property
     def max_q_len(self) -> int:
         return max(self.q_lens, default=0)
-
-
-QUERY_TILE = 128   # query tokens per tile of the portion-attention kernels
 
 
 def _round4(n: int) -> int:
@@ -65,11 +74,15 @@ def _round4(n: int) -> int:
 class BatchBuilder:
     """Builds StepContexts for one cache manager on one device, reusing its staging buffers."""
 
-    def __init__(self, manager: CacheManager, device, vocab_size: int, max_positions: int) -> None:
+    def __init__(self, manager: CacheManager, storage, device, vocab_size: int, max_positions: int,
+                 providers: Mapping[str, object] | None = None) -> None:
         self.manager = manager
+        self.storage = storage
         self.device = torch.device(device)
         self.vocab_size = vocab_size
         self.max_positions = max_positions
+        self.providers = dict(providers or {})     # key -> object with step_metadata / decode_metadata
+        self._paged = [(gi, g) for gi, g in enumerate(manager.groups) if isinstance(g, PagedGroup)]
         # Two pinned staging buffers used in turn: the copy of step n may still be queued
         # on the stream while step n+1 is packed, so a buffer is rewritten only after the
         # event recorded behind its last copy has passed.
@@ -77,6 +90,7 @@ class BatchBuilder:
         self._events: list[torch.cuda.Event | None] = [None, None]
         self._turn = 0
         self.last_h2d_bytes = 0
+        self.last_table_updates = 0
         self._dev: torch.Tensor | None = None
 
     def _buffers(self, n: int) -> tuple[torch.Tensor, torch.Tensor]:
@@ -92,6 +106,12 @@ class BatchBuilder:
             cap = max(4096, 1 << (n - 1).bit_length())
             self._dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         return self._hosts[i], self._dev
+
+    def _sent(self) -> None:
+        if self.device.type == "cuda":
+            if self._events[self._turn] is None:
+                self._events[self._turn] = torch.cuda.Event()
+            self._events[self._turn].record()
 
     def validate(self, entries: Sequence[StepEntry]) -> None:
         """Refuse a malformed batch before anything is reserved for it."""
@@ -109,30 +129,46 @@ class BatchBuilder:
                 if not 0 <= w < n:
                     raise ValueError(f"request {e.request!r}: wanted place {w} is outside its {n} tokens")
 
+    def _apply_updates(self, views: Sequence[tuple[int, torch.Tensor, int]]) -> None:
+        """Write the changed block-table entries (already on the device as triples) into the tables."""
+        for gi, triples, n in views:
+            if n:
+                table = self.storage.tables[gi]
+                ops.table_update(table, triples, n)
+
     # ------------------------------------------------------------------ fixed-shape decode batches
-    @staticmethod
-    def decode_layout(padded: int, width: int, n_paged: int) -> tuple[dict[str, tuple[int, int]], int]:
-        """Offsets of the sections of a decode batch padded to ``padded`` rows with block tables
-        ``width`` wide: the same for every step of that shape, so a captured graph can hold them."""
+    def decode_layout(self, padded: int) -> tuple[dict[str, tuple[int, int]], int, int]:
+        """Offsets of the sections of a decode batch padded to ``padded`` rows: first what every step of that
+        shape brings anew (tokens, positions, context lengths, rows of the block tables, changed table entries),
+        then what is the same for all of them and is written once, when the shape's graph is captured.
+        Returns (offsets, ints a step brings, ints in all)."""
         off, out = 0, {}
-        for name, n in [("tokens", padded), ("positions", padded), ("seq_of_token", padded), ("cu_q", padded + 1),
-                        ("kv_len", padded), ("logit_rows", padded), ("dec_tokens", padded), ("dec_seqs", padded),
-                        *[(f"bt{g}", padded * width) for g in range(n_paged)]]:
+        dynamic = [("tokens", padded), ("positions", padded), ("kv_len", padded), ("table_rows", padded),
+                   *[(f"upd{gi}", 3 * 2 * padded) for gi, _ in self._paged]]
+        for name, n in dynamic:
             out[name] = (off, n)
             off += _round4(n)
-        return out, off
+        n_dynamic = off
+        static = [("seq_of_token", padded), ("cu_q", padded + 1), ("logit_rows", padded)]
+        for key, prov in self.providers.items():
+            meta = prov.decode_metadata(padded, 1)
+            static += [(f"{key}.{name}", int(np.asarray(a).size)) for name, a in meta.arrays.items()]
+        for name, n in static:
+            out[name] = (off, n)
+            off += _round4(n)
+        return out, n_dynamic, off
 
-    def build_decode(self, entries: Sequence[StepEntry], starts: Sequence[int], padded: int, width: int,
-                     dev: torch.Tensor) -> StepContext:
+    def build_decode(self, entries: Sequence[StepEntry], starts: Sequence[int], padded: int, max_kv: int,
+                     dev: torch.Tensor, first: bool = False) -> StepContext:
         """One token for each request, padded to ``padded`` rows (padding rows hold nothing: context
-        length 0 and a block table of -1, so they read and write no page), into the buffer ``dev``."""
+        length 0 and the block tables' row that belongs to nobody, so they read and write no page), into the
+        buffer ``dev``.  ``max_kv``: the context length that the launch shapes of this bucket are made for.
+        ``first``: also write the part that never changes (at capture)."""
         m = self.manager
         B = len(entries)
-        paged = [(gi, g) for gi, g in enumerate(m.groups) if isinstance(g, PagedGroup)]
-        layout, total = self.decode_layout(padded, width, len(paged))
+        layout, n_dynamic, total = self.decode_layout(padded)
         host, _ = self._buffers(total)
         h = host.numpy()
-        ar = np.arange(padded + 1, dtype=np.int32)
 
         def put(name, values, fill=0):
             o, n = layout[name]
@@ -141,40 +177,62 @@ class BatchBuilder:
 
         put("tokens", [e.tokens[0] for e in entries])
         put("positions", list(starts))
-        put("seq_of_token", ar[:padded])
-        put("cu_q", ar)
         put("kv_len", [s + 1 for s in starts])
-        put("logit_rows", ar[:padded])
-        put("dec_tokens", ar[:padded])
-        put("dec_seqs", ar[:padded])
-        for k, (gi, g) in enumerate(paged):
-            o, n = layout[f"bt{k}"]
-            table = h[o:o + n].reshape(padded, width)
-            table[:] = -1
-            for i, e in enumerate(entries):
-                t = g.tables[e.request]
-                table[i, :len(t)] = t
-        dev[:total].copy_(host[:total], non_blocking=True)
-        self.last_h2d_bytes = total * 4
-        if self.device.type == "cuda":
-            if self._events[self._turn] is None:
-                self._events[self._turn] = torch.cuda.Event()
-            self._events[self._turn].record()
+        put("table_rows", [m.rows[e.request] for e in entries], fill=m.null_row)
+        updates = m.take_updates()
+        late = []      # more changed entries than the fixed section holds (rare: sent by themselves)
+        views = []
+        self.last_table_updates = sum(len(u) for u in updates)
+        for (gi, _), upd in zip(self._paged, updates):
+            o, n = layout[f"upd{gi}"]
+            if 3 * len(upd) > n:
+                late.append((gi, upd))
+                continue
+            if upd:
+                h[o:o + 3 * len(upd)] = np.asarray(upd, dtype=np.int32).reshape(-1)
+            views.append((gi, dev[o:o + n], len(upd)))
+        metas = {}
+        if first:
+            ar = np.arange(padded + 1, dtype=np.int32)
+            put("seq_of_token", ar[:padded])
+            put("cu_q", ar)
+            put("logit_rows", ar[:padded])
+        for key, prov in self.providers.items():
+            metas[key] = prov.decode_metadata(padded, max_kv)
+            if first:
+                for name, a in metas[key].arrays.items():
+                    put(f"{key}.{name}", np.asarray(a, dtype=np.int32).reshape(-1))
+        # a step sends what it brings: up to the end of the last changed table entry (the rest of the buffer is static)
+        n_send = layout["table_rows"][0] + _round4(padded)
+        for gi, _, n_upd in views:
+            if n_upd:
+                n_send = max(n_send, layout[f"upd{gi}"][0] + _round4(3 * n_upd))
+        if first:
+            n_send = total
+        dev[:n_send].copy_(host[:n_send], non_blocking=True)
+        self.last_h2d_bytes = n_send * 4
+        self._sent()
+        for gi, upd in late:
+            t = torch.tensor(upd, dtype=torch.int32).reshape(-1).to(self.device)
+            self.last_h2d_bytes += t.numel() * 4
+            views.append((gi, t, len(upd)))
+        self._apply_updates(views)
+
         view = lambda name: dev[layout[name][0]:layout[name][0] + layout[name][1]]
         kv_lens = [s + 1 for s in starts]
         ctx = StepContext(
             num_tokens=padded, num_seqs=padded, num_logit_rows=padded, tokens=view("tokens"),
             positions=view("positions"), seq_of_token=view("seq_of_token"), cu_q=view("cu_q"), kv_len=view("kv_len"),
-            logit_rows=view("logit_rows"), requests=[e.request for e in entries], q_lens=[1] * padded,
-            kv_lens=kv_lens + [0] * (padded - B))
-        for k, (gi, g) in enumerate(paged):
-            ctx.block_tables[gi] = view(f"bt{k}").view(padded, width)
-        ctx.work = {"dec_tokens": view("dec_tokens"), "dec_seqs": view("dec_seqs"), "n_dec": padded, "n_tiles": 0,
-                    "tile_seq": view("dec_seqs")[:0], "tile_q0": view("dec_seqs")[:0],
-                    "max_dec_kv": width * m.page_size}
+            logit_rows=view("logit_rows"), table_rows=view("table_rows"), requests=[e.request for e in entries],
+            q_lens=[1] * padded, kv_lens=kv_lens + [0] * (padded - B))
+        for gi, _ in self._paged:
+            ctx.block_tables[gi] = self.storage.tables[gi]
+        for key, meta in metas.items():
+            ctx.work[key] = {**{name: view(f"{key}.{name}") for name in meta.arrays}, **meta.values}
         return ctx
 
-    def build(self, entries: Sequence[StepEntry], starts: Sequence[int], extra_sections: dict[str, np.ndarray] | None = None) -> StepContext:
+    # ------------------------------------------------------------------ any batch
+    def build(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepContext:
         """``starts[i]`` is the number of tokens request i held before this step; its pages
         for the new tokens are already reserved."""
         m = self.manager
@@ -204,35 +262,19 @@ class BatchBuilder:
 
         sections: list[tuple[str, np.ndarray]] = [
             ("tokens", tokens.astype(np.int32)), ("positions", positions), ("seq_of_token", seq_of), ("cu_q", cu),
-            ("kv_len", np.asarray(kv_lens, dtype=np.int32)), ("logit_rows", np.asarray(rows, dtype=np.int32))]
-        shapes: dict[str, tuple] = {}
+            ("kv_len", np.asarray(kv_lens, dtype=np.int32)), ("logit_rows", np.asarray(rows, dtype=np.int32)),
+            ("table_rows", np.asarray([m.rows[e.request] for e in entries], dtype=np.int32))]
         for gi, g in enumerate(m.groups):
-            if isinstance(g, PagedGroup):
-                W = max(1, max((g.pages_for(k) for k in kv_lens), default=1))
-                table = np.full((B, W), -1, dtype=np.int32)
-                for i, e in enumerate(entries):
-                    t = g.tables[e.request]
-                    n = min(len(t), W)
-                    table[i, :n] = t[:n]
-                sections.append((f"bt{gi}", table.reshape(-1)))
-                shapes[f"bt{gi}"] = (B, W)
-            else:
+            if not isinstance(g, PagedGroup):
                 sections.append((f"st{gi}", np.asarray([g.slot_of[e.request] for e in entries], dtype=np.int32)))
-        # work lists of the attention kernels: requests with one token (decoding) and tiles of
-        # QUERY_TILE tokens of the requests with more (portions of prompts)
-        ql = np.asarray(q_lens, dtype=np.int32)
-        dec = np.nonzero(ql == 1)[0].astype(np.int32)
-        tile_seq, tile_q0 = [], []
-        for i in np.nonzero(ql > 1)[0]:
-            starts_i = np.arange(0, q_lens[i], QUERY_TILE, dtype=np.int32)[::-1]   # late tiles see most keys: first
-            tile_seq.append(np.full(starts_i.size, i, dtype=np.int32))
-            tile_q0.append(starts_i)
-        work_counts = {"dec": int(dec.size), "tiles": int(sum(t.size for t in tile_seq))}
-        sections += [("dec_tokens", cu[:-1][dec]), ("dec_seqs", dec),
-                     ("tile_seq", np.concatenate(tile_seq) if tile_seq else np.zeros(0, np.int32)),
-                     ("tile_q0", np.concatenate(tile_q0) if tile_q0 else np.zeros(0, np.int32))]
-        for name, arr in (extra_sections or {}).items():
-            sections.append((name, np.ascontiguousarray(arr, dtype=np.int32).reshape(-1)))
+        updates = m.take_updates()
+        self.last_table_updates = sum(len(u) for u in updates)
+        for (gi, _), upd in zip(self._paged, updates):
+            sections.append((f"upd{gi}", np.asarray(upd, dtype=np.int32).reshape(-1)))
+        metas = {key: prov.step_metadata(q_lens, kv_lens, cu) for key, prov in self.providers.items()}
+        for key, meta in metas.items():
+            for name, a in meta.arrays.items():
+                sections.append((f"{key}.{name}", np.ascontiguousarray(a, dtype=np.int32).reshape(-1)))
 
         total = sum(_round4(a.size) for _, a in sections)
         host, dev = self._buffers(max(total, 4))
@@ -245,27 +287,22 @@ class BatchBuilder:
             off += _round4(arr.size)
         dev[:total].copy_(host[:total], non_blocking=True)
         self.last_h2d_bytes = total * 4
-        if self.device.type == "cuda":
-            if self._events[self._turn] is None:
-                self._events[self._turn] = torch.cuda.Event()
-            self._events[self._turn].record()
+        self._sent()
 
         def view(name: str) -> torch.Tensor:
             o, n = offsets[name]
             return dev[o:o + n]
 
+        self._apply_updates([(gi, view(f"upd{gi}"), len(upd)) for (gi, _), upd in zip(self._paged, updates)])
         ctx = StepContext(
             num_tokens=T, num_seqs=B, num_logit_rows=R, tokens=view("tokens"), positions=view("positions"),
             seq_of_token=view("seq_of_token"), cu_q=view("cu_q"), kv_len=view("kv_len"), logit_rows=view("logit_rows"),
-            requests=[e.request for e in entries], q_lens=q_lens, kv_lens=kv_lens)
+            table_rows=view("table_rows"), requests=[e.request for e in entries], q_lens=q_lens, kv_lens=kv_lens)
         for gi, g in enumerate(m.groups):
             if isinstance(g, PagedGroup):
-                ctx.block_tables[gi] = view(f"bt{gi}").view(shapes[f"bt{gi}"])
+                ctx.block_tables[gi] = self.storage.tables[gi]
             else:
                 ctx.state_slots[gi] = view(f"st{gi}")
-        for name in ("dec_tokens", "dec_seqs", "tile_seq", "tile_q0", *(extra_sections or {})):
-            ctx.work[name] = view(name)
-        ctx.work["n_dec"] = work_counts["dec"]
-        ctx.work["n_tiles"] = work_counts["tiles"]
-        ctx.work["max_dec_kv"] = max((k for k, q in zip(kv_lens, q_lens) if q == 1), default=0)
+        for key, meta in metas.items():
+            ctx.work[key] = {**{name: view(f"{key}.{name}") for name in meta.arrays}, **meta.values}
         return ctx

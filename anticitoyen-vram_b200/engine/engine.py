@@ -116,7 +116,8 @@ class Engine:
         self.page_size = page_size
         if num_pages is None:
             num_pages = self._default_pages(max_batch_size, device)
-        self.runner = ModelRunner(self.model, page_size, num_pages, max_batch_size, enable_prefix_cache)
+        self.runner = ModelRunner(self.model, page_size, num_pages, max_batch_size, enable_prefix_cache,
+                                  max_len=self.max_model_len)
         self.scheduler = Scheduler(self.runner.manager, max_batch_size, token_budget, self.max_model_len)
         self.sampler = Sampler(device)
         self.tokenizer = tokenizer
@@ -321,6 +322,7 @@ class Engine:
         try:
             torch.cuda.synchronize(self.model.rt.device)
             ops.reset_after_failure()
+            self.runner.manager.resync()      # the step's changes of the block tables may not have reached the device
         except Exception:
             raise exc
         text = f"{type(exc).__name__}: {exc}"

@@ -1,13 +1,15 @@
 """CUDA-graph replay of the decode step.
 
 A step in which every request brings one token has the same launches whatever the
-requests are, once the batch is padded to a bucket and the block tables to a
-bucket width; the whole model step is then captured once per (batch bucket, table
-width) and replayed, which removes the per-launch cost of some three hundred
+requests are, once the batch is padded to a bucket and the longest context is
+rounded up to a bucket (it decides how the attention splits its work); the whole
+model step is then captured once per (batch bucket, context bucket) and replayed, which removes the per-launch cost of some three hundred
 launches a step.  The idea, buckets and padding rows follow the reference's
 ``GraphRunner`` (acvram/engine/graphs.py:8-22, 49-72; padding rows carry a context
 length of 0 and write nothing, acvram/engine/graphs.py:14-17).  Each graph owns a
-static metadata buffer; a step only copies its packed metadata there and replays.
+static metadata buffer; a step copies what changes from step to step there (tokens,
+positions, context lengths, the requests' rows of the block tables, which stay on
+the device, and the few table entries that changed) and replays.
 """
 
 from __future__ import annotations
@@ -17,7 +19,6 @@ import gc
 import torch
 
 from ..kernels import ops
-from .batch import BatchBuilder
 
 BATCH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
 MIN_TABLE_WIDTH = 8
@@ -44,6 +45,7 @@ class DecodeGraphs:
         self.graphs: dict[tuple[int, int], dict] = {}
         self.replays = 0
         self.launches = 0       # kernels of this package run through replays
+        self.refused = 0        # decode steps that ran without a graph because the table of graphs was full
         self.disabled_reason: str | None = None
         if runner.manager.state_groups:
             self.disabled_reason = "the model keeps per-request state of fixed size"
@@ -63,10 +65,11 @@ class DecodeGraphs:
         slot = self.graphs.get(key)
         if slot is None:
             if len(self.graphs) >= MAX_GRAPHS:
+                self.refused += 1
                 return None
             slot = self._capture(key, entries, starts, device_tokens)
         else:
-            ctx = r.builder.build_decode(entries, starts, padded, width, slot["dev"])
+            ctx = r.builder.build_decode(entries, starts, padded, width * m.page_size, slot["dev"])
             if device_tokens is not None:
                 ctx.tokens[:len(entries)].copy_(device_tokens)
             slot["graph"].replay()
@@ -77,15 +80,13 @@ class DecodeGraphs:
     def _capture(self, key, entries, starts, device_tokens):
         r = self.runner
         padded, width = key
-        paged = len(r.manager.paged_groups)
-        _, total = BatchBuilder.decode_layout(padded, width, paged)
+        _, _, total = r.builder.decode_layout(padded)
         dev = torch.empty(total, dtype=torch.int32, device=r.rt.device)
-        ctx = r.builder.build_decode(entries, starts, padded, width, dev)
+        # the launch shapes (how the attention splits the context) follow the bucket's longest context,
+        # width * page_size, whatever the requests of this step hold
+        ctx = r.builder.build_decode(entries, starts, padded, width * r.manager.page_size, dev, first=True)
         if device_tokens is not None:
             ctx.tokens[:len(entries)].copy_(device_tokens)
-        # the split of the context is part of the launch shape: fix it for the whole bucket
-        kv_heads = max((g.need.num_kv_heads for g in r.manager.paged_groups), default=1)
-        ctx.work["n_splits"] = ops.decode_splits(padded, kv_heads, width * r.manager.page_size)
         r.model.forward(ctx, r.storage)             # eager once: scratch buffers reach their size
         torch.cuda.synchronize(r.rt.device)
         graph = torch.cuda.CUDAGraph()

@@ -21,15 +21,20 @@ from .batch import BatchBuilder, StepContext, StepEntry
 
 class ModelRunner:
     def __init__(self, model, page_size: int, num_pages: int, max_requests: int,
-                 enable_prefix_cache: bool = False) -> None:
+                 enable_prefix_cache: bool = False, max_len: int | None = None) -> None:
+        """``max_len``: the longest request in tokens (default: what the model's positions and the pool allow);
+        the block tables on the device get that many columns' worth of pages."""
         if model.rt is None:
             raise ValueError("the model has no weights loaded")
         rt: Runtime = model.rt
         self.model = model
         self.rt = rt
         self.manager = CacheManager(model.cache_plan(), page_size, num_pages, max_requests, enable_prefix_cache)
-        self.storage = CacheStorage(self.manager, rt.device, rt.dtype)
-        self.builder = BatchBuilder(self.manager, rt.device, model.plan.vocab_size, model.plan.max_positions)
+        self.storage = CacheStorage(self.manager, rt.device, rt.dtype, min(max_len or model.plan.max_positions,
+                                                                            model.plan.max_positions))
+        self.max_len = min(model.plan.max_positions, self.storage.max_tokens)
+        self.builder = BatchBuilder(self.manager, self.storage, rt.device, model.plan.vocab_size, self.max_len,
+                                    model.metadata_providers() if hasattr(model, "metadata_providers") else {})
         self.steps = 0
         self.graphs = None          # DecodeGraphs when graph replay of decode steps is on
 
@@ -70,9 +75,9 @@ class ModelRunner:
         self.builder.validate(entries)
         for e in entries:
             have = m.lengths.get(e.request, 0)
-            if have + len(e.tokens) > self.model.plan.max_positions:
-                raise ValueError(f"request {e.request!r} would reach {have + len(e.tokens)} tokens; the model has "
-                                 f"{self.model.plan.max_positions} positions")
+            if have + len(e.tokens) > self.max_len:
+                raise ValueError(f"request {e.request!r} would reach {have + len(e.tokens)} tokens; the model's positions "
+                                 f"and the cache hold {self.max_len}")
         starts = []
         for e in entries:
             if e.request not in m.lengths:
@@ -94,8 +99,9 @@ class ModelRunner:
             if e.request not in m.lengths:
                 self.admit(e.request)
             start = m.lengths[e.request]
-            if start + 1 > self.model.plan.max_positions:
-                raise ValueError(f"request {e.request!r} would pass the model's {self.model.plan.max_positions} positions")
+            if start + 1 > self.max_len:
+                raise ValueError(f"request {e.request!r} would pass the {self.max_len} tokens that the model's positions "
+                                 f"and the cache hold")
             m.grow(e.request, start + 1)
             starts.append(start)
         with torch.cuda.device(self.rt.device):

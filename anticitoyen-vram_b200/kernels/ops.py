@@ -70,14 +70,16 @@ def _declare(lib: ctypes.CDLL) -> None:
         "acv_embed": [P, P, P, I, I, I, I, P],
         "acv_add_rmsnorm": [P, P, P, P, P, I, I, F, I, P],
         "acv_swiglu": [P, P, I, I, I, P],
-        "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, I, I, I, P],
-        "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, P],
+        "acv_add_bias": [P, I, P, I, I, I, P],
+        "acv_qk_norm_rope_append": [P, I, I, I, I, I, P, P, F, P, I, I, P, P, P, I, P, P, P, I, I, I, P],
+        "acv_attention_generic": [P, I, P, I, P, P, P, P, P, I, P, I, I, I, I, I, I, F, I, I, P],
         "acv_gemm_simt": [P, I, P, I, P, I, I, I, I, I, I, P],
-        "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, I, I, P],
+        "acv_gemm_tc_qkv": [P, I, P, I, P, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, I, I, I, P, P, F, P, I, P, P, P, I, P, P, P, I, I, P],
         "acv_gemm_tc": [P, I, P, I, P, I, I, I, I, I, I, I, I, I, P, LL, P, LL, P, I, I, I, P],
-        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, I, P],
-        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, P, P],
-        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, I, I, I, I, I, F, I, I, P],
+        "acv_attention_decode": [P, I, P, I, P, P, P, P, I, P, P, I, P, I, I, I, I, I, F, I, I, P, P, P, LL, LL, LL, I, I, P],
+        "acv_attention_tc": [P, I, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, P, P],
+        "acv_attention_chunk": [P, I, P, I, P, P, P, P, I, P, P, P, I, P, I, I, I, I, I, F, I, I, P],
+        "acv_table_update": [P, I, I, P, I, P],
         "acv_argmax": [P, I, I, I, P, P],
         "acv_apply_penalties": [P, I, I, P, P, P, I, P, P, P, P],
         "acv_sample": [P, I, I, I, P, P, P, P, P, P, P, P, P],
@@ -165,6 +167,24 @@ def add_rmsnorm(x: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tenso
     return out
 
 
+def add_bias(out: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """out[t, n] += bias[n] in place (bias float32 [N]; the sum in float, rounded once to out's type)."""
+    _need_cuda(out, bias)
+    if bias.dtype != torch.float32 or bias.numel() != out.shape[1] or out.stride(1) != 1:
+        raise KernelError("add_bias: a float32 bias of the output's width is wanted")
+    _check(library().acv_add_bias(_p(out), out.stride(0), _p(bias), out.shape[0], out.shape[1], dtype_code(out.dtype),
+                                  _stream()), "add_bias")
+    return out
+
+
+def table_update(table: torch.Tensor, triples: torch.Tensor, n: int) -> None:
+    """table[row, column] = page for the first ``n`` (row, column, page) triples of ``triples`` (int32, on the device)."""
+    _need_cuda(table, triples)
+    if table.dtype != torch.int32 or triples.dtype != torch.int32 or not table.is_contiguous() or triples.numel() < 3 * n:
+        raise KernelError("table_update: a contiguous int32 table and 3 n int32 values are wanted")
+    _check(library().acv_table_update(_p(table), table.shape[0], table.shape[1], _p(triples), n, _stream()), "table_update")
+
+
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """out = silu(gate_up[:, :I]) * gate_up[:, I:].  gate_up [T, 2I] contiguous."""
     _need_cuda(gate_up, out)
@@ -198,10 +218,11 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
                         q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float,
                         cos_sin: torch.Tensor | None, positions: torch.Tensor, seq_of_token: torch.Tensor,
                         block_table: torch.Tensor | None, k_pages: torch.Tensor | None,
-                        v_pages: torch.Tensor | None) -> None:
+                        v_pages: torch.Tensor | None, table_rows: torch.Tensor | None = None) -> None:
     """Per-head norm, rotation and cache append over the stacked projection qkv [T, (NH+2NKV)*D], in place.
 
-    cos_sin float32 [positions, R] (cos of R/2 angles, then sin); pages [NP, NKV, page, D]."""
+    cos_sin float32 [positions, R] (cos of R/2 angles, then sin); pages [NP, NKV, page, D].  ``table_rows``
+    (int32 [requests], optional): the row of ``block_table`` of each request of the batch (default: its index)."""
     _need_cuda(qkv)
     T = qkv.shape[0]
     rot = cos_sin.shape[1] if cos_sin is not None else 0
@@ -211,19 +232,20 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
     bts = block_table.stride(0) if block_table is not None else 0
     _check(library().acv_qk_norm_rope_append(
         _p(qkv), qkv.stride(0), T, num_heads, num_kv_heads, head_dim, _p(q_weight), _p(k_weight), eps, _p(cos_sin),
-        rot, rows, _p(positions), _p(seq_of_token), _p(block_table), bts, _p(k_pages), _p(v_pages), page, n_pages,
+        rot, rows, _p(positions), _p(seq_of_token), _p(block_table), bts, _p(table_rows), _p(k_pages), _p(v_pages), page, n_pages,
         dtype_code(qkv.dtype), _stream()), "qk_norm_rope_append")
 
 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                       positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor,
-                      num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0) -> torch.Tensor:
+                      num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
+                      table_rows: torch.Tensor | None = None) -> torch.Tensor:
     """Paged causal attention for every token of the step.  q: rows of num_heads*head_dim (row stride free)."""
     _need_cuda(q, out, k_pages)
     T = q.shape[0]
     _check(library().acv_attention_generic(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(positions), _p(seq_of_token),
-        _p(block_table), block_table.stride(0), T, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
+        _p(block_table), block_table.stride(0), _p(table_rows), T, num_heads, num_kv_heads, head_dim, k_pages.shape[2],
         k_pages.shape[0], scale, window, dtype_code(q.dtype), _stream()), "attention_generic")
     return out
 
@@ -264,31 +286,57 @@ def _gemm_buffers(device, ws_floats: int, n_counters: int):
     return have
 
 
-def gemm_tc_plan(M: int, N: int, K: int) -> tuple[int, int, int, int]:
-    """(swap, bn, splits, stages) for x[M,K] @ w[N,K]^T.
+_sm_counts: dict = {}
+
+
+def sm_count(device=None) -> int:
+    """Streaming multiprocessors of the device (asked once per device; 148, a B200's, where there is no device)."""
+    if not torch.cuda.is_available():
+        return 148
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None else torch.device(device).index
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
+# Split and pipeline depth of the products with few tokens (weight rows on the tensor core's M side), as measured
+# on a B200 with layer sizes from 0.6B to 32B models: the first row that fits decides.  Splits of K are the CTAs
+# of one cluster (summed through its shared memory).  Columns: tiles per SM from (inclusive) to (exclusive),
+# k-blocks of 64 from to, tokens per tile (bn) from to (inclusive), then what to do: splits, stages.
+#   many tiles: no split, several CTAs share an SM; few tiles: 2..4 splits fill the SMs
+INF = float("inf")
+GEMM_FEW_TOKENS_RULES = (
+    (2.0,    INF,    0,   INF, 16, 128, 1, 8),
+    (1.0,    2.0,    0,   INF, 16, 16,  2, 3),
+    (1.0,    2.0,    0,   INF, 32, 128, 1, 4),
+    (0.0,    1.0,    0,   16,  16, 128, 1, 8),
+    (0.0,    1.0,    128, INF, 16, 32,  4, 8),
+    (0.0,    1.0,    128, INF, 64, 128, 4, 6),
+    (0.2501, 1.0,    16,  128, 16, 16,  4, 4),
+    (0.0,    0.2501, 16,  128, 16, 16,  4, 6),
+    (0.0,    0.2196, 16,  128, 32, 32,  4, 6),
+    (0.2196, 1.0,    16,  128, 32, 32,  2, 6),
+    (0.0,    1.0,    16,  128, 64, 128, 3, 6),
+)
+
+
+def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None) -> tuple[int, int, int, int]:
+    """(swap, bn, splits, stages) for x[M,K] @ w[N,K]^T on a device of ``sms`` multiprocessors.
 
     Up to 128 tokens the weight rows fill the tensor core's M = 128 and the tokens are the narrow
     side (weights stream once whatever the batch); above, tokens are the M side with 256 features
-    per tile.  Splits of K are chosen so that the work items fill whole waves of the SMs."""
+    per tile.  Splits of K are chosen so that the work items fill whole waves of the SMs
+    (``GEMM_FEW_TOKENS_RULES``)."""
     n_kb = -(-K // 64)
     if M <= 128:
+        sms = sms or sm_count()
         bn = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128
         tiles = -(-N // 128) * -(-M // bn)
-        # measured on a B200 at the layer sizes of Qwen3-8B (splits are CTAs of one cluster, summed through
-        # its shared memory): enough tiles -> no split, several CTAs per SM instead; few tiles -> 2..4 splits
-        if tiles >= 2 * _SM_COUNT:
-            return 1, bn, 1, 8
-        if tiles >= _SM_COUNT:
-            return (1, bn, 2, 3) if bn <= 16 else (1, bn, 1, 4)
-        if n_kb < 16:
-            return 1, bn, 1, 8
-        if n_kb >= 128:
-            return 1, bn, 4, 8 if bn <= 32 else 6
-        if bn <= 16:
-            return 1, bn, 4, 4 if tiles * 4 > _SM_COUNT else 6
-        if bn == 32:
-            return 1, bn, 4 if tiles <= 32 else 2, 6
-        return 1, bn, 3, 6
+        per_sm = tiles / sms
+        for t0, t1, k0, k1, b0, b1, splits, stages in GEMM_FEW_TOKENS_RULES:
+            if t0 <= per_sm < t1 and k0 <= n_kb < k1 and b0 <= bn <= b1:
+                return 1, bn, splits, stages
+        return 1, bn, 1, 8
     bn = 256 if N >= 256 else 128 if N > 64 else 64
     return 0, bn, 1, 8
 
@@ -321,7 +369,7 @@ def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | N
     _check(library().acv_gemm_tc(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K,
                                  1 if out.dtype == torch.float32 else 0, 1 if swiglu_pairs else 0, swap, bn, splits,
                                  _p(ws), ws.numel(), _p(cnt),
-                                 cnt.numel(), _p(status), _SM_COUNT, stages, cluster | (2 if static_weights else 0), _stream()), "gemm_tc")
+                                 cnt.numel(), _p(status), sm_count(x.device), stages, cluster | (2 if static_weights else 0), _stream()), "gemm_tc")
     return out
 
 
@@ -340,13 +388,13 @@ def gemm_tc_qkv_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, cos_sin: 
     if not swap:            # tokens on M: a thread of the epilogue holds whole heads of one token
         return splits == 1 and bn >= head_dim and bn % head_dim == 0
     tiles = -(-N // 128) * -(-M // bn)
-    return bn <= 32 and (1 < splits <= 8 or (splits == 1 and tiles <= _SM_COUNT))
+    return bn <= 32 and (1 < splits <= 8 or (splits == 1 and tiles <= sm_count(x.device)))
 
 
 def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                 q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
                 positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                v_pages: torch.Tensor, static_weights: bool = False) -> torch.Tensor:
+                v_pages: torch.Tensor, static_weights: bool = False, table_rows: torch.Tensor | None = None) -> torch.Tensor:
     """The stacked q,k,v projection out[M, (NH+2NKV)*D] = x @ w^T with the epilogue of ``qk_norm_rope_append``
     inside the product's kernel: the query columns of out hold the normed, rotated queries, keys and values go
     to their pages (the key and value columns of out are not written).  ``gemm_tc_qkv_takes`` says when."""
@@ -359,10 +407,11 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_heads: 
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     _check(library().acv_gemm_tc_qkv(
         _p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), M, N, K, swap, bn, splits, _p(ws), ws.numel(),
-        _p(cnt), cnt.numel(), _p(status), _SM_COUNT, stages, cluster | (2 if static_weights else 0), num_heads,
+        _p(cnt), cnt.numel(), _p(status), sm_count(x.device), stages, cluster | (2 if static_weights else 0), num_heads,
         num_kv_heads, head_dim, _p(q_weight), _p(k_weight), eps, _p(cos_sin),
         cos_sin.shape[0] if cos_sin is not None else 0, _p(positions), _p(seq_of_token), _p(block_table),
-        block_table.stride(0), _p(k_pages), _p(v_pages), k_pages.shape[2], k_pages.shape[0], _stream()), "gemm_tc_qkv")
+        block_table.stride(0), _p(table_rows), _p(k_pages), _p(v_pages), k_pages.shape[2], k_pages.shape[0], _stream()),
+        "gemm_tc_qkv")
     return out
 
 
@@ -449,7 +498,6 @@ def top_logprobs(logits: torch.Tensor, k: int) -> tuple[torch.Tensor, torch.Tens
 
 
 # ----------------------------------------------------------------------------- tensor-core attention (bfloat16)
-_SM_COUNT = 148
 _scratch: dict = {}
 _retired: list = []     # outgrown scratch buffers, never freed (graphs captured earlier point into them)
 
@@ -479,7 +527,7 @@ def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
     splits merge inside a cluster, which is so much cheaper than the merge through scratch memory that
     more than 8 pay only when a split would otherwise hold more than 1024 keys."""
     pairs = max(1, n_dec * num_kv_heads)
-    want = max(1, round(256 / pairs))
+    want = max(1, round(256 / 148 * sm_count() / pairs))
     splits = max(1, min(want, -(-max_kv // 256)))
     if splits > 8 and max_kv <= 8 * 1024:
         splits = 8
@@ -489,7 +537,8 @@ def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                      dec_tokens: torch.Tensor, dec_seqs: torch.Tensor, n_dec: int, kv_len: torch.Tensor,
                      block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                     window: int, n_splits: int, max_kv: int = 0, cluster_merge: bool = True) -> torch.Tensor:
+                     window: int, n_splits: int, max_kv: int = 0, cluster_merge: bool = True,
+                     table_rows: torch.Tensor | None = None) -> torch.Tensor:
     """Attention of requests that bring one token each, over their pages, split over the context.
 
     Up to 8 splits are merged inside a thread-block cluster (through its shared memory); more, or
@@ -500,8 +549,8 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
     acc, ml, cnt = _decode_scratch(q.device, parts * n_rep * head_dim, parts * n_rep * 2, n_dec * num_kv_heads)
     _check(library().acv_attention_decode(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(dec_tokens), _p(dec_seqs), n_dec,
-        _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim, k_pages.shape[2],
-        k_pages.shape[0], scale, window, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
+        _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
+        k_pages.shape[2], k_pages.shape[0], scale, window, n_splits, _p(acc), _p(ml), _p(cnt), acc.numel(), ml.numel(), cnt.numel(),
         max_kv or block_table.shape[1] * k_pages.shape[2], 1 if use_cluster else 0, _stream()), "attention_decode")
     return out
 
@@ -509,12 +558,12 @@ def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, 
 def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor,
                     kv_len: torch.Tensor, block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
-                    scale: float, window: int) -> torch.Tensor:
+                    scale: float, window: int, table_rows: torch.Tensor | None = None, max_kv: int = 0) -> torch.Tensor:
     """Causal attention of portions of prompts (tiles of QUERY_TILE query tokens) over their requests' pages."""
     _check(library().acv_attention_chunk(
         _p(q), q.stride(0), _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0), n_tiles,
-        _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim,
-        k_pages.shape[2], k_pages.shape[0], scale, window, block_table.shape[1] * k_pages.shape[2], _stream()),
+        _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads, head_dim,
+        k_pages.shape[2], k_pages.shape[0], scale, window, max_kv or block_table.shape[1] * k_pages.shape[2], _stream()),
         "attention_chunk")
     return out
 
@@ -522,13 +571,13 @@ def attention_chunk(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v
 def attention_tc(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
                  tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, cu_q: torch.Tensor, kv_len: torch.Tensor,
                  block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                 window: int) -> torch.Tensor:
+                 window: int, table_rows: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of portions of prompts on tcgen05 (tiles of QUERY_TILE query tokens, pages by TMA)."""
     _, _, status = _gemm_buffers(q.device, 0, 0)
     _check(library().acv_attention_tc(
         _p(q), q.stride(0), q.shape[0], _p(out), out.stride(0), _p(k_pages), _p(v_pages), _p(tile_seq), _p(tile_q0),
-        n_tiles, _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), num_heads, num_kv_heads, head_dim,
-        k_pages.shape[2], k_pages.shape[0], scale, window, _p(status), _stream()), "attention_tc")
+        n_tiles, _p(cu_q), _p(kv_len), _p(block_table), block_table.stride(0), _p(table_rows), num_heads, num_kv_heads,
+        head_dim, k_pages.shape[2], k_pages.shape[0], scale, window, _p(status), _stream()), "attention_tc")
     return out
 
 
@@ -543,30 +592,67 @@ def tensor_core_attention_takes(dtype: torch.dtype, num_heads: int, num_kv_heads
 
 
 # ----------------------------------------------------------------------------- dispatch by shape
+QUERY_TILE = 128   # query tokens per tile of the portion-attention kernels (AT_BM of attention_tc.cu)
+
+
+def attention_work(q_lens, kv_lens, cu_q) -> tuple[dict, dict]:
+    """Work lists of the attention kernels for a step: the requests with one token (decoding) and tiles of
+    QUERY_TILE tokens of the requests with more (portions of prompts), late tiles first since they see most keys.
+    Returns (int32 arrays that the kernels read on the device, counts and maxima for the launches)."""
+    import numpy as np
+    ql = np.asarray(q_lens, dtype=np.int32)
+    dec = np.nonzero(ql == 1)[0].astype(np.int32)
+    tile_seq, tile_q0 = [], []
+    for i in np.nonzero(ql > 1)[0]:
+        starts_i = np.arange(0, q_lens[i], QUERY_TILE, dtype=np.int32)[::-1]
+        tile_seq.append(np.full(starts_i.size, i, dtype=np.int32))
+        tile_q0.append(starts_i)
+    empty = np.zeros(0, np.int32)
+    arrays = {"dec_tokens": np.asarray(cu_q, dtype=np.int32)[:-1][dec], "dec_seqs": dec,
+              "tile_seq": np.concatenate(tile_seq) if tile_seq else empty,
+              "tile_q0": np.concatenate(tile_q0) if tile_q0 else empty}
+    values = {"n_dec": int(dec.size), "n_tiles": int(sum(t.size for t in tile_seq)),
+              "max_dec_kv": max((k for k, q in zip(kv_lens, q_lens) if q == 1), default=0),
+              "max_tile_kv": max((k for k, q in zip(kv_lens, q_lens) if q > 1), default=0)}
+    return arrays, values
+
+
+def attention_work_decode(padded: int, max_kv: int) -> tuple[dict, dict]:
+    """The same for a batch of ``padded`` requests with one token each, made for contexts up to ``max_kv``."""
+    import numpy as np
+    ar = np.arange(padded, dtype=np.int32)
+    return ({"dec_tokens": ar, "dec_seqs": ar, "tile_seq": np.zeros(0, np.int32), "tile_q0": np.zeros(0, np.int32)},
+            {"n_dec": padded, "n_tiles": 0, "max_dec_kv": max_kv, "max_tile_kv": 0})
+
+
 def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, ctx,
               block_table: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-              window: int = 0) -> torch.Tensor:
+              window: int = 0, work: dict | None = None) -> torch.Tensor:
     """Attention of every token of the step over its request's pages.
 
     ``qkv`` is the stacked projection after norm and rotation (queries are its first
-    num_heads*head_dim columns); ``ctx`` is the step's StepContext.  bfloat16 with a head
-    size of 64 or 128 goes to the tensor-core kernels, requests with one token to the
-    split-KV kernel and portions to the tiled one; everything else to the generic kernel."""
+    num_heads*head_dim columns); ``ctx`` is the step's StepContext; ``work`` the step's work lists
+    (``attention_work``; default: ``ctx.work``).  bfloat16 with a head size of 64 or 128 goes to the
+    tensor-core kernels, requests with one token to the split-KV kernel and portions to the tiled
+    one; everything else to the generic kernel."""
+    rows = getattr(ctx, "table_rows", None)
     if not tensor_core_attention_takes(qkv.dtype, num_heads, num_kv_heads, head_dim):
         return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
-                                 num_kv_heads, head_dim, scale, window)
-    w = ctx.work
+                                 num_kv_heads, head_dim, scale, window, table_rows=rows)
+    w = work if work is not None else ctx.work
     if w["n_dec"]:
         kv = min(w["max_dec_kv"], window) if window > 0 else w["max_dec_kv"]
         attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
                          block_table, num_heads, num_kv_heads, head_dim, scale, window,
-                         w.get("n_splits") or decode_splits(w["n_dec"], num_kv_heads, kv), w["max_dec_kv"])
+                         w.get("n_splits") or decode_splits(w["n_dec"], num_kv_heads, kv), w["max_dec_kv"],
+                         table_rows=rows)
     if w["n_tiles"] and attention_tc_takes(qkv, out, k_pages, head_dim):
         attention_tc(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
-                     block_table, num_heads, num_kv_heads, head_dim, scale, window)
+                     block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows)
     elif w["n_tiles"]:
         attention_chunk(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
-                        block_table, num_heads, num_kv_heads, head_dim, scale, window)
+                        block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows,
+                        max_kv=w.get("max_tile_kv", 0))
     return out
 
 

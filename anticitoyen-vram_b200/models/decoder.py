@@ -96,6 +96,35 @@ class DecoderModel:
                     raise ValueError(f"layer {e.layer} reads cache slot {e.cache}, which no layer of equal need writes")
         return CachePlan(needs)
 
+    def step_cost(self, q_lens, kv_lens, logit_rows: int, cache_itemsize: int | None = None) -> dict:
+        """What one step has to read and compute, summed over the scheduled layers as the parts report it:
+        ``weight_bytes`` (each weight once; a layer that runs twice reads its weights twice), ``cache_bytes`` of the
+        requests (``q_lens`` new tokens each, ``kv_lens`` held after the step), and ``flops`` of the products, the
+        mixing and the head at ``logit_rows`` rows."""
+        T = sum(q_lens)
+        itemsize = cache_itemsize or self.rt.dtype.itemsize
+        weight_bytes = self.head.weight_bytes() + self.final_norm.weight_bytes()
+        cache_bytes, flops = 0, self.head.flops(logit_rows)
+        for e in self.plan.schedule:
+            block = self.blocks[e.layer]
+            weight_bytes += block.weight_bytes()
+            flops += block.flops(T)
+            mixer = getattr(block, "mixer", None)
+            if mixer is not None and e.cache >= 0:
+                flops += mixer.mixing_flops(q_lens, kv_lens)
+                cache_bytes += mixer.cache_bytes_read(q_lens, kv_lens, itemsize)
+        return {"weight_bytes": weight_bytes, "cache_bytes": cache_bytes, "flops": flops}
+
+    def metadata_providers(self) -> dict:
+        """{key: a mixer that makes the per-step data its kind needs}: one for each distinct ``metadata_key``."""
+        out = {}
+        for block in self.blocks:
+            mixer = getattr(block, "mixer", None)
+            key = getattr(mixer, "metadata_key", None)
+            if key is not None and key not in out:
+                out[key] = mixer
+        return out
+
     # ------------------------------------------------------------------ the step
     def forward(self, ctx, storage) -> torch.Tensor:
         """Run the step's tokens through every scheduled layer; logits float32 [R, V] at ctx.logit_rows."""

@@ -44,6 +44,12 @@ class PreNormBlock:
     def cache_need(self):
         return self.mixer.cache_need()
 
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in (self.input_norm, self.post_norm, self.mixer, self.feed_forward))
+
+    def flops(self, num_tokens: int) -> float:
+        return self.mixer.flops(num_tokens) + self.feed_forward.flops(num_tokens)
+
     def forward(self, x, delta, ctx, cache: CacheView | None):
         h = self.input_norm.forward(x, delta)
         a = self.mixer.forward(h, ctx, cache)

@@ -27,6 +27,9 @@ class RMSNorm(Norm):
     def load(self, tensors, rt: Runtime) -> None:
         self.weight = tensors["weight"].to(device=rt.device, dtype=torch.float32).contiguous()
 
+    def weight_bytes(self) -> int:
+        return 0 if self.weight is None else self.weight.numel() * 4
+
     def forward(self, x, delta, rows=None):
         n = rows.shape[0] if rows is not None else x.shape[0]
         out = torch.empty((n, x.shape[1]), device=x.device, dtype=x.dtype)

@@ -13,7 +13,7 @@ import argparse
 
 import torch
 
-from .engine.batch import QUERY_TILE
+from .kernels.ops import QUERY_TILE
 from .kernels import ops
 
 

@@ -9,7 +9,7 @@ from dataclasses import dataclass
 class TensorNeed:
     """One tensor that a part reads by name.
 
-    ``role`` decides the random initialisation ("matrix" and "embedding":
+    ``role`` decides the random initialisation ("matrix", "embedding" and "bias":
     N(0, 0.02); "norm": 1 + N(0, 0.1); "table": integers) and nothing else;
     ``optional`` tensors may be absent from the file (a tied output head).
     """

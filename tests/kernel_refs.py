@@ -40,6 +40,11 @@ def add_rmsnorm(x, delta, weight, eps, out, rows=None):
     return out
 
 
+def add_bias(out, bias):
+    out.copy_((out.float() + bias.float()).to(out.dtype))
+    return out
+
+
 def swiglu(gate_up, out):
     I = out.shape[1]
     g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
@@ -47,8 +52,20 @@ def swiglu(gate_up, out):
     return out
 
 
+def _row(table_rows, seq: int) -> int:
+    """The row of the block table that belongs to request ``seq`` of the batch."""
+    return seq if table_rows is None else int(table_rows[seq])
+
+
+def table_update(table, triples, n):
+    t = triples[:3 * n].view(n, 3).long()
+    for row, col, page in t.tolist():
+        if 0 <= row < table.shape[0] and 0 <= col < table.shape[1]:
+            table[row, col] = page
+
+
 def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weight, eps, cos_sin, positions,
-                        seq_of_token, block_table, k_pages, v_pages):
+                        seq_of_token, block_table, k_pages, v_pages, table_rows=None):
     T = qkv.shape[0]
     NH, NKV, D = num_heads, num_kv_heads, head_dim
     dt = qkv.dtype
@@ -77,7 +94,7 @@ def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weig
         return
     page = k_pages.shape[2]
     for t in range(T):
-        pg = int(block_table[int(seq_of_token[t]), int(pos[t]) // page])
+        pg = int(block_table[_row(table_rows, int(seq_of_token[t])), int(pos[t]) // page])
         if pg < 0:
             continue
         k_pages[pg, :, int(pos[t]) % page] = k[t].to(dt)
@@ -85,7 +102,7 @@ def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_weight, k_weig
 
 
 def attention_generic(q, out, k_pages, v_pages, positions, seq_of_token, block_table, num_heads, num_kv_heads,
-                      head_dim, scale, window=0):
+                      head_dim, scale, window=0, table_rows=None):
     T = q.shape[0]
     NH, NKV, D = num_heads, num_kv_heads, head_dim
     page = k_pages.shape[2]
@@ -95,7 +112,7 @@ def attention_generic(q, out, k_pages, v_pages, positions, seq_of_token, block_t
         seq = int(seq_of_token[t])
         lo = max(0, p - window + 1) if window > 0 else 0
         js = torch.arange(lo, p + 1, device=q.device)
-        pages = block_table[seq].long()[js // page]
+        pages = block_table[_row(table_rows, seq)].long()[js // page]
         keep = pages >= 0
         js, pages = js[keep], pages[keep]
         kk = k_pages[pages, :, js % page].float()      # [n, NKV, D]
@@ -109,9 +126,9 @@ def attention_generic(q, out, k_pages, v_pages, positions, seq_of_token, block_t
     return out
 
 
-def attention(qkv, out, k_pages, v_pages, ctx, block_table, num_heads, num_kv_heads, head_dim, scale, window=0):
+def attention(qkv, out, k_pages, v_pages, ctx, block_table, num_heads, num_kv_heads, head_dim, scale, window=0, work=None):
     return attention_generic(qkv, out, k_pages, v_pages, ctx.positions, ctx.seq_of_token, block_table, num_heads,
-                             num_kv_heads, head_dim, scale, window)
+                             num_kv_heads, head_dim, scale, window, table_rows=getattr(ctx, "table_rows", None))
 
 
 def gemm_simt(a, w, out):
@@ -132,7 +149,7 @@ def argmax(logits, out):
     return out
 
 
-PATCHABLE = ["embed", "add_rmsnorm", "swiglu", "qk_norm_rope_append", "attention_generic", "attention", "gemm_simt",
+PATCHABLE = ["embed", "add_rmsnorm", "swiglu", "add_bias", "table_update", "qk_norm_rope_append", "attention_generic", "attention", "gemm_simt",
              "linear_bf16", "linear_bf16_f32out", "argmax"]
 
 

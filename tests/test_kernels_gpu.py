@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import kernel_refs as ref
-from acvram_b200.engine.batch import QUERY_TILE
+from acvram_b200.kernels.ops import QUERY_TILE
 
 pytestmark = pytest.mark.gpu
 

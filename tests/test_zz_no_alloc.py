@@ -5,8 +5,8 @@ allocator, a process that has given all device memory to its own pool, a loop th
 not enter cudaMalloc.  For them the split-KV decode attention exists once more with its
 scratch in a fixed device array inside the library (csrc/no_alloc.h).  This test calls
 that symbol with raw pointers, twice in a row with different shapes (the array keeps what
-the first call left), and compares each result with the ordinary entry point's, within
-the bfloat16 tolerance of the kernel tests.  It stands in a file of its own that pytest
+the first call left), and compares each result with the ordinary entry point's and with
+the float32 reference of the kernel tests, within their bfloat16 tolerance.  It stands in a file of its own that pytest
 collects last.
 """
 
@@ -58,6 +58,11 @@ def _case(seed, lens, NH, NKV, D, page, n_splits):
     assert rc == 0, f"acv_attention_decode_static returned {rc}"
     torch.cuda.synchronize()
     torch.testing.assert_close(got, want, rtol=1.6e-2, atol=1.6e-2)
+    # and against the plain float32 reference, so that a fault shared by both entry points would show too
+    import kernel_refs
+    plain = torch.zeros_like(want)
+    kernel_refs.attention_generic(q, plain, kp, vp, kv_len - 1, rows, table, NH, NKV, D, scale, 0)
+    torch.testing.assert_close(got, plain, rtol=1.6e-2, atol=1.6e-2)
     return lib
 
 
