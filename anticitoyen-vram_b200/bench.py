@@ -23,26 +23,20 @@ from .kernels import ops
 
 
 # --------------------------------------------------------------------------- arithmetic of a step
-def layer_matrix_params(cfg) -> int:
-    H, I = cfg.hidden_size, cfg.intermediate_size
-    return H * (cfg.q_size + 2 * cfg.kv_size) + cfg.q_size * H + 3 * H * I
-
-
-def kv_bytes_per_token(cfg, num_layers: int, itemsize: int = 2) -> int:
-    return num_layers * 2 * cfg.kv_size * itemsize
-
-
-def decode_step_bytes(cfg, num_layers: int, batch: int, context: int, itemsize: int = 2) -> int:
+# What a step has to read and compute is asked of the model (``DecoderModel.step_cost``: every scheduled part reports
+# its own weights, products, mixing and cache reads), so the figures follow the plan that runs, whatever the architecture.
+def decode_step_bytes(model, batch: int, context: int) -> int:
     """Bytes a decode step has to read: every weight it uses once, and the cache of the live requests."""
-    weights = (num_layers * (layer_matrix_params(cfg) + 2 * cfg.hidden_size + 2 * cfg.head_dim) + cfg.hidden_size
-               + cfg.vocab_size * cfg.hidden_size) * itemsize
-    return weights + batch * context * kv_bytes_per_token(cfg, num_layers, itemsize)
+    cost = model.step_cost([1] * batch, [context] * batch, batch)
+    return cost["weight_bytes"] + cost["cache_bytes"]
 
 
-def prefill_flops(cfg, num_layers: int, tokens: int, logit_rows: int = 1) -> float:
-    matmul = 2.0 * tokens * num_layers * layer_matrix_params(cfg) + 2.0 * logit_rows * cfg.vocab_size * cfg.hidden_size
-    attention = num_layers * 4.0 * cfg.num_attention_heads * cfg.head_dim * tokens * (tokens + 1) / 2
-    return matmul + attention
+def prefill_flops(model, tokens: int, logit_rows: int = 1) -> float:
+    return model.step_cost([tokens], [tokens], logit_rows)["flops"]
+
+
+class Refused(RuntimeError):
+    """A measurement whose preconditions failed: its number is not published (acvram/bench.py:426-447)."""
 
 
 # --------------------------------------------------------------------------- clocks during the timed region
@@ -118,11 +112,15 @@ def fill_contexts(runner, names: list, context: int, chunk: int = 2048) -> None:
 
 
 def time_decode(runner, names: list, steps: int, warmup: int) -> dict:
-    """W untimed then K timed decode steps of the live requests ``names``; tokens stay on the device."""
+    """W untimed then K timed decode steps of the live requests ``names``; tokens stay on the device.
+
+    Refused (``Refused``) when a timed step did not replay a captured graph although graphs are on, when a kernel
+    gave up a bounded wait, or when the requests did not all advance by exactly K + W tokens."""
     B = len(names)
     dev = runner.rt.device
     tokens = torch.full((B,), 11, dtype=torch.int32, device=dev)
     entries = [StepEntry(n, [0], (0,)) for n in names]
+    before = [runner.manager.lengths[n] for n in names]
 
     def one():
         logits = runner.step(entries, device_tokens=tokens)
@@ -133,6 +131,7 @@ def time_decode(runner, names: list, steps: int, warmup: int) -> dict:
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     torch.cuda.synchronize(dev)
     launches0 = ops.LAUNCHES + getattr(runner, "graph_launches", 0)
+    replays0 = runner.graphs.replays if runner.graphs is not None else 0
     start.record()
     for _ in range(steps):
         one()
@@ -140,8 +139,56 @@ def time_decode(runner, names: list, steps: int, warmup: int) -> dict:
     torch.cuda.synchronize(dev)
     ms = start.elapsed_time(end) / steps
     launches = ops.LAUNCHES + getattr(runner, "graph_launches", 0) - launches0
+    if ops.gemm_status():
+        ops.reset_after_failure()
+        raise Refused("a kernel gave up a bounded wait during the timed steps")
+    if runner.graphs is not None and runner.graphs.disabled_reason is None and runner.graphs.replays - replays0 != steps:
+        raise Refused(f"{steps - (runner.graphs.replays - replays0)} of {steps} timed steps did not replay a captured graph")
+    if [runner.manager.lengths[n] - b for n, b in zip(names, before)] != [steps + warmup] * B:
+        raise Refused("the requests did not all advance by one token per step")
     return {"ms_per_step": ms, "tokens_per_s": B * 1000.0 / ms, "launches": launches, "batch": B,
             "context_end": runner.manager.lengths[names[0]]}
+
+
+def time_mixed(runner, names: list, portion: int, prompt_len: int, steps: int, warmup: int) -> dict:
+    """Steps that serving makes under load: every live request of ``names`` decodes one token beside a portion of
+    ``portion`` tokens of another request's prompt (prompts of ``prompt_len`` tokens, one after the other; a prompt
+    that is through gives its pages to the next).  Returns ms per step and tokens per second (all tokens of a step)."""
+    B = len(names)
+    dev = runner.rt.device
+    vocab = runner.model.plan.vocab_size
+    tokens = torch.full((B,), 11, dtype=torch.int32, device=dev)
+    state = {"k": 0, "pos": 0, "ids": synthetic_ids(vocab, prompt_len, 5000)}
+
+    def one():
+        name = f"mixed-prompt-{state['k']}"
+        ids = state["ids"][state["pos"]:state["pos"] + portion]
+        last = state["pos"] + len(ids) >= prompt_len
+        entries = [StepEntry(n, [11], (0,)) for n in names] + [StepEntry(name, ids, (len(ids) - 1,) if last else ())]
+        logits = runner.step(entries)
+        ops.argmax(logits[:B], tokens)
+        state["pos"] += len(ids)
+        if last:
+            runner.release(name)
+            state.update(k=state["k"] + 1, pos=0, ids=synthetic_ids(vocab, prompt_len, 5001 + state["k"]))
+
+    for _ in range(warmup):
+        one()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+    start.record()
+    for _ in range(steps):
+        one()
+    end.record()
+    torch.cuda.synchronize(dev)
+    name = f"mixed-prompt-{state['k']}"
+    if name in runner.manager.lengths:
+        runner.release(name)
+    if ops.gemm_status():
+        ops.reset_after_failure()
+        raise Refused("a kernel gave up a bounded wait during the timed steps")
+    ms = start.elapsed_time(end) / steps
+    return {"ms_per_step": ms, "tokens_per_s": (B + portion) * 1000.0 / ms, "decode_tokens_per_s": B * 1000.0 / ms}
 
 
 def time_prefill(runner, tokens: int, reps: int = 3, warmup: int = 1) -> dict:
@@ -160,6 +207,9 @@ def time_prefill(runner, tokens: int, reps: int = 3, warmup: int = 1) -> dict:
         runner.release(name)
         if k >= warmup:
             times.append(start.elapsed_time(end))
+    if ops.gemm_status():
+        ops.reset_after_failure()
+        raise Refused("a kernel gave up a bounded wait during the timed steps")
     ms = statistics.median(times)
     return {"ms": ms, "tokens": tokens, "tokens_per_s": tokens * 1000.0 / ms, "spread_ms": max(times) - min(times)}
 

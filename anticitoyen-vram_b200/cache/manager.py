@@ -73,6 +73,12 @@ class PagedNeed:
     def kind(self) -> str:
         return "paged"
 
+    @property
+    def takes_over(self) -> bool:
+        """Whether a new request can start on pages that an earlier request filled: yes where all keys are kept
+        (a window gives pages back as it goes, so an earlier request's first pages are gone)."""
+        return self.window <= 0
+
 
 @dataclass(frozen=True)
 class StateNeed:
@@ -82,6 +88,12 @@ class StateNeed:
     @property
     def kind(self) -> str:
         return "state"
+
+    @property
+    def takes_over(self) -> bool:
+        """A state of fixed size has no page to hand to a later request; a mixer that wanted to join prefix reuse
+        would have to keep a copy of its state at every page's end (the hook is not built: no part here needs it)."""
+        return False
 
 
 class PagePool:
@@ -351,8 +363,8 @@ class CacheManager:
         for g in self._paged:
             g.rows = self.rows
         # pages are taken over only where every group keeps all keys in pages
-        self.prefix_reuse = bool(enable_prefix_cache) and bool(self.groups) and all(
-            isinstance(g, PagedGroup) and g.need.window <= 0 for g in self.groups)
+        # (every group is asked: each need says whether what it keeps can be handed to a later request)
+        self.prefix_reuse = bool(enable_prefix_cache) and bool(self.groups) and all(g.need.takes_over for g in self.groups)
         self.reused_tokens = 0          # tokens that requests took over instead of computing them
 
     # ------------------------------------------------------------------ prefix reuse

@@ -15,7 +15,8 @@ class CacheStorage:
     so a tile of keys is a run of ``page_size * head_dim`` elements.  The
     reference keeps ``[num_blocks, 16, kv_heads, head_dim]`` per layer
     (acvram/memory/kvcache.py:463-469).  State group:
-    ``[slots, max_requests, *shape]``.  Everything starts at zero, so that a key
+    ``[slots, max_requests + 1, *shape]`` (the last slot belongs to nobody: padding rows of a
+    fixed-shape batch work on it).  Everything starts at zero, so that a key
     that is masked out never brings a NaN into a product.
 
     Beside its pages a paged group has its block table on the device, int32
@@ -40,7 +41,7 @@ class CacheStorage:
                 self.tables[gi] = torch.full((manager.max_requests + 1, width), -1, device=self.device, dtype=torch.int32)
             else:
                 sdtype = getattr(torch, g.need.dtype)
-                self.tensors.append(torch.zeros((g.num_slots, g.max_requests, *g.need.shape), device=self.device,
+                self.tensors.append(torch.zeros((g.num_slots, g.max_requests + 1, *g.need.shape), device=self.device,
                                                 dtype=sdtype))
 
     def bytes(self) -> int:
@@ -58,7 +59,7 @@ class CacheStorage:
         return t[0], t[1]
 
     def state(self, cache_slot: int) -> torch.Tensor:
-        """State of a cache slot for all request slots: ``[max_requests, *shape]``."""
+        """State of a cache slot for all request slots: ``[max_requests + 1, *shape]``."""
         plan = self.manager.plan
         return self.tensors[plan.group_of_slot[cache_slot]][plan.index_in_group[cache_slot]]
 

@@ -20,8 +20,9 @@ import sys
 from . import __version__
 
 
-def _engine_args(p: argparse.ArgumentParser) -> None:
-    p.add_argument("model", help="model folder (config.json and safetensors), or a config.json with --random-weights")
+def _engine_args(p: argparse.ArgumentParser, model_optional: bool = False) -> None:
+    p.add_argument("model", nargs="?" if model_optional else None,
+                   help="model folder (config.json and safetensors), or a config.json with --random-weights")
     p.add_argument("--random-weights", action="store_true", help="ignore the folder's weights; draw them from --seed")
     p.add_argument("--seed", type=int, default=0, help="seed of random weights and of sampling")
     p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
@@ -71,8 +72,24 @@ def cmd_generate(args) -> int:
 
 def cmd_bench(args) -> int:
     from .bench import bench_decode
-    if args.what not in ("all", "decode"):
-        print(f"bench --what {args.what}: only 'decode' is built", file=sys.stderr)
+    if args.what not in ("all", "decode", "kernels"):
+        print(f"bench --what {args.what}: 'decode' and 'kernels' are built", file=sys.stderr)
+        return 2
+    if args.what == "kernels":
+        import contextlib
+        from .profile_cases import CASES, bench_kernels
+        cases = args.case.split(",") if args.case else None
+        unknown = [c for c in cases or () if c not in CASES]
+        if unknown:
+            print(f"bench --what kernels: no case named {', '.join(unknown)}; there are {', '.join(sorted(CASES))}", file=sys.stderr)
+            return 2
+        with contextlib.redirect_stdout(sys.stderr if args.json else sys.stdout):
+            res = bench_kernels(cases)
+        if args.json:
+            print(json.dumps(res))
+        return 0
+    if not args.model:
+        print("bench --what decode needs a model folder (or a config.json with --random-weights)", file=sys.stderr)
         return 2
     res = bench_decode(args.model, random_weights=args.random_weights, seed=args.seed, dtype=args.dtype,
                        batches=[int(b) for b in args.batch.split(",")], context=args.context,
@@ -127,9 +144,10 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--json", action="store_true")
     g.set_defaults(func=cmd_generate)
 
-    b = sub.add_parser("bench", help="measure decode throughput")
-    _engine_args(b)
-    b.add_argument("--what", default="decode", help="all | decode")
+    b = sub.add_parser("bench", help="measure decode throughput, or the hot kernels one by one")
+    _engine_args(b, model_optional=True)
+    b.add_argument("--what", default="decode", help="all | decode | kernels (the reference's names, acvram/cli.py:1476)")
+    b.add_argument("--case", default="", help="with --what kernels: the cases to run, comma separated (default: all)")
     b.add_argument("--batch", default="1", help="batch sizes, comma separated")
     b.add_argument("--context", type=int, default=128, help="tokens of context before decoding (reference: 128)")
     b.add_argument("--tokens", type=int, default=256, help="tokens decoded per request (reference: 256)")

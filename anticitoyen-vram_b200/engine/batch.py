@@ -144,6 +144,7 @@ class BatchBuilder:
         Returns (offsets, ints a step brings, ints in all)."""
         off, out = 0, {}
         dynamic = [("tokens", padded), ("positions", padded), ("kv_len", padded), ("table_rows", padded),
+                   *[(f"st{gi}", padded) for gi, g in enumerate(self.manager.groups) if not isinstance(g, PagedGroup)],
                    *[(f"upd{gi}", 3 * 2 * padded) for gi, _ in self._paged]]
         for name, n in dynamic:
             out[name] = (off, n)
@@ -179,6 +180,11 @@ class BatchBuilder:
         put("positions", list(starts))
         put("kv_len", [s + 1 for s in starts])
         put("table_rows", [m.rows[e.request] for e in entries], fill=m.null_row)
+        last_fixed = "table_rows"
+        for gi, g in enumerate(m.groups):
+            if not isinstance(g, PagedGroup):      # padding rows work on the state slot that belongs to nobody
+                put(f"st{gi}", [g.slot_of[e.request] for e in entries], fill=g.max_requests)
+                last_fixed = f"st{gi}"
         updates = m.take_updates()
         late = []      # more changed entries than the fixed section holds (rare: sent by themselves)
         views = []
@@ -203,7 +209,7 @@ class BatchBuilder:
                 for name, a in metas[key].arrays.items():
                     put(f"{key}.{name}", np.asarray(a, dtype=np.int32).reshape(-1))
         # a step sends what it brings: up to the end of the last changed table entry (the rest of the buffer is static)
-        n_send = layout["table_rows"][0] + _round4(padded)
+        n_send = layout[last_fixed][0] + _round4(padded)
         for gi, _, n_upd in views:
             if n_upd:
                 n_send = max(n_send, layout[f"upd{gi}"][0] + _round4(3 * n_upd))
@@ -225,8 +231,11 @@ class BatchBuilder:
             positions=view("positions"), seq_of_token=view("seq_of_token"), cu_q=view("cu_q"), kv_len=view("kv_len"),
             logit_rows=view("logit_rows"), table_rows=view("table_rows"), requests=[e.request for e in entries],
             q_lens=[1] * padded, kv_lens=kv_lens + [0] * (padded - B))
-        for gi, _ in self._paged:
-            ctx.block_tables[gi] = self.storage.tables[gi]
+        for gi, g in enumerate(m.groups):
+            if isinstance(g, PagedGroup):
+                ctx.block_tables[gi] = self.storage.tables[gi]
+            else:
+                ctx.state_slots[gi] = view(f"st{gi}")
         for key, meta in metas.items():
             ctx.work[key] = {**{name: view(f"{key}.{name}") for name in meta.arrays}, **meta.values}
         return ctx

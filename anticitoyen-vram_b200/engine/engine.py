@@ -142,13 +142,18 @@ class Engine:
 
     def _default_pages(self, max_batch_size: int, device) -> int:
         """Pages for max_batch_size requests of max_model_len tokens, within 85 % of the free memory."""
-        per_page = 0
+        per_page = state_bytes = 0
         for need in self.model.cache_plan().needs:
             if need is not None and need.kind == "paged":
                 per_page += 2 * need.num_kv_heads * need.head_dim * self.page_size * self.model.rt.dtype.itemsize
+            elif need is not None:       # state of fixed size: a slot for each request (and one for nobody)
+                n = 1
+                for d in need.shape:
+                    n *= d
+                state_bytes += n * getattr(torch, need.dtype).itemsize * (max_batch_size + 1)
         want = max_batch_size * ((self.max_model_len + self.page_size - 1) // self.page_size)
         free, _ = torch.cuda.mem_get_info(torch.device(device))
-        fit = int(free * 0.85 // max(per_page, 1))
+        fit = int(max(0, free * 0.85 - state_bytes) // max(per_page, 1))
         return max(1, min(want, fit))
 
     # ------------------------------------------------------------------ requests

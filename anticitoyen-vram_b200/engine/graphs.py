@@ -47,8 +47,11 @@ class DecodeGraphs:
         self.launches = 0       # kernels of this package run through replays
         self.refused = 0        # decode steps that ran without a graph because the table of graphs was full
         self.disabled_reason: str | None = None
-        if runner.manager.state_groups:
-            self.disabled_reason = "the model keeps per-request state of fixed size"
+        # a part whose forward reads device memory on the host (a toy that loops over requests in Python, say)
+        # cannot be captured; everything else can, state of fixed size included (its slots travel with the step)
+        blocked = runner.model.uncapturable_parts() if hasattr(runner.model, "uncapturable_parts") else []
+        if blocked:
+            self.disabled_reason = "parts that cannot run in a CUDA graph: " + ", ".join(blocked)
 
     def usable(self, entries) -> bool:
         return (self.disabled_reason is None and all(len(e.tokens) == 1 for e in entries)

@@ -84,12 +84,15 @@ class ModelRunner:
                 self.admit(e.request)
             start = m.lengths[e.request]
             if start == 0:     # a request's first step (also after a preemption): its state starts at zero
-                for gi, g in enumerate(m.groups):
-                    if g.need.kind == "state":
-                        self.storage.zero_state(gi, g.slot_of[e.request])
+                self._zero_state(e.request)
             m.grow(e.request, start + len(e.tokens))   # takes nothing if the scheduler reserved already
             starts.append(start)
         return self.builder.build(entries, starts)
+
+    def _zero_state(self, request: Hashable) -> None:
+        for gi, g in enumerate(self.manager.groups):
+            if g.need.kind == "state":
+                self.storage.zero_state(gi, g.slot_of[request])
 
     def _graph_step(self, entries, device_tokens):
         m = self.manager
@@ -102,6 +105,8 @@ class ModelRunner:
             if start + 1 > self.max_len:
                 raise ValueError(f"request {e.request!r} would pass the {self.max_len} tokens that the model's positions "
                                  f"and the cache hold")
+            if start == 0:
+                self._zero_state(e.request)
             m.grow(e.request, start + 1)
             starts.append(start)
         with torch.cuda.device(self.rt.device):

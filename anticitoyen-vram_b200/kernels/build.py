@@ -27,7 +27,6 @@ NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "--expt-relaxed-constexpr", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
 ]
-NVCC_FLAGS += os.environ.get("ACVRAM_B200_NVCC_FLAGS", "").split()      # extra flags (experiments); part of the hash
 LIB_PREFIX = "libacvram_b200_"
 if os.environ.get("ACVRAM_B200_TIMELINE", "0") not in ("", "0"):
     NVCC_FLAGS.append("-DACV_TIMELINE")      # diagnostic build: kernels log their CTAs' begin and end times

@@ -9,7 +9,6 @@ CUDA device, the first call raises.
 from __future__ import annotations
 
 import ctypes
-import os
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -45,8 +44,6 @@ def library() -> ctypes.CDLL:
             raise KernelError(f"the CUDA kernels of acvram_b200 could not be built: {exc}") from exc
         lib = ctypes.CDLL(path)
         _declare(lib)
-        if os.environ.get("ACVRAM_B200_PDL"):
-            lib.acv_set_pdl(int(os.environ["ACVRAM_B200_PDL"], 0))
         _lib = lib
     return _lib
 

@@ -115,6 +115,15 @@ class DecoderModel:
                 cache_bytes += mixer.cache_bytes_read(q_lens, kv_lens, itemsize)
         return {"weight_bytes": weight_bytes, "cache_bytes": cache_bytes, "flops": flops}
 
+    def uncapturable_parts(self) -> list[str]:
+        """Kinds of the parts whose ``capturable`` is false (their forward cannot run inside a CUDA graph)."""
+        out = []
+        for block in self.blocks:
+            for part in (block, *vars(block).values()):
+                if getattr(part, "capturable", True) is False and getattr(part, "kind", "?") not in out:
+                    out.append(getattr(part, "kind", "?"))
+        return out
+
     def metadata_providers(self) -> dict:
         """{key: a mixer that makes the per-step data its kind needs}: one for each distinct ``metadata_key``."""
         out = {}

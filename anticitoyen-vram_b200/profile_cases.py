@@ -1,10 +1,13 @@
-"""Small cases of the hot kernels, for profiling under ncu.
+"""The hot kernels one by one: ``acvram bench --what kernels`` (the reference's name for its per-kernel
+measurements, acvram/cli.py:1476), and the small cases that are profiled under ncu.
 
+    acvram bench --what kernels [--case NAME] [--json]
     python -m acvram_b200.profile_cases gemm_decode|gemm_prefill|attention_decode|attention_prefill [--reps N]
 
 Each case runs a few launches of one kernel at the layer sizes of Qwen3-8B on inputs larger than
 the L2 cache (weights and pages rotate), holding a few GB at most, and ends by itself in seconds;
-it prints the mean CUDA-event time of a launch.  The summaries under profiles/ name the command.
+it reports the mean CUDA-event time of a launch with the bytes or operations per second that this
+makes.  The summaries under profiles/ name the command.
 """
 
 from __future__ import annotations
@@ -30,7 +33,7 @@ def _time(fn, reps: int) -> float:
     return s.elapsed_time(e) / reps * 1e3
 
 
-def gemm_case(M: int, N: int, K: int, reps: int) -> None:
+def gemm_case(M: int, N: int, K: int, reps: int) -> dict:
     copies = max(2, int(400e6 // (N * K * 2)) + 1)
     ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
@@ -39,9 +42,11 @@ def gemm_case(M: int, N: int, K: int, reps: int) -> None:
     plan = ops.gemm_tc_plan(M, N, K)
     print(f"gemm_tc M={M} N={N} K={K} plan(swap, bn, splits)={plan}: {us:.1f} us, "
           f"{N * K * 2 / us / 1e3:.0f} GB/s of weights, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
+    return {"kernel": "gemm_tc", "M": M, "N": N, "K": K, "us": us, "weights_gbs": N * K * 2 / us / 1e3,
+            "tflops": 2 * M * N * K / us / 1e6}
 
 
-def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool = False, page: int = 64) -> None:
+def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool = False, page: int = 64) -> dict:
     NH, NKV, D = 32, 8, 128
     pages_per = (context + page - 1) // page
     n_pages = batch * pages_per
@@ -62,6 +67,7 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
         us = _time(fn, reps)
         gb = batch * context * NKV * D * 2 * 2 / 1e9
         print(f"attention_decode batch={batch} context={context} page={page} splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of pages")
+        return {"kernel": "attention_decode", "batch": batch, "context": context, "us": us, "pages_gbs": gb / us * 1e6}
     else:
         tiles = [(b, s) for b in range(batch) for s in range(0, q_len, QUERY_TILE)][::-1]
         tile_seq = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
@@ -72,6 +78,7 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
         us = _time(fn, reps)
         flops = batch * 4.0 * NH * D * (q_len * (context - q_len) + q_len * (q_len + 1) / 2)
         print(f"{kernel.__name__} batch={batch} q_len={q_len} context={context} page={page}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
+        return {"kernel": kernel.__name__, "batch": batch, "q_len": q_len, "context": context, "us": us, "tflops": flops / us / 1e6}
 
 
 CASES = {
@@ -85,6 +92,12 @@ CASES = {
     "attention_prefill_8k": lambda r: attention_case(1, 2048, 8192, r),
     "attention_prefill_mma_sync": lambda r: attention_case(1, 2048, 2048, r, legacy=True),
 }
+
+
+def bench_kernels(cases=None, reps: int = 6) -> dict:
+    """{case: its figures} for the named cases (default: all)."""
+    ops.library()
+    return {name: CASES[name](reps) for name in (cases or sorted(CASES))}
 
 
 def main(argv=None) -> int:

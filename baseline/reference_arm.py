@@ -84,7 +84,7 @@ def run(args) -> int:
     sys.path.insert(0, REF)
     work = tempfile.mkdtemp(prefix="acvram_ref_", dir=os.environ.get("ACVRAM_REF_TMP", tempfile.gettempdir()))
     try:
-        from bench import SHAPES  # the sizes bench.py names
+        from bench import SHAPES, bench_config  # the sizes and the configuration keys that bench.py names
 
         shape = SHAPES[getattr(args, "shape", "8b")]
         shape_name = f"Qwen3-{getattr(args, 'shape', '8b').upper()} shape"
@@ -142,9 +142,9 @@ def run(args) -> int:
                 "value": round(tokens / dt, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
                 "ms_per_step": round(dt / K * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
                 "dtype": "bf16", "data": "synthetic token ids, random weights N(0,0.02)",
-                "config": {"model": shape_name, "layers": layers, "layers_full": shape["num_hidden_layers"],
-                           "global_batch": args.batch, "seq_len": args.context, "max_model_len": max_len,
-                           "kv_dtype": "bf16", "parallelism": "single GPU", "timing": "wall clock around Engine.step"},
+                # the same keys and, where they describe the workload, the same values as the other arm's line; the
+                # reference's page is 16 tokens, fixed in its code, and it times with the wall clock around Engine.step
+                "config": bench_config(args, cfg, layers, shape["num_hidden_layers"], 16, True),
                 "e2e": {"value": round(tokens / dt, 1), "unit": "tokens/s"}}
         print(json.dumps(line))
         return 0

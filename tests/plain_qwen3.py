@@ -116,34 +116,44 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: f
     return torch.einsum("hqk,khd->qhd", p, v32).to(q.dtype)
 
 
-def linear(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
-    """y = x @ W^T, W is [out, in]; no bias (acvram/engine/layers.py:463-558)."""
-    return (x.to(torch.float32) @ w.to(torch.float32).T).to(x.dtype)
+def linear(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor | None = None) -> torch.Tensor:
+    """y = x @ W^T (+ b), W is [out, in] (acvram/engine/layers.py:463-558).  A bias exists where the file holds a
+    ``.bias`` tensor beside the weight (acvram/engine/loader.py:269-270); Qwen3's files hold none.  The product is
+    rounded to the model dtype, then the bias is added in 32-bit and the sum rounded."""
+    y = (x.to(torch.float32) @ w.to(torch.float32).T).to(x.dtype)
+    if b is not None:
+        y = (y.to(torch.float32) + b.to(torch.float32)).to(x.dtype)
+    return y
+
+
+def proj(x: torch.Tensor, t: dict, name: str) -> torch.Tensor:
+    """The projection stored as ``name + "weight"`` (and ``name + "bias"`` when present)."""
+    return linear(x, t[name + "weight"], t.get(name + "bias"))
 
 
 def attention_block(h: torch.Tensor, t: dict, p: str, s: dict, positions: torch.Tensor, window: int = 0) -> torch.Tensor:
     """q/k/v projections, QK-norm, rotation, attention, o projection
     (acvram/engine/attention.py:290-365, 519-584)."""
     T = h.shape[0]
-    q = linear(h, t[p + "self_attn.q_proj.weight"]).view(T, s["NH"], s["D"])
-    k = linear(h, t[p + "self_attn.k_proj.weight"]).view(T, s["NKV"], s["D"])
-    v = linear(h, t[p + "self_attn.v_proj.weight"]).view(T, s["NKV"], s["D"])
+    q = proj(h, t, p + "self_attn.q_proj.").view(T, s["NH"], s["D"])
+    k = proj(h, t, p + "self_attn.k_proj.").view(T, s["NKV"], s["D"])
+    v = proj(h, t, p + "self_attn.v_proj.").view(T, s["NKV"], s["D"])
     cos, sin = rotary_tables(positions, s["D"], s["theta"])
     q = qk_norm_rotary(q, t[p + "self_attn.q_norm.weight"], s["eps"], cos, sin)
     k = qk_norm_rotary(k, t[p + "self_attn.k_norm.weight"], s["eps"], cos, sin)
     o = causal_attention(q, k, v, s["D"] ** -0.5, window)
-    return linear(o.reshape(T, s["NH"] * s["D"]), t[p + "self_attn.o_proj.weight"])
+    return proj(o.reshape(T, s["NH"] * s["D"]), t, p + "self_attn.o_proj.")
 
 
 def swiglu_mlp(h: torch.Tensor, t: dict, p: str) -> torch.Tensor:
     """y = (silu(g) * u) @ Wd^T with silu(g) = g/(1+exp(-g)) in 32-bit, rounded to
     the model dtype before the product (acvram/engine/attention.py:745-761;
     kernel acvram/kernels/acvram_kernels.cu:8441-8452)."""
-    g = linear(h, t[p + "mlp.gate_proj.weight"])
-    u = linear(h, t[p + "mlp.up_proj.weight"])
+    g = proj(h, t, p + "mlp.gate_proj.")
+    u = proj(h, t, p + "mlp.up_proj.")
     g32 = g.to(torch.float32)
     act = (g32 / (1.0 + torch.exp(-g32))).to(h.dtype)
-    return linear(act * u, t[p + "mlp.down_proj.weight"])
+    return proj(act * u, t, p + "mlp.down_proj.")
 
 
 def residual_add(x: torch.Tensor, y: torch.Tensor) -> torch.Tensor:

@@ -158,6 +158,13 @@ def test_command_line_generate_and_random_model(tiny_folders, plain_models, tmp_
     res = json.loads(out.stdout.strip().splitlines()[-1])
     assert res["decode_b1"]["tokens_per_s"] > 0 and res["decode_b3"]["tokens_per_s"] > res["decode_b1"]["tokens_per_s"] * 0.5
     assert res["prefill"]["tokens"] == 40 and res["prefill"]["tokens_per_s"] > 0
+    # `bench --what kernels`: the hot kernels one by one, here two cases of them
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "acvram"), "bench", "--what", "kernels", "--case",
+                          "gemm_decode,attention_decode", "--json"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    res = json.loads(out.stdout.strip().splitlines()[-1])
+    assert res["gemm_decode"]["kernel"] == "gemm_tc" and res["gemm_decode"]["weights_gbs"] > 100
+    assert res["attention_decode"]["pages_gbs"] > 100
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
