@@ -106,13 +106,13 @@ def register_toys():
             self.t = {k: v.to(rt.device, torch.float32) for k, v in tensors.items()}
 
         def forward(self, h, ctx):
+            # both experts run on every token and the router picks the result: no shape depends on the data, so
+            # the host never has to read the choice (a toy: a real routed feed-forward would permute the tokens)
             x = h.float()
             choice = (x @ self.t["toy_router.weight"].T).argmax(-1)
-            out = torch.zeros_like(x)
-            for e in range(2):
-                m = choice == e
-                out[m] = torch.relu(x[m] @ self.t[f"toy_experts.{e}.up.weight"].T) @ self.t[f"toy_experts.{e}.down.weight"].T
-            return out.to(h.dtype)
+            outs = [torch.relu(x @ self.t[f"toy_experts.{e}.up.weight"].T) @ self.t[f"toy_experts.{e}.down.weight"].T
+                    for e in range(2)]
+            return torch.where((choice == 0)[:, None], outs[0], outs[1]).to(h.dtype)
 
 
 def toy_plan(cfg, state_mixer=("toy_decay", {"decay": 0.9})):
