@@ -88,12 +88,36 @@ def _declare(lib: ctypes.CDLL) -> None:
         fn.restype = c_int
     lib.acv_set_pdl.argtypes = [c_int]
     lib.acv_set_pdl.restype = None
+    lib.acv_decode_layer.argtypes = [ctypes.POINTER(DecodeLayerArgs), P]
+    lib.acv_decode_layer.restype = c_int
+    lib.acv_decode_layer_takes.argtypes = [I] * 8
+    lib.acv_decode_layer_takes.restype = c_int
     lib.acv_random_normal.argtypes = [P, LL, ctypes.c_ulonglong, F, F, P, P, I, P]
     lib.acv_random_normal.restype = c_int
     lib.acv_random_int.argtypes = [P, LL, ctypes.c_ulonglong, ctypes.c_uint, P]
     lib.acv_random_int.restype = c_int
     lib.acv_gemm_tc_test_fault.argtypes = [c_int, c_int]
     lib.acv_gemm_tc_test_fault.restype = None
+
+
+class DecodeLayerArgs(ctypes.Structure):
+    """The arguments of ``acv_decode_layer`` (csrc/decode_layer.cu, ``DlLayerArgs``), field for field."""
+    _P, _I, _F, _LL = c_void_p, c_int, c_float, ctypes.c_longlong
+    _fields_ = [
+        ("T", _I), ("H", _I), ("I", _I), ("NH", _I), ("NKV", _I), ("D", _I),
+        ("eps", _F), ("qk_eps", _F), ("scale", _F),
+        ("x", _P), ("delta_in", _P), ("w_norm1", _P), ("w_norm2", _P),
+        ("w_qkv", _P), ("w_o", _P), ("w_gu", _P), ("w_down", _P),
+        ("q_norm", _P), ("k_norm", _P), ("cos_sin", _P), ("table_rows", _I),
+        ("positions", _P), ("seq_of_token", _P), ("kv_len", _P),
+        ("block_table", _P), ("bt_stride", _I), ("bt_rows", _P),
+        ("k_pages", _P), ("v_pages", _P), ("page_size", _I), ("num_pages", _I),
+        ("h", _P), ("qkv", _P), ("attn_out", _P), ("a_out", _P), ("act", _P), ("delta_out", _P),
+        ("workspace", _P), ("workspace_floats", _LL), ("counters", _P), ("n_counters", _LL),
+        ("part", _P), ("part_floats", _LL), ("att_counters", _P), ("n_att_counters", _LL),
+        ("bars", _P), ("status", _P),
+        ("sm_count", _I), ("max_kv", _I),
+    ]
 
 
 LAUNCHES = 0   # kernels of this package launched so far (library matrix products are not counted)
@@ -435,6 +459,8 @@ def reset_after_failure() -> None:
         cnt.zero_()
     for _, _, cnt in _scratch.values():
         cnt.zero_()
+    for buf in _layer_scratch.values():
+        buf["bars"].zero_()
 
 
 def gemm_tc_test_fault(wait_limit: int, skip_k_block: int) -> None:
@@ -651,6 +677,69 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
                         block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows,
                         max_kv=w.get("max_tile_kv", 0))
     return out
+
+
+# ----------------------------------------------------------------------------- one decoder layer of a decode step
+DECODE_LAYER_TOKENS = 16     # DL_BN of decode_layer.cu
+_layer_scratch: dict = {}
+
+
+def decode_layer_takes(T: int, H: int, I: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                       window: int) -> bool:
+    """Whether the fused decode-layer kernel runs a layer of these sizes for a step of ``T`` one-token requests."""
+    return bool(library().acv_decode_layer_takes(T, H, I, num_heads, num_kv_heads, head_dim, page_size, window))
+
+
+def _layer_buffers(device, H: int, I: int, qkv_width: int, q_width: int):
+    """Activations of one layer (16 rows each) and the grid barriers, kept between calls (layers run one after the
+    other on one stream, and a captured graph holds the addresses)."""
+    key = (str(device), H, I, qkv_width, q_width)
+    have = _layer_scratch.get(key)
+    if have is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("decode_layer: its buffers would be made during a graph capture; run the shape once first")
+        n = DECODE_LAYER_TOKENS
+        mk = lambda w: torch.zeros((n, w), device=device, dtype=torch.bfloat16)
+        have = {"h": mk(H), "qkv": mk(qkv_width), "attn": mk(q_width), "a": mk(H), "act": mk(I),
+                "bars": torch.zeros(8, device=device, dtype=torch.int32)}
+        _layer_scratch[key] = have
+    return have
+
+
+def decode_layer(x: torch.Tensor, delta: torch.Tensor | None, delta_out: torch.Tensor, norm1_w: torch.Tensor,
+                 norm2_w: torch.Tensor, eps: float, w_qkv: torch.Tensor, w_o: torch.Tensor, w_gate_up_pairs: torch.Tensor,
+                 w_down: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, qk_eps: float,
+                 cos_sin: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                 positions: torch.Tensor, seq_of_token: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor,
+                 table_rows: torch.Tensor | None, k_pages: torch.Tensor, v_pages: torch.Tensor, max_kv: int) -> torch.Tensor:
+    """A whole pre-norm decoder layer for a step of up to 16 one-token requests in one persistent kernel
+    (csrc/decode_layer.cu): x += delta; a = attention(norm1(x)); x += a; delta_out = swiglu_mlp(norm2(x)).
+    ``x`` [T, H] is updated in place, ``delta_out`` [T, H] receives what the next layer adds; the keys and values of
+    the step's tokens go to their pages.  ``w_gate_up_pairs``: rows (gate_i, up_i) interleaved, as the fused SwiGLU
+    product takes them.  ``decode_layer_takes`` says for which sizes."""
+    _need_cuda(x, delta_out, w_qkv, k_pages)
+    T, H = x.shape
+    I = w_down.shape[1]
+    qkv_width, q_width = w_qkv.shape[0], num_heads * head_dim
+    buf = _layer_buffers(x.device, H, I, qkv_width, q_width)
+    n_rep = num_heads // num_kv_heads
+    sms = sm_count(x.device)
+    tiles = [-(-n // 128) for n in (qkv_width, H, 2 * I, H)]
+    ws, cnt, status = _gemm_buffers(x.device, max(tiles) * 16 * 16 * 128, sum(tiles))
+    part, _, att_cnt = _decode_scratch(x.device, sms * n_rep * (head_dim + 2), 0, DECODE_LAYER_TOKENS * num_kv_heads)
+    a = DecodeLayerArgs(
+        T=T, H=H, I=I, NH=num_heads, NKV=num_kv_heads, D=head_dim, eps=eps, qk_eps=qk_eps, scale=scale,
+        x=_p(x), delta_in=_p(delta), w_norm1=_p(norm1_w), w_norm2=_p(norm2_w), w_qkv=_p(w_qkv), w_o=_p(w_o),
+        w_gu=_p(w_gate_up_pairs), w_down=_p(w_down), q_norm=_p(q_norm), k_norm=_p(k_norm), cos_sin=_p(cos_sin),
+        table_rows=cos_sin.shape[0] if cos_sin is not None else 0, positions=_p(positions), seq_of_token=_p(seq_of_token),
+        kv_len=_p(kv_len), block_table=_p(block_table), bt_stride=block_table.stride(0), bt_rows=_p(table_rows),
+        k_pages=_p(k_pages), v_pages=_p(v_pages), page_size=k_pages.shape[2], num_pages=k_pages.shape[0],
+        h=_p(buf["h"]), qkv=_p(buf["qkv"]), attn_out=_p(buf["attn"]), a_out=_p(buf["a"]), act=_p(buf["act"]),
+        delta_out=_p(delta_out), workspace=_p(ws), workspace_floats=ws.numel(), counters=_p(cnt), n_counters=cnt.numel(),
+        part=_p(part), part_floats=part.numel(), att_counters=_p(att_cnt), n_att_counters=att_cnt.numel(),
+        bars=_p(buf["bars"]), status=_p(status), sm_count=sms, max_kv=max(1, max_kv))
+    _check(library().acv_decode_layer(ctypes.byref(a), _stream()), "decode_layer")
+    return delta_out
 
 
 def linear_bf16(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, static_weights: bool = False) -> torch.Tensor:

@@ -2,6 +2,9 @@
 
 from __future__ import annotations
 
+import torch
+
+from ..kernels import ops
 from .base import CacheView, Runtime
 from .plan import LayerSpec
 from .registry import build, register
@@ -23,6 +26,7 @@ class PreNormBlock:
         self.post_norm = build("norm", spec.norm, hidden_size)
         self.mixer = build("mixer", spec.mixer, hidden_size)
         self.feed_forward = build("feed_forward", spec.feed_forward, hidden_size)
+        self.fuse_decode = True      # let small decode steps run the layer as one kernel where the parts allow it
 
     def tensor_needs(self):
         needs = {}
@@ -50,7 +54,38 @@ class PreNormBlock:
     def flops(self, num_tokens: int) -> float:
         return self.mixer.flops(num_tokens) + self.feed_forward.flops(num_tokens)
 
+    def _fused_decode(self, x, delta, ctx, cache: CacheView | None):
+        """A step of up to 16 one-token requests in bfloat16 runs the whole layer as one persistent kernel, when the
+        parts are of the kinds that kernel knows (each part says so itself: ``decode_layer_spec``) and the sizes fit;
+        None otherwise, and the parts run one by one."""
+        if x.dtype != torch.bfloat16 or cache is None or not cache.writes or ctx.max_q_len != 1:
+            return None
+        T = x.shape[0]
+        if T > ops.DECODE_LAYER_TOKENS or T != ctx.num_seqs:
+            return None
+        specs = [getattr(part, "decode_layer_spec", lambda: None)()
+                 for part in (self.input_norm, self.post_norm, self.mixer, self.feed_forward)]
+        if any(s is None for s in specs):
+            return None
+        n1, n2, m, f = specs
+        if n1["eps"] != n2["eps"] or cache.k_pages is None:
+            return None
+        if not ops.decode_layer_takes(T, x.shape[1], f["intermediate_size"], m["num_heads"], m["num_kv_heads"], m["head_dim"],
+                                      cache.k_pages.shape[2], m["window"]):
+            return None
+        work = ctx.work.get(m["metadata_key"], {})
+        out = torch.empty_like(x)
+        ops.decode_layer(x, delta, out, n1["weight"], n2["weight"], n1["eps"], m["w_qkv"], m["w_o"], f["w_gate_up_pairs"],
+                         f["w_down"], m["q_norm"], m["k_norm"], m["qk_eps"], m["cos_sin"], m["num_heads"], m["num_kv_heads"],
+                         m["head_dim"], m["scale"], ctx.positions, ctx.seq_of_token, ctx.kv_len, ctx.block_tables[cache.group],
+                         ctx.table_rows, cache.k_pages, cache.v_pages, int(work.get("max_dec_kv", 0)))
+        return x, out
+
     def forward(self, x, delta, ctx, cache: CacheView | None):
+        if self.fuse_decode:
+            fused = self._fused_decode(x, delta, ctx, cache)
+            if fused is not None:
+                return fused
         h = self.input_norm.forward(x, delta)
         a = self.mixer.forward(h, ctx, cache)
         h = self.post_norm.forward(x, a)

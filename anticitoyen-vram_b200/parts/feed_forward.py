@@ -51,6 +51,12 @@ class SwiGLU(FeedForward):
             self.gate_up = Linear.stacked([gate, up], [gate_b, up_b])
         self.down = Linear(w(self.prefix + "down_proj.weight"), down_b)
 
+    def decode_layer_spec(self):
+        """What the fused decode-layer kernel needs of this feed-forward: gate and up rows interleaved, no biases."""
+        if not self.fused or self.down.bias is not None:
+            return None
+        return {"intermediate_size": self.intermediate_size, "w_gate_up_pairs": self.gate_up.weight, "w_down": self.down.weight}
+
     def forward(self, h, ctx):
         if self.fused and h.shape[0] and ops.gemm_tc_takes(h, self.gate_up.weight):
             act = torch.empty((h.shape[0], self.intermediate_size), device=h.device, dtype=h.dtype)

@@ -78,6 +78,17 @@ class Attention(Mixer):
             self.q_norm, self.k_norm = f(self.prefix + "q_norm.weight"), f(self.prefix + "k_norm.weight")
         self.position.load({n[len(self.prefix):]: t for n, t in tensors.items() if n.startswith(self.prefix)}, rt)
 
+    def decode_layer_spec(self):
+        """What the fused decode-layer kernel needs of this mixer (it knows rotary positions over the whole head,
+        applied by table, and no biases)."""
+        rotary = self.position.rotary_table()
+        if self.qkv.bias is not None or self.o.bias is not None or rotary is None or rotary.shape[1] != self.head_dim:
+            return None
+        return {"num_heads": self.num_heads, "num_kv_heads": self.num_kv_heads, "head_dim": self.head_dim,
+                "window": self.window, "scale": self.scale, "w_qkv": self.qkv.weight, "w_o": self.o.weight,
+                "q_norm": self.q_norm, "k_norm": self.k_norm, "qk_eps": self.qk_norm_eps or 0.0, "cos_sin": rotary,
+                "metadata_key": self.metadata_key}
+
     # ---- cost of a step
     def weight_bytes(self) -> int:
         norms = sum(t.numel() * 4 for t in (self.q_norm, self.k_norm) if t is not None)

@@ -27,6 +27,10 @@ class RMSNorm(Norm):
     def load(self, tensors, rt: Runtime) -> None:
         self.weight = tensors["weight"].to(device=rt.device, dtype=torch.float32).contiguous()
 
+    def decode_layer_spec(self):
+        """What the fused decode-layer kernel needs of this norm."""
+        return {"weight": self.weight, "eps": self.eps}
+
     def weight_bytes(self) -> int:
         return 0 if self.weight is None else self.weight.numel() * 4
 
