@@ -139,9 +139,10 @@ def time_decode(runner, names: list, steps: int, warmup: int) -> dict:
     torch.cuda.synchronize(dev)
     ms = start.elapsed_time(end) / steps
     launches = ops.LAUNCHES + getattr(runner, "graph_launches", 0) - launches0
-    if ops.gemm_status():
+    code = ops.gemm_status()
+    if code:
         ops.reset_after_failure()
-        raise Refused("a kernel gave up a bounded wait during the timed steps")
+        raise Refused(f"a kernel gave up a bounded wait during the timed steps (status {code})")
     if runner.graphs is not None and runner.graphs.disabled_reason is None and runner.graphs.replays - replays0 != steps:
         raise Refused(f"{steps - (runner.graphs.replays - replays0)} of {steps} timed steps did not replay a captured graph")
     if [runner.manager.lengths[n] - b for n, b in zip(names, before)] != [steps + warmup] * B:
@@ -184,9 +185,10 @@ def time_mixed(runner, names: list, portion: int, prompt_len: int, steps: int, w
     name = f"mixed-prompt-{state['k']}"
     if name in runner.manager.lengths:
         runner.release(name)
-    if ops.gemm_status():
+    code = ops.gemm_status()
+    if code:
         ops.reset_after_failure()
-        raise Refused("a kernel gave up a bounded wait during the timed steps")
+        raise Refused(f"a kernel gave up a bounded wait during the timed steps (status {code})")
     ms = start.elapsed_time(end) / steps
     return {"ms_per_step": ms, "tokens_per_s": (B + portion) * 1000.0 / ms, "decode_tokens_per_s": B * 1000.0 / ms}
 
@@ -207,9 +209,10 @@ def time_prefill(runner, tokens: int, reps: int = 3, warmup: int = 1) -> dict:
         runner.release(name)
         if k >= warmup:
             times.append(start.elapsed_time(end))
-    if ops.gemm_status():
+    code = ops.gemm_status()
+    if code:
         ops.reset_after_failure()
-        raise Refused("a kernel gave up a bounded wait during the timed steps")
+        raise Refused(f"a kernel gave up a bounded wait during the timed steps (status {code})")
     ms = statistics.median(times)
     return {"ms": ms, "tokens": tokens, "tokens_per_s": tokens * 1000.0 / ms, "spread_ms": max(times) - min(times)}
 

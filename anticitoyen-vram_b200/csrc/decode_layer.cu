@@ -82,6 +82,7 @@ struct DlParams {
     int* status;
     unsigned int wait_limit;
     int n_slots;
+    unsigned long long* trace;  // null, or [gridDim.x][8] device-wide nanosecond stamps of each CTA's phase ends
 };
 
 struct DlMaps {
@@ -183,6 +184,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
     uint64_t* bars = (uint64_t*)(aux + DL_BN * 8 + DL_BN * D * 4);
     const uint32_t ring_addr = gt_smem(ring);
     const uint32_t full0 = gt_smem(bars), empty0 = full0 + 8 * NS, tfull0 = empty0 + 8 * NS, tempty0 = tfull0 + 16;
+    const uint32_t att_done = tempty0 + 16;     // this CTA's workers are through with the key tiles of its attention item
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
     __shared__ int last_s;
@@ -193,6 +195,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
         abort_s = 0;
         for (int s = 0; s < NS; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        mbar_init(att_done, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -279,39 +282,41 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             unsigned int spins = 0;
             while (lead_on || trail_on) {
                 bool moved = false;
-                // -- the trailing cursor: dependent loads of units that the leading one has opened
-                if (trail_on && n_trail < n_lead) {
-                    const int dep = dep_of(trail);
-                    if (dep <= passed || dl_passed(p, dep)) {
-                        if (dep > passed) { passed = dep; asm volatile("fence.proxy.async.global;" ::: "memory"); }
-                        if (trail.phase == 1) {
-                            if (holds_new_token(trail)) att_tile(trail, true);
-                        } else {
-                            tma_load_2d(ring_addr + trail.s * DL_SLOT + DL_SLOT_A, &maps.b[dl_gemm_of(trail.phase)],
-                                        full0 + 8 * trail.s, trail.kb * GT_BK, 0);
-                        }
-                        ++n_trail;
-                        trail_on = dl_seq_next(p, att, trail);
-                        moved = true;
-                    }
-                }
-                // -- the leading cursor: a free slot gets its announcement and what does not depend on the step
-                if (lead_on) {
+                // -- the leading cursor: every free slot gets its announcement and what does not depend on the step
+                while (lead_on) {
                     const bool prefilled = (int)n_lead < early;         // its weight tile is already on its way
-                    if (prefilled || mbar_try_wait(empty0 + 8 * lead.s, lead.ph ^ 1)) {
-                        if (lead.phase == 1) {
-                            const uint32_t bytes = att_tile(lead, false);
-                            if (bytes) mbar_expect_tx(full0 + 8 * lead.s, bytes); else mbar_arrive(full0 + 8 * lead.s);
-                            if (!holds_new_token(lead)) att_tile(lead, true);
-                        } else if (!prefilled) {
-                            mbar_expect_tx(full0 + 8 * lead.s, DL_SLOT);
-                            tma_load_2d(ring_addr + lead.s * DL_SLOT, &maps.w[dl_gemm_of(lead.phase)], full0 + 8 * lead.s,
-                                        lead.kb * GT_BK, lead.tile * GT_BM);
-                        }
-                        ++n_lead;
-                        lead_on = dl_seq_next(p, att, lead);
-                        moved = true;
+                    if (!prefilled && !mbar_try_wait(empty0 + 8 * lead.s, lead.ph ^ 1)) break;
+                    if (lead.phase == 1) {
+                        const uint32_t bytes = att_tile(lead, false);
+                        if (bytes) mbar_expect_tx(full0 + 8 * lead.s, bytes); else mbar_arrive(full0 + 8 * lead.s);
+                        if (!holds_new_token(lead)) att_tile(lead, true);
+                    } else if (!prefilled) {
+                        mbar_expect_tx(full0 + 8 * lead.s, DL_SLOT);
+                        tma_load_2d(ring_addr + lead.s * DL_SLOT, &maps.w[dl_gemm_of(lead.phase)], full0 + 8 * lead.s,
+                                    lead.kb * GT_BK, lead.tile * GT_BM);
                     }
+                    ++n_lead;
+                    lead_on = dl_seq_next(p, att, lead);
+                    moved = true;
+                }
+                // -- the trailing cursor: dependent loads of the units that the leading one has opened, as far as the
+                //    grid barriers that they wait for have been passed (one look at a barrier per turn)
+                while (trail_on && n_trail < n_lead) {
+                    const int dep = dep_of(trail);
+                    if (dep > passed) {
+                        if (!dl_passed(p, dep)) break;
+                        passed = dep;
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                    }
+                    if (trail.phase == 1) {
+                        if (holds_new_token(trail)) att_tile(trail, true);
+                    } else {
+                        tma_load_2d(ring_addr + trail.s * DL_SLOT + DL_SLOT_A, &maps.b[dl_gemm_of(trail.phase)],
+                                    full0 + 8 * trail.s, trail.kb * GT_BK, 0);
+                    }
+                    ++n_trail;
+                    trail_on = dl_seq_next(p, att, trail);
+                    moved = true;
                 }
                 if (moved) { spins = 0; continue; }
                 if (++spins > p.wait_limit) { abort_s = 1; atomicExch(p.status, 21); break; }
@@ -327,8 +332,16 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             DlSeq c; c.phase = 0; c.item = 0; c.s = 0; c.ph = 0;
             bool on = dl_seq_enter(p, att, c);
             uint32_t local = 0;
+            bool past_attention = false;
             while (on && !abort_s) {
                 if (c.phase == 1) { on = dl_seq_next(p, att, c); continue; }        // key tiles are the workers'
+                // A wait on a slot tells its rounds apart by one bit.  The slots of the output product's first tiles
+                // held key tiles a round before: this thread may look at them only when the workers are through with
+                // the key tiles, or it would take a key tile that has not landed yet for its own tile of weights.
+                if (c.phase >= 2 && !past_attention) {
+                    if (!mbar_wait(att_done, 0, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 27); break; }
+                    past_attention = true;
+                }
                 const uint32_t buf = local & 1, use = local >> 1;
                 if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 22); break; }
                 tc_fence_after();
@@ -359,10 +372,18 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
         const DlAtt att = att_of();
         const int T = p.T, H = p.H;
         auto sync_workers = [&]() { asm volatile("bar.sync 1, 128;" ::: "memory"); };
+        auto stamp = [&](int i) {
+            if (p.trace && et == 0) {
+                unsigned long long t;
+                asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+                p.trace[(size_t)blockIdx.x * 8 + i] = t;
+            }
+        };
         auto arrive = [&](int which) {              // this CTA's part of a phase is written
             __threadfence();
             sync_workers();
             if (et == 0) atomicAdd(p.bars + which, 1u);
+            stamp(which + 1);
         };
         auto wait_bar = [&](int which, int code) -> bool {      // all workers wait for a grid barrier
             if (et == 0) last_s = dl_wait_bar(p, which, &abort_s, code) ? 1 : 0;
@@ -529,11 +550,16 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             const float scale_log2 = p.scale * DL_LOG2E;
             const int mi = lane >> 3, lr = lane & 7;
             bool ok = true;
-            for (int i = wr; i < att.n_tiles && ok; i += 4) {
+            // Four tiles at a time, one to a warp, and the warps meet after each four: a wait on a slot's barrier tells
+            // the phases apart by one bit, so no warp may come to a slot a whole round of the ring before the warp that
+            // had the slot's tile of the round before (the ring holds more than four slots).
+            for (int i0 = 0; i0 < att.n_tiles; i0 += 4, sync_workers()) {
+                const int i = i0 + wr;
+                if (i >= att.n_tiles || !ok) continue;
                 const int n = unit0 + i;
                 const int s = n % NS;
                 const uint32_t ph = (uint32_t)(n / NS) & 1u;
-                if (!mbar_wait(full0 + 8 * s, ph, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 25); ok = false; break; }
+                if (!mbar_wait(full0 + 8 * s, ph, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 25); ok = false; continue; }
                 const uint32_t kbase = ring_addr + s * DL_SLOT, vbase = kbase + DA * (DL_KEYS * 128);
 #pragma unroll
                 for (int half = 0; half < DL_KEYS / 16; ++half) {
@@ -677,6 +703,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
 
         // ---- the layer, phase by phase
         bool ok = true;
+        stamp(0);
         if ((int)blockIdx.x < T) norm_row(p.delta_in, p.w_norm1);
         arrive(DL_B_NORM1);
         // units of this CTA's q/k/v items: where its key tiles start in the sequence of slots
@@ -692,6 +719,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
             ok = wait_bar(DL_B_QKV, 31);
             if (ok) attention(unit0);
         }
+        if (et == 0) mbar_arrive(att_done);
         arrive(DL_B_ATT);
         if (ok) ok = gemm_items(1);
         arrive(DL_B_O);
@@ -704,6 +732,7 @@ decode_layer_kernel(const __grid_constant__ DlMaps maps, const __grid_constant__
         arrive(DL_B_GU);
         if (ok) gemm_items(3);
         __threadfence();
+        stamp(7);
     }
 
     tc_fence_before();
@@ -730,7 +759,9 @@ static int dl_pick_splits(int tiles, int n_kb, int grid) {
         const int kbps = (n_kb + s - 1) / s;
         const int real = (n_kb + kbps - 1) / kbps;
         const long long rounds = ((long long)tiles * real + grid - 1) / grid;
-        const long long cost = rounds * kbps * 8 + real;            // time first, then fewer partial tiles
+        // a work item's epilogue (partial tile out, arrival, the last one's sum) hides behind the next item's loads
+        // only when the item streams long enough: count an item as at least 8 k-blocks; then fewer partial tiles
+        const long long cost = rounds * (kbps > 8 ? kbps : 8) * 32 + real;
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = real; }
     }
     return best;
@@ -754,6 +785,7 @@ struct DlLayerArgs {
     float* part; long long part_floats; int* att_counters; long long n_att_counters;   // partial results of the attention's splits
     unsigned int* bars; int* status;
     int sm_count; int max_kv;
+    unsigned long long* trace;      // optional: [sm_count][8] time stamps (see DlParams)
 };
 
 // Whether the fused kernel takes a layer of these sizes (the separate kernels take everything else).
@@ -849,6 +881,7 @@ ACV_API int acv_decode_layer(const DlLayerArgs* a, cudaStream_t stream) {
     p.part_acc = a->part; p.part_ml = a->part + (long long)p.n_att_items * n_rep * D; p.att_counters = a->att_counters;
     p.workspace = a->workspace; p.counters = a->counters; p.bars = a->bars; p.status = a->status;
     p.wait_limit = GT_WAIT_LIMIT;
+    p.trace = a->trace;
     const long long pool_rows = (long long)a->num_pages * NKV * a->page_size;
     if (pool_rows > 0x7fffffffLL || ((uintptr_t)a->k_pages & 15) || ((uintptr_t)a->v_pages & 15)) return ACV_ERR_SIZE;
     int rc = make_map(&maps.k, a->k_pages, pool_rows, D, D, p.box_keys);

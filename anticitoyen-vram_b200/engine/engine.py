@@ -90,13 +90,15 @@ class Engine:
                  page_size: int = 64, num_pages: int | None = None, token_budget: int = 2048,
                  random_weights: bool = False, seed: int = 0, device: str = "cuda:0",
                  enable_cuda_graphs: bool = True, run_ahead: bool = True, enable_prefix_cache: bool = True,
-                 tokenizer=None) -> None:
+                 tokenizer=None, fuse_decode_layers: bool = False) -> None:
         """``model``: a folder with config.json and model.safetensors, or (with
         ``random_weights``) a typed configuration or a folder whose config.json alone is read.
         ``tokenizer``: anything with ``decode(ids) -> str``; with one, outputs carry the text that their tokens
         add (``text_delta``) and ``SamplingParams.stop`` strings end a request.
         ``enable_prefix_cache`` (the reference's name and default, acvram/engine/runner.py:689-694): the full
-        pages of a finished request stay known, and a later request that begins the same way takes them over."""
+        pages of a finished request stay known, and a later request that begins the same way takes them over.
+        ``fuse_decode_layers``: steps of up to 16 decoding requests run each layer as one persistent kernel instead
+        of seven launches (slower on a B200 at the sizes measured; kept as a choice)."""
         from ..config import load_config
         from ..models import build_from_folder, build_random
 
@@ -112,6 +114,9 @@ class Engine:
         else:
             self.config, self.model = build_from_folder(model, run_dtype, device)
         plan = self.model.plan
+        for block in getattr(self.model, "blocks", ()):
+            if hasattr(block, "fuse_decode"):
+                block.fuse_decode = bool(fuse_decode_layers)
         self.max_model_len = min(max_model_len, plan.max_positions)
         self.page_size = page_size
         if num_pages is None:

@@ -116,7 +116,7 @@ class DecodeLayerArgs(ctypes.Structure):
         ("workspace", _P), ("workspace_floats", _LL), ("counters", _P), ("n_counters", _LL),
         ("part", _P), ("part_floats", _LL), ("att_counters", _P), ("n_att_counters", _LL),
         ("bars", _P), ("status", _P),
-        ("sm_count", _I), ("max_kv", _I),
+        ("sm_count", _I), ("max_kv", _I), ("trace", _P),
     ]
 
 
@@ -711,12 +711,15 @@ def decode_layer(x: torch.Tensor, delta: torch.Tensor | None, delta_out: torch.T
                  w_down: torch.Tensor, q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, qk_eps: float,
                  cos_sin: torch.Tensor | None, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  positions: torch.Tensor, seq_of_token: torch.Tensor, kv_len: torch.Tensor, block_table: torch.Tensor,
-                 table_rows: torch.Tensor | None, k_pages: torch.Tensor, v_pages: torch.Tensor, max_kv: int) -> torch.Tensor:
+                 table_rows: torch.Tensor | None, k_pages: torch.Tensor, v_pages: torch.Tensor, max_kv: int,
+                 trace: torch.Tensor | None = None) -> torch.Tensor:
     """A whole pre-norm decoder layer for a step of up to 16 one-token requests in one persistent kernel
     (csrc/decode_layer.cu): x += delta; a = attention(norm1(x)); x += a; delta_out = swiglu_mlp(norm2(x)).
     ``x`` [T, H] is updated in place, ``delta_out`` [T, H] receives what the next layer adds; the keys and values of
     the step's tokens go to their pages.  ``w_gate_up_pairs``: rows (gate_i, up_i) interleaved, as the fused SwiGLU
-    product takes them.  ``decode_layer_takes`` says for which sizes."""
+    product takes them.  ``decode_layer_takes`` says for which sizes.  ``trace`` (int64 [SMs, 8], optional): each CTA
+    leaves the device-wide nanosecond time at which it began and at which it finished each phase (norm, q/k/v,
+    attention, output product, norm, gate/up, down)."""
     _need_cuda(x, delta_out, w_qkv, k_pages)
     T, H = x.shape
     I = w_down.shape[1]
@@ -737,7 +740,7 @@ def decode_layer(x: torch.Tensor, delta: torch.Tensor | None, delta_out: torch.T
         h=_p(buf["h"]), qkv=_p(buf["qkv"]), attn_out=_p(buf["attn"]), a_out=_p(buf["a"]), act=_p(buf["act"]),
         delta_out=_p(delta_out), workspace=_p(ws), workspace_floats=ws.numel(), counters=_p(cnt), n_counters=cnt.numel(),
         part=_p(part), part_floats=part.numel(), att_counters=_p(att_cnt), n_att_counters=att_cnt.numel(),
-        bars=_p(buf["bars"]), status=_p(status), sm_count=sms, max_kv=max(1, max_kv))
+        bars=_p(buf["bars"]), status=_p(status), sm_count=sms, max_kv=max(1, max_kv), trace=_p(trace))
     _check(library().acv_decode_layer(ctypes.byref(a), _stream()), "decode_layer")
     return delta_out
 

@@ -26,7 +26,10 @@ class PreNormBlock:
         self.post_norm = build("norm", spec.norm, hidden_size)
         self.mixer = build("mixer", spec.mixer, hidden_size)
         self.feed_forward = build("feed_forward", spec.feed_forward, hidden_size)
-        self.fuse_decode = True      # let small decode steps run the layer as one kernel where the parts allow it
+        # Small decode steps can run the whole layer as one persistent kernel (csrc/decode_layer.cu).  Off unless asked
+        # for: measured on a B200 at the layer sizes of Qwen3-8B it is slower than the seven separate launches (a step's
+        # time goes to the chain of dependent phases, which one kernel does not shorten), see profiles/.
+        self.fuse_decode = False
 
     def tensor_needs(self):
         needs = {}
