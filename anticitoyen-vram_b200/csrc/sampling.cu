@@ -363,11 +363,236 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const float* __re
     }
 }
 
+// ----------------------------------------------------------------------------- sample, a cluster to a row
+// A wide row (a vocabulary of 150 thousand) read 70 times by one block is bound by the latency of its loads: a
+// second per thousand steps of eight rows.  Here the CTAs of one thread-block cluster share a row: each keeps its
+// slice of the scaled logits in shared memory, so the row is read from memory once and the bisections' passes run
+// on shared memory; what a pass counts is added up over the cluster through the CTAs' shared memory (every CTA
+// writes its part into every CTA's table, one cluster barrier, every CTA adds the parts in rank order, so all take
+// the same decision).  The arithmetic is sample_kernel's; sums are formed slice by slice.
+#define SMPC_CTAS 8
+#define SMPC_THREADS 1024
+
+struct ClusterSum {
+    float* parts;          // [2][SMPC_CTAS] in this CTA's shared memory
+    float* warps;          // [32]
+    int turn;
+    uint32_t rank;
+};
+
+// every thread gets the sum over the cluster of `v` (a float; counts up to 2^24 are exact)
+__device__ __forceinline__ float cluster_all_sum(ClusterSum& c, float v) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    if (lane == 0) c.warps[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < (int)(blockDim.x >> 5) ? c.warps[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane < SMPC_CTAS)
+            cluster_store_f32(cluster_map((uint32_t)__cvta_generic_to_shared(c.parts + c.turn * SMPC_CTAS + c.rank), lane), t);
+    }
+    cluster_sync_all();
+    float total = 0.f;
+#pragma unroll
+    for (int r = 0; r < SMPC_CTAS; ++r) total += c.parts[c.turn * SMPC_CTAS + r];
+    c.turn ^= 1;
+    return total;
+}
+__device__ __forceinline__ float cluster_all_max(ClusterSum& c, float v) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    if (lane == 0) c.warps[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < (int)(blockDim.x >> 5) ? c.warps[lane] : -INFINITY;
+        t = warp_max(t);
+        if (lane < SMPC_CTAS)
+            cluster_store_f32(cluster_map((uint32_t)__cvta_generic_to_shared(c.parts + c.turn * SMPC_CTAS + c.rank), lane), t);
+    }
+    cluster_sync_all();
+    float total = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < SMPC_CTAS; ++r) total = fmaxf(total, c.parts[c.turn * SMPC_CTAS + r]);
+    c.turn ^= 1;
+    return total;
+}
+
+__global__ void __launch_bounds__(SMPC_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int ld, int V, int slice, const float* __restrict__ temperature,
+                      const int* __restrict__ top_k, const float* __restrict__ top_p, const float* __restrict__ min_p,
+                      const unsigned long long* __restrict__ seed, const unsigned long long* __restrict__ counter,
+                      int* __restrict__ out_token, float* __restrict__ out_logprob) {
+    extern __shared__ float sl[];               // this CTA's slice of the scaled logits
+    __shared__ float parts[2 * SMPC_CTAS];
+    __shared__ float warps[32];
+    __shared__ float scan[SMPC_THREADS];
+    __shared__ float bestv[2 * SMPC_CTAS];
+    __shared__ int owner_s;
+    __shared__ float before_s, target_s;
+    ClusterSum cs;
+    cs.parts = parts; cs.warps = warps; cs.turn = 0; cs.rank = cluster_ctarank();
+    const int r = blockIdx.x / SMPC_CTAS;
+    const float* row = logits + (size_t)r * ld;
+    const int lo = (int)cs.rank * slice, hi = min(V, lo + slice), n = max(0, hi - lo);
+    const float temp = temperature[r];
+    const bool greedy = temp <= 0.f;
+    const float inv_t = greedy ? 1.f : 1.f / fmaxf(temp, 1e-5f);
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const float v = row[lo + i] * inv_t;
+        sl[i] = v;
+        mx = fmaxf(mx, v);
+    }
+    mx = cluster_all_max(cs, mx);           // (its barriers also make the slice visible to the CTA's threads)
+
+    if (greedy) {
+        // the lowest index that holds the maximum: the smallest of the CTAs' candidates (slices are in index order)
+        int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < n; i += blockDim.x)
+            if (sl[i] == mx) bi = min(bi, lo + i);
+        const float first = -cluster_all_max(cs, bi == 0x7fffffff ? -INFINITY : -(float)bi);     // indices < 2^24: exact
+        const int pick = first == INFINITY ? 0 : (int)first;
+        float z = 0.f;
+        if (out_logprob) {
+            float local = 0.f;
+            for (int i = threadIdx.x; i < n; i += blockDim.x) local += expf(sl[i] - mx);
+            z = cluster_all_sum(cs, local);
+        }
+        if (cs.rank == 0 && threadIdx.x == 0) {
+            out_token[r] = pick;
+            if (out_logprob) out_logprob[r] = -logf(z);
+        }
+        return;
+    }
+
+    uint32_t cut = 0;  // keys >= cut are kept
+    const int k = top_k[r];
+    if (k > 0 && k < V) {
+        uint32_t prefix = 0;
+        for (int b = 31; b >= 0; --b) {
+            const uint32_t cand = prefix | (1u << b);
+            int cnt = 0;
+            for (int i = threadIdx.x; i < n; i += blockDim.x) cnt += order_key(sl[i]) >= cand;
+            if (cluster_all_sum(cs, (float)cnt) >= (float)k) prefix = cand;
+        }
+        cut = prefix;
+    }
+    const float mp = min_p[r];
+    const bool use_minp = mp > 0.f;
+    const float tp = top_p[r];
+    if (tp > 0.f && tp < 1.f) {
+        float z = 0.f;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) {
+            const float s = sl[i];
+            const float e = expf(s - mx);
+            if (order_key(s) >= cut && !(use_minp && e < mp)) z += e;
+        }
+        z = cluster_all_sum(cs, z);
+        const float limit = tp * z;
+        uint32_t prefix = 0;  // the largest key value t with mass(key > t) > limit
+        for (int b = 31; b >= 0; --b) {
+            const uint32_t cand = prefix | (1u << b);
+            float mass = 0.f;
+            for (int i = threadIdx.x; i < n; i += blockDim.x) {
+                const float s = sl[i];
+                const uint32_t key = order_key(s);
+                const float e = expf(s - mx);
+                if (key > cand && key >= cut && !(use_minp && e < mp)) mass += e;
+            }
+            if (cluster_all_sum(cs, mass) > limit) prefix = cand;
+        }
+        const uint32_t cut_p = prefix + 1u;
+        cut = cut_p > cut ? cut_p : cut;
+    }
+
+    // inverse CDF in index order: CTA by CTA, inside a CTA each thread owns a contiguous range of its slice
+    const int chunk = (n + (int)blockDim.x - 1) / (int)blockDim.x;
+    const int c_lo = min(n, (int)threadIdx.x * chunk), c_hi = min(n, c_lo + chunk);
+    float local = 0.f;
+    for (int i = c_lo; i < c_hi; ++i) {
+        const float s = sl[i];
+        const float e = expf(s - mx);
+        if (order_key(s) >= cut && !(use_minp && e < mp)) local += e;
+    }
+    scan[threadIdx.x] = local;
+    // every CTA learns every CTA's total (the same exchange as a sum's, read part by part)
+    {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        float v = warp_sum(local);
+        if (lane == 0) warps[warp] = v;
+        __syncthreads();
+        if (warp == 0) {
+            float tot = lane < (int)(blockDim.x >> 5) ? warps[lane] : 0.f;
+            tot = warp_sum(tot);
+            if (lane < SMPC_CTAS)
+                cluster_store_f32(cluster_map((uint32_t)__cvta_generic_to_shared(bestv + cs.rank), lane), tot);
+        }
+        cluster_sync_all();
+    }
+    float run = 0.f;
+#pragma unroll
+    for (int c = 0; c < SMPC_CTAS; ++c) run += bestv[c];
+    const float u = philox_uniform(seed[r], counter[r]);
+    const float target = u * run;
+    // the CTA in which the target falls (the last CTA with anything kept, if rounding leaves the target beyond all)
+    int owner_cta = -1, last_cta = 0;
+    float acc = 0.f, before_cta = 0.f;
+#pragma unroll
+    for (int c = 0; c < SMPC_CTAS; ++c) {
+        if (bestv[c] > 0.f) last_cta = c;
+        if (owner_cta < 0 && bestv[c] > 0.f && acc + bestv[c] >= target) { owner_cta = c; before_cta = acc; }
+        if (owner_cta < 0) acc += bestv[c];
+    }
+    if (owner_cta < 0) { owner_cta = last_cta; before_cta = acc - bestv[last_cta]; }
+    if ((int)cs.rank != owner_cta) return;
+    if (threadIdx.x == 0) {
+        float a2 = before_cta;
+        int owner = -1, last_nonempty = 0;
+        for (int t = 0; t < (int)blockDim.x; ++t) {
+            if (scan[t] > 0.f) last_nonempty = t;
+            if (owner < 0 && scan[t] > 0.f && a2 + scan[t] >= target) { owner = t; before_s = a2; }
+            if (owner < 0) a2 += scan[t];
+        }
+        if (owner < 0) { owner = last_nonempty; before_s = a2 - scan[last_nonempty]; }
+        owner_s = owner;
+        target_s = target;
+    }
+    __syncthreads();
+    if ((int)threadIdx.x == owner_s) {
+        float a3 = before_s;
+        int pick = -1, last_kept = -1;
+        for (int i = c_lo; i < c_hi; ++i) {
+            const float s = sl[i];
+            const float e = expf(s - mx);
+            if (order_key(s) >= cut && !(use_minp && e < mp)) {
+                last_kept = i;
+                a3 += e;
+                if (a3 >= target_s) { pick = i; break; }
+            }
+        }
+        if (pick < 0) pick = last_kept;
+        out_token[r] = lo + pick;
+        if (out_logprob) out_logprob[r] = (sl[pick] - mx) - logf(run);
+    }
+}
+
 ACV_API int acv_sample(const float* logits, int ld, int rows, int V, const float* temperature, const int* top_k,
                        const float* top_p, const float* min_p, const unsigned long long* seed,
                        const unsigned long long* counter, int* out_token, float* out_logprob, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (V <= 0) return ACV_ERR_SIZE;
+    // wide rows: a cluster of CTAs to a row, the row's slices in their shared memory
+    const int slice = ((V + SMPC_CTAS - 1) / SMPC_CTAS + 3) & ~3;
+    const int smem = slice * (int)sizeof(float);
+    if (V >= 16384 && V < (1 << 24) && smem <= 200 * 1024) {
+        static AcvSmemConfig smem_config;
+        if (int rc = acv_ensure_smem(smem_config, sample_cluster_kernel, smem)) return rc;
+        acv_launch_cluster(0, dim3(SMPC_CTAS, 1, 1), sample_cluster_kernel, dim3((unsigned)rows * SMPC_CTAS), dim3(SMPC_THREADS),
+                           (size_t)smem, stream, logits, ld, V, slice, temperature, top_k, top_p, min_p, seed, counter,
+                           out_token, out_logprob);
+        return acv_launch_status();
+    }
     sample_kernel<<<rows, SMP_THREADS, 0, stream>>>(logits, ld, V, temperature, top_k, top_p, min_p, seed, counter,
                                                     out_token, out_logprob);
     return acv_launch_status();

@@ -681,6 +681,7 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
 
 # ----------------------------------------------------------------------------- one decoder layer of a decode step
 DECODE_LAYER_TOKENS = 16     # DL_BN of decode_layer.cu
+DECODE_LAYER_TRACE: torch.Tensor | None = None   # int64 [SMs, 8] on the device: every fused layer leaves its phase stamps there
 _layer_scratch: dict = {}
 
 
@@ -740,7 +741,8 @@ def decode_layer(x: torch.Tensor, delta: torch.Tensor | None, delta_out: torch.T
         h=_p(buf["h"]), qkv=_p(buf["qkv"]), attn_out=_p(buf["attn"]), a_out=_p(buf["a"]), act=_p(buf["act"]),
         delta_out=_p(delta_out), workspace=_p(ws), workspace_floats=ws.numel(), counters=_p(cnt), n_counters=cnt.numel(),
         part=_p(part), part_floats=part.numel(), att_counters=_p(att_cnt), n_att_counters=att_cnt.numel(),
-        bars=_p(buf["bars"]), status=_p(status), sm_count=sms, max_kv=max(1, max_kv), trace=_p(trace))
+        bars=_p(buf["bars"]), status=_p(status), sm_count=sms, max_kv=max(1, max_kv),
+        trace=_p(trace if trace is not None else DECODE_LAYER_TRACE))
     _check(library().acv_decode_layer(ctypes.byref(a), _stream()), "decode_layer")
     return delta_out
 

@@ -81,6 +81,59 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
         return {"kernel": kernel.__name__, "batch": batch, "q_len": q_len, "context": context, "us": us, "tflops": flops / us / 1e6}
 
 
+def sample_case(rows: int, vocab: int, reps: int) -> dict:
+    """Temperature 0.7 and top-p 0.9 over rows of a real vocabulary (a cluster of CTAs shares a row)."""
+    logits = [torch.randn(rows, vocab, device="cuda") * 3.0 for _ in range(4)]
+    f = lambda v: torch.full((rows,), v, device="cuda", dtype=torch.float32)
+    temp, top_p, min_p = f(0.7), f(0.9), f(0.0)
+    top_k = torch.zeros(rows, device="cuda", dtype=torch.int32)
+    seed = torch.arange(rows, device="cuda", dtype=torch.int64)
+    out = torch.empty(rows, device="cuda", dtype=torch.int32)
+    counter = torch.zeros(rows, device="cuda", dtype=torch.int64)
+    us = _time(lambda i: ops.sample(logits[i % 4], temp, top_k, top_p, min_p, seed, counter, out), reps)
+    print(f"sample rows={rows} vocab={vocab} temperature 0.7 top-p 0.9: {us:.1f} us")
+    return {"kernel": "sample", "rows": rows, "vocab": vocab, "us": us}
+
+
+def decode_layer_case(batch: int, context: int, reps: int, fused: bool) -> dict:
+    """One layer of the Qwen3-8B sizes in a decode step of ``batch`` requests: the persistent kernel, or the seven
+    separate launches, on the same inputs (weights rotate over three layers so that none is found in L2)."""
+    from .config import Qwen3Config
+    from .engine.batch import StepEntry
+    from .engine.runner import ModelRunner
+    from .models import build_random
+    cfg = Qwen3Config(vocab_size=2048, hidden_size=4096, intermediate_size=12288, num_hidden_layers=3, num_attention_heads=32,
+                      num_key_value_heads=8, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=16384, tie_word_embeddings=False)
+    model = build_random(cfg, 0, torch.bfloat16, "cuda:0")
+    for b in model.blocks:
+        b.fuse_decode = fused
+    page = 16
+    runner = ModelRunner(model, page, batch * (context + 256) // page + 8, batch, max_len=context + 256)
+    runner.enable_graphs()          # as serving runs decode steps: replayed from a captured graph
+    names = [f"r{i}" for i in range(batch)]
+    ids = [(7 * i + 3) % 2000 + 5 for i in range(context)]
+    for n in names:
+        for pos in range(0, context, 2048):
+            runner.step([StepEntry(n, ids[pos:pos + 2048], ())])
+    entries = [StepEntry(n, [11], (0,)) for n in names]
+    us = _time(lambda i: runner.step(entries), reps) / 3.0
+    runner.check_status()
+    if fused:       # when each CTA finished each phase of the last layer that ran (device-wide nanosecond timer)
+        ops.DECODE_LAYER_TRACE = torch.zeros(ops.sm_count(), 8, dtype=torch.int64, device="cuda")
+        runner.graphs = None        # a captured graph holds the arguments it was captured with: this one step runs eagerly
+        runner.step(entries)
+        torch.cuda.synchronize()
+        t = ops.DECODE_LAYER_TRACE.cpu().numpy()
+        ops.DECODE_LAYER_TRACE = None
+        rel = (t - t[:, 0].min()) / 1e3
+        names_ph = ["begin", "norm", "q/k/v", "attention", "output", "norm", "gate/up", "down"]
+        print("phase ends, us after the first CTA began (earliest..latest CTA): " +
+              "  ".join(f"{n} {rel[:, i].min():.1f}..{rel[:, i].max():.1f}" for i, n in enumerate(names_ph)))
+    print(f"decode layer ({'one persistent kernel' if fused else 'separate launches'}) batch={batch} context={context}: "
+          f"{us:.1f} us a layer (the step's embedding, final norm and head included, divided by 3 layers)")
+    return {"kernel": "decode_layer" if fused else "separate", "batch": batch, "context": context, "us_per_layer": us}
+
+
 CASES = {
     "gemm_decode": lambda r: gemm_case(8, 6144, 4096, r),
     "gemm_decode_mlp": lambda r: gemm_case(8, 24576, 4096, r),
@@ -91,6 +144,9 @@ CASES = {
     "attention_prefill": lambda r: attention_case(1, 2048, 2048, r),
     "attention_prefill_8k": lambda r: attention_case(1, 2048, 8192, r),
     "attention_prefill_mma_sync": lambda r: attention_case(1, 2048, 2048, r, legacy=True),
+    "sample": lambda r: sample_case(8, 151936, r),
+    "decode_layer_fused": lambda r: decode_layer_case(8, 2048, r, True),
+    "decode_layer_separate": lambda r: decode_layer_case(8, 2048, r, False),
 }
 
 

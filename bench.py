@@ -156,18 +156,6 @@ def run_ours(args) -> int:
                           "steps": K, "warmup": W}))
         return 3
 
-    # one prompt of 2048 tokens (a different one each time): 3 untimed, then the median of 5
-    pre = B.time_prefill(runner, 2048, reps=5, warmup=3)
-    pre_frac = B.prefill_flops(model, 2048) / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12)
-
-    if not args.skip_points:
-        for b in (1, 64):
-            def f(b=b):
-                r = decode_point(runner, b, args.context, K, W)
-                points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
-                points[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / pk["hbm_gbs"], 4)
-            point(f"decode_b{b}", f)
-
     # end to end through the public entry point: host ids in, host ids out, every step
     def end_to_end(sp_of) -> tuple[float, int]:
         for i in range(args.batch):
@@ -204,6 +192,18 @@ def run_ours(args) -> int:
         e2e = {"value": round(e2e_rate, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * args.batch + 4}
     except B.Refused as exc:
         e2e = {"value": None, "unit": "tokens/s", "refused": str(exc)}
+    # one prompt of 2048 tokens (a different one each time): 3 untimed, then the median of 5
+    pre = B.time_prefill(runner, 2048, reps=5, warmup=3)
+    pre_frac = B.prefill_flops(model, 2048) / (pre["ms"] * 1e-3) / (pk["bf16_tflops"] * 1e12)
+
+    if not args.skip_points:
+        for b in (1, 64):
+            def f(b=b):
+                r = decode_point(runner, b, args.context, K, W)
+                points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+                points[f"decode_b{b}_hbm_frac"] = round(r["gbs"] / pk["hbm_gbs"], 4)
+            point(f"decode_b{b}", f)
+
     if not args.skip_points:
         def sampled():
             rate, _ = end_to_end(lambda i: SamplingParams(temperature=0.7, top_p=0.9, max_tokens=n_out, ignore_eos=True, seed=i))
