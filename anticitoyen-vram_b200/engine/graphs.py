@@ -90,7 +90,10 @@ class DecodeGraphs:
         ctx = r.builder.build_decode(entries, starts, padded, width * r.manager.page_size, dev, first=True)
         if device_tokens is not None:
             ctx.tokens[:len(entries)].copy_(device_tokens)
-        r.model.forward(ctx, r.storage)             # eager once: scratch buffers reach their size
+        # This step itself runs eagerly (scratch buffers reach their size on the way) and its logits are the step's
+        # answer; the capture below records the same launches without running them.  Replaying the new graph for this
+        # step as well would run the step twice, which a mixer that adds to a state of its own must not see.
+        eager_logits = r.model.forward(ctx, r.storage)
         torch.cuda.synchronize(r.rt.device)
         graph = torch.cuda.CUDAGraph()
         before = ops.LAUNCHES
@@ -108,7 +111,7 @@ class DecodeGraphs:
             if gc_was_on:
                 gc.enable()
         kernels = ops.LAUNCHES - before
-        graph.replay()
+        logits.copy_(eager_logits)
         slot = {"graph": graph, "dev": dev, "ctx": ctx, "logits": logits, "kernels": kernels}
         self.graphs[key] = slot
         return slot
