@@ -144,7 +144,8 @@ template <int BN>
 struct GemmShape {
     static constexpr int STAGE_BYTES = (GT_BM + BN) * GT_BK * 2;
     static constexpr int MAX_STAGES = (200 * 1024 / STAGE_BYTES) > 8 ? 8 : (200 * 1024 / STAGE_BYTES);
-    static constexpr int TMEM_COLS = (2 * BN < 32) ? 32 : 2 * BN;     // two accumulator buffers; a power of two
+    // two accumulator buffers side by side; tensor memory is given out in powers of two of columns
+    static constexpr int TMEM_COLS = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
     static constexpr int PART_BYTES = BN * GT_BM * 4;                 // one CTA's partial tile in float
     static constexpr int smem_bytes(int stages, int cluster_parts, int aux_bytes = 0) {
         return stages * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/ + cluster_parts * PART_BYTES + aux_bytes;
@@ -322,7 +323,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             const int row_a = ta * GT_BM + wq * 32 + lane;          // row of the A operand this thread holds
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(wq * 32) << 16);
             if (p.splits == 1 && p.qkv && !p.swap) {
-                if constexpr (BN >= 128) {
+                if constexpr (BN == 128 || BN == 256) {
                     if (p.head_dim == 128) gt_store_qkv_rows<BN, 128>(p, taddr, row_a, tb);
                     else gt_store_qkv_rows<BN, 64>(p, taddr, row_a, tb);
                 } else if constexpr (BN == 64) {
@@ -508,7 +509,7 @@ ACV_API void acv_gemm_tc_test_fault(int wait_limit, int skip_kb) {
 }
 
 // x [M,K] (row stride ldx), w [N,K] (row stride ldw), C [M,N] (row stride ldc) bf16 or float.
-// bn: rows of the B operand per tile (16, 32, 64, 128 or 256); swap: the weight is the A operand.
+// bn: rows of the B operand per tile (16, 32, 64, 128, 160, 192, 224 or 256); swap: the weight is the A operand.
 // splits > 1 needs workspace of tiles*splits*bn*128 floats and `tiles` zeroed counters.
 // status: one int, 0 unless a bounded wait inside the kernel ran out.
 static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int ldw, void* C, int ldc, int M, int N, int K,
@@ -547,6 +548,12 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
         case 32: return launch_gemm<32>(ma, mb, p, sm_count, stages, stream);
         case 64: return launch_gemm<64>(ma, mb, p, sm_count, stages, stream);
         case 128: return launch_gemm<128>(ma, mb, p, sm_count, stages, stream);
+        // widths between 128 and 256 exist for the tokens-on-rows form: with them the number of tiles can be made to
+        // fill whole rounds of the SMs (2048 x 4096 in tiles of 128 x 160 is three full rounds of 148, in tiles of
+        // 128 x 256 two rounds of which the second is three quarters empty)
+        case 160: return launch_gemm<160>(ma, mb, p, sm_count, stages, stream);
+        case 192: return launch_gemm<192>(ma, mb, p, sm_count, stages, stream);
+        case 224: return launch_gemm<224>(ma, mb, p, sm_count, stages, stream);
         case 256: return launch_gemm<256>(ma, mb, p, sm_count, stages, stream);
         default: return ACV_ERR_SIZE;
     }

@@ -341,13 +341,23 @@ GEMM_FEW_TOKENS_RULES = (
 )
 
 
-def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None) -> tuple[int, int, int, int]:
+# Widths of a tile of the tokens-on-rows form, and what a tile costs beside its width, in columns' worth of time.
+# Measured on a B200 (2048 x 4096 x 4096: 61 us in tiles of 256 columns, two rounds of the SMs of which the second is
+# three quarters empty; 72 us in tiles of 160, three full rounds): a k-block of a tile costs about as much for the 128
+# token rows it loads as for 120 of its columns, so a narrower tile pays only where it saves a whole round (1056 x 5120:
+# 69 us at 256, 63 us at 160).  The width is chosen so that rounds x (width + overhead) comes out least.
+GEMM_TILE_WIDTHS = (256, 224, 192, 160, 128)
+GEMM_TILE_OVERHEAD = 120
+
+
+def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None, bn_multiple: int = 16) -> tuple[int, int, int, int]:
     """(swap, bn, splits, stages) for x[M,K] @ w[N,K]^T on a device of ``sms`` multiprocessors.
 
     Up to 128 tokens the weight rows fill the tensor core's M = 128 and the tokens are the narrow
-    side (weights stream once whatever the batch); above, tokens are the M side with 256 features
-    per tile.  Splits of K are chosen so that the work items fill whole waves of the SMs
-    (``GEMM_FEW_TOKENS_RULES``)."""
+    side (weights stream once whatever the batch); splits of K are chosen so that the work items fill
+    whole waves of the SMs (``GEMM_FEW_TOKENS_RULES``).  Above, tokens are the M side and a tile is 128
+    tokens by 128..256 features: the width that needs the least rounds x width (``GEMM_TILE_WIDTHS``;
+    ``bn_multiple``: widths that are multiples of this only, for an epilogue that wants whole heads)."""
     n_kb = -(-K // 64)
     if M <= 128:
         sms = sms or sm_count()
@@ -358,8 +368,18 @@ def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None) -> tuple[int, i
             if t0 <= per_sm < t1 and k0 <= n_kb < k1 and b0 <= bn <= b1:
                 return 1, bn, splits, stages
         return 1, bn, 1, 8
-    bn = 256 if N >= 256 else 128 if N > 64 else 64
-    return 0, bn, 1, 8
+    if N < 256:
+        return 0, (128 if N > 64 else 64), 1, 8
+    sms = sms or sm_count()
+    best, best_cost = 256, None
+    for bn in GEMM_TILE_WIDTHS:
+        if bn % bn_multiple:
+            continue
+        tiles = -(-M // 128) * -(-N // bn)
+        cost = -(-tiles // sms) * (bn + GEMM_TILE_OVERHEAD)
+        if best_cost is None or cost < 0.97 * best_cost:       # a narrower tile has to win clearly
+            best, best_cost = bn, cost
+    return 0, best, 1, 8
 
 
 def gemm_tc(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, plan: tuple | None = None,
@@ -405,7 +425,7 @@ def gemm_tc_qkv_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, cos_sin: 
         return False
     M, K = x.shape
     N = w.shape[0]
-    swap, bn, splits = gemm_tc_plan(M, N, K)[:3]
+    swap, bn, splits = gemm_tc_plan(M, N, K, bn_multiple=head_dim if M > 128 else 16)[:3]
     if not swap:            # tokens on M: a thread of the epilogue holds whole heads of one token
         return splits == 1 and bn >= head_dim and bn % head_dim == 0
     tiles = -(-N // 128) * -(-M // bn)
@@ -422,7 +442,7 @@ def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_heads: 
     _need_cuda(x, w, out, k_pages, v_pages)
     M, K = x.shape
     N = w.shape[0]
-    swap, bn, splits, stages = gemm_tc_plan(M, N, K)
+    swap, bn, splits, stages = gemm_tc_plan(M, N, K, bn_multiple=head_dim if M > 128 else 16)
     cluster = 1 if swap and 1 < splits <= 8 else 0
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)

@@ -400,7 +400,7 @@ def test_gemm_tc_at_the_real_vocabulary(ops, M, K):
 
 
 @pytest.mark.parametrize("plan", [(1, 16, 1), (1, 16, 4), (1, 32, 3), (1, 64, 2), (1, 128, 5), (0, 64, 1), (0, 128, 2),
-                                  (0, 256, 1), (0, 256, 3)])
+                                  (0, 256, 1), (0, 256, 3), (0, 160, 1), (0, 192, 1), (0, 224, 1), (0, 160, 2)])
 def test_gemm_tc_every_tile_shape_and_split(ops, plan):
     M, N, K = (50 if plan[0] else 300), 700, 1160
     if plan[0] and M > plan[1]:
