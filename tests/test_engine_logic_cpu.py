@@ -183,3 +183,24 @@ def test_requests_that_take_pages_over_get_the_plain_logits(tiny_folders, plain_
     for req, p in zip(reqs, prompts):
         assert req.output == plain_qwen3.greedy_generate(cfg, t, p, 7)
     assert s.counters["reused_tokens"] >= 32 + 16 + 32 and r.manager.free_pages() == [14]
+
+
+def test_step_cost_follows_the_plan(tiny_folders, plain_models):
+    """What a step reads and computes, as the parts report it, against the sums written out for this architecture."""
+    cfg, _ = plain_models["B"]
+    model = build(tiny_folders["B"])
+    L, H, I, V = cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    NH, NKV, D = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    matrices = L * (H * (NH + 2 * NKV) * D + NH * D * H + 3 * H * I) + V * H
+    norms = L * (2 * H + 2 * D) + H
+    q_lens, kv_lens = [1, 1, 5], [30, 7, 12]
+    cost = model.step_cost(q_lens, kv_lens, logit_rows=3)
+    assert cost["weight_bytes"] == 4 * (matrices + norms)              # a float32 model; norm weights are float32 too
+    assert cost["cache_bytes"] == L * 2 * sum(kv_lens) * NKV * D * 4
+    seen = 30 + 7 + sum(range(8, 13))                                   # keys that each query sees
+    want = 2.0 * 7 * (matrices - V * H) + 2.0 * 3 * V * H + L * 4.0 * NH * D * seen
+    assert abs(cost["flops"] - want) < 1e-6 * want
+    # a layer that runs twice is read twice
+    twice = build(tiny_folders["B"], lambda p: dataclasses.replace(
+        p, schedule=p.schedule + (ScheduleEntry(0, p.num_cache_slots, True),)))
+    assert twice.step_cost([1], [5], 1)["weight_bytes"] > model.step_cost([1], [5], 1)["weight_bytes"]

@@ -378,3 +378,26 @@ def test_text_deltas_and_stop_strings_with_a_tokenizer(tiny_folders, plain_model
     assert [x for o in outs[a] for x in o.token_ids] == want[0][:j + 1], "the token that completed the string is the last"
     assert eng.runner.manager.free_pages() == [64]
     eng.runner.manager.check()
+
+
+def test_generation_with_the_layers_as_single_kernels(tiny_folders, plain_models):
+    """``Engine(fuse_decode_layers=True)``: decode steps of up to 16 requests run each layer as one persistent kernel;
+    the tokens follow the plain implementation's logits as the ordinary path's do."""
+    from acvram_b200 import SamplingParams
+    cfg, t = plain_models["F"]
+    prompts = [random_ids(cfg["vocab_size"], n, 300 + n) for n in (5, 70, 131)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    fused = engine_for(tiny_folders["F"], "bfloat16", page_size=16, max_model_len=512, fuse_decode_layers=True)
+    plain = engine_for(tiny_folders["F"], "bfloat16", page_size=16, max_model_len=512)
+    got_f, got_p = fused.generate_batch(prompts, sp), plain.generate_batch(prompts, sp)
+    assert fused.stats.failed_steps == 0 and all(b.fuse_decode for b in fused.model.blocks)
+    for p, gf, gp in zip(prompts, got_f, got_p):
+        ref = plain_qwen3.forward_logits(cfg, t, p)
+        assert gf[0] == gp[0] == int(ref[-1].argmax())
+    # from then on each path follows its own roundings; both stay close to the plain model's choice at every step
+    for p, gf in zip(prompts, got_f):
+        ids = list(p)
+        for tok in gf:
+            lg = plain_qwen3.forward_logits(cfg, t, ids)[-1]
+            assert float(lg.max() - lg[tok]) < 0.05, "a token far from the plain model's best"
+            ids.append(tok)

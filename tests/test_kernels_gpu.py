@@ -84,6 +84,28 @@ def test_swiglu(ops, dtype, T, I):
     assert torch.isfinite(o1.float()).all()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,N", [(1, 17), (9, 331), (300, 4096)])
+def test_add_bias(ops, dtype, T, N):
+    out = rnd(T, N + 5, dtype=dtype, seed=21)[:, :N]          # a row stride that is not the width
+    bias = rnd(N, seed=22)
+    want = out.clone()
+    ref.add_bias(want, bias)
+    ops.add_bias(out, bias)
+    torch.testing.assert_close(out, want, **tol(dtype))
+
+
+def test_table_update(ops):
+    """The (row, column, page) triples of a step reach the block table on the device; what lies outside is skipped."""
+    table = torch.full((5, 7), -1, dtype=torch.int32, device="cuda")
+    triples = torch.tensor([[0, 0, 11], [4, 6, 12], [2, 3, 13], [2, 3, 14], [5, 0, 15], [0, 7, 16], [-1, 2, 17], [1, 1, 99]],
+                           dtype=torch.int32, device="cuda").reshape(-1)
+    ops.table_update(table, triples, 7)             # the eighth triple is not part of the step
+    want = torch.full((5, 7), -1, dtype=torch.int32)
+    want[0, 0], want[4, 6], want[2, 3] = 11, 12, 14
+    assert torch.equal(table.cpu(), want)
+
+
 def _paged_setup(B, lens, NKV, D, page, dtype, n_pages, seed, shuffle=True):
     """Random block tables over a shuffled pool; returns (k_pages, v_pages, table[B, W])."""
     g = torch.Generator().manual_seed(seed)
