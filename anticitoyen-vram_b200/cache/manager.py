@@ -515,10 +515,13 @@ class CacheManager:
         return self.max_requests
 
     def take_updates(self) -> list[list[tuple[int, int, int]]]:
-        """For each paged group the (row, column, page) entries that changed since the last call, oldest first."""
+        """For each paged group the (row, column, page) entries that changed since the last call, each entry once."""
         out = []
         for g in self._paged:
-            out.append(g.dirty)
+            # an entry noted twice (a row given back and taken again before a step ran) goes out once, with its last
+            # value: the kernel that writes the entries runs them side by side
+            last = {(row, col): page for row, col, page in g.dirty}
+            out.append([(row, col, page) for (row, col), page in last.items()] if len(last) != len(g.dirty) else g.dirty)
             g.dirty = []
         return out
 

@@ -301,3 +301,29 @@ def test_random_orders_with_shared_beginnings(seed):
         m.release(r, m.page_keys(tokens))
     m.check()
     assert m.free_pages() == [14] and m.reused_tokens > 0
+
+
+def test_changed_block_table_entries_go_out_once_each():
+    """The device's copy of the block tables gets (row, column, page) triples; an entry that changed twice between
+    two steps (a row given back and taken again) goes out once, with its last value."""
+    m = CacheManager(CachePlan([PagedNeed(1, 8, 0)]), 4, 8, 2)
+    m.admit("a")
+    m.grow("a", 6)
+    row_a = m.rows["a"]
+    first = m.take_updates()[0]
+    assert sorted(first) == [(row_a, 0, m.block_table("a", 0)[0]), (row_a, 1, m.block_table("a", 0)[1])]
+    assert m.take_updates() == [[]]
+    m.admit("b")
+    m.grow("b", 3)
+    m.release("b")                      # given back before any step ran
+    m.admit("c")                        # takes the same row
+    m.grow("c", 9)
+    assert m.rows["c"] != row_a
+    got = m.take_updates()[0]
+    assert len(got) == len({(r, c) for r, c, _ in got}) == 3
+    assert sorted(got) == [(m.rows["c"], i, p) for i, p in enumerate(m.block_table("c", 0))]
+    m.resync()
+    again = m.take_updates()[0]
+    assert sorted(again) == sorted([(row_a, i, p) for i, p in enumerate(m.block_table("a", 0))] +
+                                   [(m.rows["c"], i, p) for i, p in enumerate(m.block_table("c", 0))])
+    m.check()

