@@ -33,13 +33,13 @@ def _time(fn, reps: int) -> float:
     return s.elapsed_time(e) / reps * 1e3
 
 
-def gemm_case(M: int, N: int, K: int, reps: int) -> dict:
+def gemm_case(M: int, N: int, K: int, reps: int, plan: tuple | None = None) -> dict:
     copies = max(2, int(400e6 // (N * K * 2)) + 1)
     ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-    us = _time(lambda i: ops.gemm_tc(x, ws[i % copies], out), reps)
-    plan = ops.gemm_tc_plan(M, N, K)
+    us = _time(lambda i: ops.gemm_tc(x, ws[i % copies], out, plan), reps)
+    plan = plan or ops.gemm_tc_plan(M, N, K)
     print(f"gemm_tc M={M} N={N} K={K} plan(swap, bn, splits)={plan}: {us:.1f} us, "
           f"{N * K * 2 / us / 1e3:.0f} GB/s of weights, {2 * M * N * K / us / 1e6:.0f} TFLOP/s")
     return {"kernel": "gemm_tc", "M": M, "N": N, "K": K, "us": us, "weights_gbs": N * K * 2 / us / 1e3,
@@ -79,6 +79,18 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
         flops = batch * 4.0 * NH * D * (q_len * (context - q_len) + q_len * (q_len + 1) / 2)
         print(f"{kernel.__name__} batch={batch} q_len={q_len} context={context} page={page}: {us:.1f} us, {flops / us / 1e6:.0f} TFLOP/s")
         return {"kernel": kernel.__name__, "batch": batch, "q_len": q_len, "context": context, "us": us, "tflops": flops / us / 1e6}
+
+
+def tile_width_case(reps: int) -> dict:
+    """The tokens-on-rows product at every tile width, for the shapes of a 2048-token prefill (8B sizes) and of a
+    1024-token portion beside 32 decoding requests (14B sizes): what ``ops.GEMM_TILE_OVERHEAD`` was read from."""
+    out = {}
+    for M, N, K in ((2048, 4096, 4096), (2048, 4096, 12288), (2048, 24576, 4096), (1056, 5120, 5120), (1056, 5120, 17408),
+                    (1056, 34816, 5120)):
+        for bn in ops.GEMM_TILE_WIDTHS:
+            out[f"{M}x{N}x{K} bn={bn}"] = gemm_case(M, N, K, reps, plan=(0, bn, 1, 8))["us"]
+        print(f"   chosen for {M}x{N}x{K}: {ops.gemm_tc_plan(M, N, K)[1]} columns")
+    return out
 
 
 def sample_case(rows: int, vocab: int, reps: int) -> dict:
@@ -144,6 +156,7 @@ CASES = {
     "attention_prefill": lambda r: attention_case(1, 2048, 2048, r),
     "attention_prefill_8k": lambda r: attention_case(1, 2048, 8192, r),
     "attention_prefill_mma_sync": lambda r: attention_case(1, 2048, 2048, r, legacy=True),
+    "gemm_tile_widths": tile_width_case,
     "sample": lambda r: sample_case(8, 151936, r),
     "decode_layer_fused": lambda r: decode_layer_case(8, 2048, r, True),
     "decode_layer_separate": lambda r: decode_layer_case(8, 2048, r, False),
