@@ -28,7 +28,7 @@ class PreNormBlock:
         self.feed_forward = build("feed_forward", spec.feed_forward, hidden_size)
         # Small decode steps can run the whole layer as one persistent kernel (csrc/decode_layer.cu).  Off unless asked
         # for: measured on a B200 at the layer sizes of Qwen3-8B it is slower than the seven separate launches (a step's
-        # time goes to the chain of dependent phases, which one kernel does not shorten), see profiles/.
+        # time goes to the chain of dependent phases, which one kernel does not shorten).
         self.fuse_decode = False
 
     def tensor_needs(self):
