@@ -114,3 +114,77 @@ def test_kernels_refuse_cpu_tensors_and_unknown_types():
         pages = torch.zeros(1, 1, 16, 512, device="cuda")
         z = torch.zeros(1, dtype=torch.int32, device="cuda")
         ops.attention_generic(q, torch.zeros(1, 512, device="cuda"), pages, pages, z, z, z.view(1, 1), 1, 1, 512, 1.0)
+
+
+@pytest.mark.parametrize("name,dtype,window", [("A", "float32", 16), ("F", "bfloat16", 40), ("D", "bfloat16", 24)])
+def test_window_layers_on_the_device(name, dtype, window, tiny_folders, plain_models):
+    """A window on the second layer (a toy plan of the test's own): another cache group with pages given back as the
+    window passes them, their block-table entries on the device set to "no page", and later pages of the same request
+    taking the freed ones.  Portions and single tokens, two requests, against the plain layers."""
+    import dataclasses
+
+    import numpy as np
+
+    import plain_qwen3
+    from acvram_b200.engine.batch import StepEntry
+    from acvram_b200.engine.runner import ModelRunner
+    from acvram_b200.models import DecoderModel, plan_of_folder
+    from acvram_b200.parts import Runtime
+    from acvram_b200.weights import load_tensors
+    from conftest import random_ids
+
+    cfg, t = plain_models[name]
+    _, plan = plan_of_folder(tiny_folders[name])
+    layers = list(plan.layers)
+    layers[1] = dataclasses.replace(layers[1], mixer=layers[1].mixer.with_params(window=window))
+    plan = dataclasses.replace(plan, layers=tuple(layers))
+    model = DecoderModel(plan)
+    run_dtype = getattr(torch, dtype)
+    model.load(load_tensors(tiny_folders[name], model.tensor_needs()), Runtime(torch.device("cuda:0"), run_dtype))
+    assert len(model.cache_plan().groups) == 2
+    page = 8
+    pool = (60 + 2 * window) // page + 8                 # the windowed group's pool holds less than the requests' tokens
+    runner = ModelRunner(model, page, [40, pool], 3)
+    if run_dtype == torch.bfloat16:
+        runner.enable_graphs()
+    reqs = {"a": random_ids(cfg["vocab_size"], 150, 61), "b": random_ids(cfg["vocab_size"], 90, 62)}
+
+    def plain(ids, dt):
+        s = plain_qwen3.sizes(cfg)
+        x = plain_qwen3.embed(t["model.embed_tokens.weight"], torch.tensor(ids), dt)
+        positions = torch.arange(len(ids))
+        for i in range(s["L"]):
+            x = plain_qwen3.decoder_layer(x, t, i, s, positions, window if i == 1 else 0)
+        return plain_qwen3.output_logits(x, t, s).numpy()
+
+    ref = {k: plain(v, torch.float32) for k, v in reqs.items()}
+    if dtype == "float32":
+        bound = 2e-5 * max(1.0, max(float(np.abs(v).max()) for v in ref.values()))
+    else:
+        bound = 2.5 * max(float(np.abs(plain(v, torch.bfloat16) - ref[k]).max()) for k, v in reqs.items())
+    at = {"a": 0, "b": 0}
+    worst = 0.0
+    schedule = [{"a": 37}, {"a": 2, "b": 30}, {"a": 1, "b": 1}, {"a": 1, "b": 1}, {"a": 40, "b": 1}, {"a": 1, "b": 17},
+                {"a": 1, "b": 1}, {"a": 1, "b": 1}, {"a": 60, "b": 1}, {"a": 1, "b": 30}] + [{"a": 1, "b": 1}] * 6
+    for step in schedule:
+        entries = []
+        for k, n in step.items():
+            n = min(n, len(reqs[k]) - at[k])
+            if n > 0:
+                entries.append(StepEntry(k, reqs[k][at[k]:at[k] + n], range(n)))
+        lg = runner.step(entries).float().cpu().numpy()
+        row = 0
+        for e in entries:
+            for i in range(len(e.tokens)):
+                worst = max(worst, float(np.abs(lg[row] - ref[e.request][at[e.request] + i]).max()))
+                row += 1
+            at[e.request] += len(e.tokens)
+    runner.check_status()
+    assert worst <= bound, f"max |logit - plain| = {worst:.3e} (bound {bound:.3e})"
+    full_free, window_free = runner.manager.free_pages()
+    held = sum(-(-at[k] // page) for k in reqs)
+    assert full_free == 40 - held and window_free >= pool - 2 * (window // page + 2), "the window's pages went back"
+    for k in reqs:
+        runner.release(k)
+    runner.manager.check()
+    assert runner.manager.free_pages() == [40, pool]
