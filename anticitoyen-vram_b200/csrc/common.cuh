@@ -191,8 +191,8 @@ __device__ __forceinline__ void cluster_sync_all() {
 // Without the flag the macros expand to nothing.
 #ifdef ACV_TIMELINE
 #define ACV_TL_CAP (1 << 16)
-#define ACV_TL_MARKS 8
-struct AcvTlRecord { unsigned long long t0, t1; int kernel, block, grid, smid; unsigned long long mark[ACV_TL_MARKS]; };
+#define ACV_TL_MARKS 12
+struct AcvTlRecord { unsigned long long t0, t1; int kernel, block, grid, smid; unsigned long long mark[ACV_TL_MARKS]; unsigned long long cycles; };
 static __device__ AcvTlRecord acv_tl_log[ACV_TL_CAP];
 static __device__ unsigned int acv_tl_count;
 __device__ __forceinline__ unsigned long long acv_tl_now() {
@@ -203,17 +203,19 @@ __device__ __forceinline__ unsigned long long acv_tl_now() {
 // begin at construction, end at destruction; the marks of the CTA's threads wait in shared memory and the
 // whole record is written once, by one thread, when the kernel ends (nothing is sent to memory before)
 struct AcvTlScope {
-    unsigned long long t0; int kernel; bool mine; unsigned long long* marks;
+    unsigned long long t0; long long c0; int kernel; bool mine; unsigned long long* marks;
     __device__ __forceinline__ AcvTlScope(int k, int thread, unsigned long long* m)
         : kernel(k), mine((int)threadIdx.x == thread), marks(m) {
         if (mine) {
             t0 = acv_tl_now();
+            c0 = clock64();
             for (int i = 0; i < ACV_TL_MARKS; ++i) marks[i] = 0;
         }
     }
     __device__ __forceinline__ ~AcvTlScope() {
         if (!mine) return;
         const unsigned long long t1 = acv_tl_now();
+        const long long c1 = clock64();        // SM cycles of the CTA's life: with t1 - t0, the clock it ran at
         const unsigned int i = atomicAdd(&acv_tl_count, 1u);
         if (i >= ACV_TL_CAP) return;
         unsigned int smid;
@@ -223,6 +225,7 @@ struct AcvTlScope {
         r.block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
         r.grid = gridDim.x * gridDim.y * gridDim.z; r.smid = (int)smid;
         for (int k = 0; k < ACV_TL_MARKS; ++k) r.mark[k] = marks[k];
+        r.cycles = (unsigned long long)(c1 - c0);
         acv_tl_log[i] = r;
     }
 };
@@ -230,6 +233,15 @@ struct AcvTlScope {
     __shared__ unsigned long long acv_tl_marks[ACV_TL_MARKS];       \
     AcvTlScope acv_tl_scope(kernel_id, thread, acv_tl_marks)
 #define ACV_TL_MARK(i) (acv_tl_marks[i] = acv_tl_now())             // by one thread; i < ACV_TL_MARKS
+// sums of waiting times inside the loops of the matrix product (marks used as sums of nanoseconds, each by one
+// thread): the timer reads cost the loops some 35 cycles each, so they are compiled only with -DACV_TIMELINE_SUMS
+#ifdef ACV_TIMELINE_SUMS
+#define ACV_TL_NOW() acv_tl_now()
+#define ACV_TL_ADD(i, since) (acv_tl_marks[i] += acv_tl_now() - (since))
+#else
+#define ACV_TL_NOW() 0ull
+#define ACV_TL_ADD(i, since) ((void)(since))
+#endif
 #define ACV_TL_EXPORT(file)                                                                                     \
     ACV_API int acv_tl_read_##file(void* host, int cap, int reset) {                                            \
         unsigned int n = 0;                                                                                     \
@@ -243,6 +255,8 @@ struct AcvTlScope {
 #else
 #define ACV_TL(kernel_id, thread)
 #define ACV_TL_MARK(i)
+#define ACV_TL_NOW() 0ull
+#define ACV_TL_ADD(i, since) ((void)(since))
 #define ACV_TL_EXPORT(file)
 #endif
 // kernel ids of the timeline
@@ -263,5 +277,12 @@ struct AcvTlScope {
 #define TL_M_CLUSTER_MET 4     // ... and the cluster's CTAs have met
 #define TL_M_STORED 5          // the CTA's results are written
 #define TL_M_WAIT_OVER 6       // the producer's wait for the predecessor has ended
+// sums of nanoseconds (tokens on rows, no split of K, where marks 3 and 4 are free)
+#define TL_M_SUM_STAGE_WAIT 3  // the issuing thread waited for operand stages
+#define TL_M_SUM_ACC_WAIT 4    // the issuing thread waited for an accumulator buffer
+#define TL_M_SUM_EPILOGUE 7    // the first epilogue thread worked on finished accumulators
+#define TL_M_SUM_FREE_WAIT 8   // the loading thread waited for a stage to be free
+#define TL_M_SUM_LOAD_ISSUE 9  // the loading thread issued loads
+#define TL_M_SUM_MMA_ISSUE 10  // the issuing thread issued products and commits
 // marks of the decode attention
 #define TL_M_ATTN_LOOP_DONE 0  // a CTA's keys are done, the merge begins

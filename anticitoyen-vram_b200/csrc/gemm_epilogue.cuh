@@ -17,6 +17,7 @@ struct GemmParams {
     int out_f32;
     int act;                // 1: output features come in (gate, up) pairs and C[:, n/2] = silu(gate) * up
     int tiles_a, tiles_b, splits, kb_per_split, n_kb;
+    int group_a;            // rows of tiles that are walked together (see gt_tile_of)
     int early_w;            // 1: the weights were written long before this launch: their first tiles are loaded before the predecessor ends
     int cluster;            // 1: the splits of a tile are the CTAs of one cluster and are summed through its shared memory
     int stages;             // pipeline depth (2..8); shared memory = stages * (128 + BN) * 128 bytes

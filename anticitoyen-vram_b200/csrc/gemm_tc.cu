@@ -152,6 +152,22 @@ struct GemmShape {
     }
 };
 
+// Which tile a work item is.  Tiles are walked in groups of `group` rows of tiles (all columns of a group before the
+// next group), rows fastest: the CTAs that run at one time then share few rows of tiles and a few columns of
+// them, so that with many tokens neither the activations nor the weights are read from memory over and over.
+__device__ __forceinline__ void gt_tile_of(int tile, int tiles_a, int tiles_b, int group, int& ta, int& tb) {
+    if (group >= tiles_a) {         // one group (weights on the rows): a single division, the thread that loads is waited for
+        tb = tile / tiles_a;
+        ta = tile - tb * tiles_a;
+        return;
+    }
+    const int per_group = group * tiles_b;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int rows = min(group, tiles_a - g * group);
+    tb = r / rows;
+    ta = g * group + (r - tb * rows);
+}
+
 // Registers are handed out to a CTA for its warps rounded up to four: 192 threads count as 8 warps, and three
 // such CTAs share an SM (what the narrow decode products with short pipelines want) only up to 80 registers
 // a thread (measured: at 106 registers two came to an SM and the gate/up product of a decode step ran in
@@ -212,7 +228,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             int early = 0;
             if (p.early_w && (int)blockIdx.x < n_items) {
                 const int split = blockIdx.x % p.splits, tile = blockIdx.x / p.splits;
-                const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+                int ta, tb;
+                gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
                 early = min(STAGES, kb1 - kb0);
                 for (int i = 0; i < early; ++i) {
@@ -228,7 +245,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             uint32_t ph = 0;
             for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x) {
                 const int split = item % p.splits, tile = item / p.splits;
-                const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+                int ta, tb;
+                gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
                 for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
                     const uint32_t a_dst = tiles_addr + s * S::STAGE_BYTES;
@@ -236,38 +254,53 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (half_done) {
                         --early;
                     } else {
+                        [[maybe_unused]] const unsigned long long tp0 = ACV_TL_NOW();
                         if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 1); break; }
+                        ACV_TL_ADD(TL_M_SUM_FREE_WAIT, tp0);
                         mbar_expect_tx(full0 + 8 * s, S::STAGE_BYTES);
                     }
                     if (kb == p.skip_kb) continue;          // test of the bounded waits: the bytes announced never come
+                    [[maybe_unused]] const unsigned long long tp1 = ACV_TL_NOW();
                     if (!(half_done && p.swap)) tma_load_2d(a_dst, &map_a, full0 + 8 * s, kb * GT_BK, ta * GT_BM);
                     if (!(half_done && !p.swap)) tma_load_2d(a_dst + GT_BM * GT_BK * 2, &map_b, full0 + 8 * s, kb * GT_BK, tb * BN);
+                    ACV_TL_ADD(TL_M_SUM_LOAD_ISSUE, tp1);
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
         if (lane == 0) {
+            // The one thread's instructions are what a k-block costs beside its products: the descriptors are kept as
+            // their low halves (address and leading offset), a stage or 16 elements of k further is one 32-bit add.
             const uint32_t idesc = umma_idesc(BN);
-            uint32_t local = 0, ph = 0;
+            const uint32_t a_lo0 = umma_desc_lo(tiles_addr), b_lo0 = umma_desc_lo(tiles_addr + GT_BM * GT_BK * 2);
+            constexpr uint32_t STAGE_LO = S::STAGE_BYTES >> 4;
+            uint32_t local = 0, ph = 0, s_lo = 0;
             int s = 0;
             for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
                 const int split = item % p.splits;
                 const int kb0 = split * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.n_kb);
                 const uint32_t buf = local & 1, use = local >> 1;
+                [[maybe_unused]] const unsigned long long tw0 = ACV_TL_NOW();
                 if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 2); break; }
+                if (p.splits == 1) ACV_TL_ADD(TL_M_SUM_ACC_WAIT, tw0);
                 tc_fence_after();
                 const uint32_t d = tmem_base + buf * BN;
                 bool failed = false;
-                for (int kb = kb0; kb < kb1; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    [[maybe_unused]] const unsigned long long tw1 = ACV_TL_NOW();
                     if (!mbar_wait(full0 + 8 * s, ph, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 3); failed = true; break; }
-                    tc_fence_after();
+                    if (p.splits == 1) ACV_TL_ADD(TL_M_SUM_STAGE_WAIT, tw1);
                     if (local == 0 && kb == kb0) ACV_TL_MARK(TL_M_FIRST_FULL);
-                    const uint32_t a_addr = tiles_addr + s * S::STAGE_BYTES, b_addr = a_addr + GT_BM * GT_BK * 2;
+                    [[maybe_unused]] const unsigned long long ti0 = ACV_TL_NOW();
+                    const uint32_t a_lo = a_lo0 + s_lo, b_lo = b_lo0 + s_lo;
+                    tc_mma_bf16_h(d, a_lo, b_lo, idesc, kb > kb0 ? 1u : 0u);
 #pragma unroll
-                    for (int k = 0; k < GT_BK / 16; ++k)
-                        tc_mma_bf16(d, umma_desc(a_addr + k * 32), umma_desc(b_addr + k * 32), idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    for (int k = 1; k < GT_BK / 16; ++k) tc_mma_bf16_h(d, a_lo + 2 * k, b_lo + 2 * k, idesc, 1u);
                     tc_commit(empty0 + 8 * s);      // frees the stage when these MMAs have read it
+                    ACV_TL_ADD(TL_M_SUM_MMA_ISSUE, ti0);
+                    ++s; s_lo += STAGE_LO;
+                    if (s == STAGES) { s = 0; s_lo = 0; ph ^= 1; }
                 }
                 if (failed) break;
                 tc_commit(tfull0 + 8 * buf);        // the accumulator is complete
@@ -282,7 +315,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (p.qkv && p.swap && (int)blockIdx.x < n_items && (!cluster_split || cluster_ctarank() == 0)) {
             // where each token of the tile stands and goes, and its angles: read now, needed when the tile leaves
             const int tile = blockIdx.x / p.splits;
-            const int tb = tile / p.tiles_a;
+            int ta0, tb;
+            gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta0, tb);
             int* pos_s = reinterpret_cast<int*>(aux);
             int* pg_s = pos_s + BN;
             float* cs_s = reinterpret_cast<float*>(pg_s + BN);
@@ -315,10 +349,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         uint32_t local = 0;
         for (int item = blockIdx.x; item < n_items && !abort_s; item += gridDim.x, ++local) {
             const int split = item % p.splits, tile = item / p.splits;
-            const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+            int ta, tb;
+            gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
             const uint32_t buf = local & 1, use = local >> 1;
             if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 4); break; }
             tc_fence_after();
+            [[maybe_unused]] const unsigned long long te0 = ACV_TL_NOW();
             if (et == 0 && item + (int)gridDim.x >= n_items) ACV_TL_MARK(TL_M_ACC_DONE);
             const int row_a = ta * GT_BM + wq * 32 + lane;          // row of the A operand this thread holds
             const uint32_t taddr = tmem_base + buf * BN + ((uint32_t)(wq * 32) << 16);
@@ -332,6 +368,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+                if (et == 0) ACV_TL_ADD(TL_M_SUM_EPILOGUE, te0);
                 continue;
             }
             if (p.splits == 1) {
@@ -350,6 +387,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty0 + 8 * buf);
+                if (et == 0 && !p.swap) ACV_TL_ADD(TL_M_SUM_EPILOGUE, te0);
                 if (p.staged) {         // the only item of this CTA: its loads have all been consumed
                     asm volatile("bar.sync 1, 128;" ::: "memory");
                     if (p.qkv) gt_flush_qkv(p, tiles, aux, ta, tb, BN, et);
@@ -424,7 +462,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         if (warp >= 2 && cluster_ctarank() == 0 && !abort_s) {
             const int wq = warp & 3;
             const int tile = blockIdx.x / p.splits;
-            const int ta = tile % p.tiles_a, tb = tile / p.tiles_a;
+            int ta, tb;
+            gt_tile_of(tile, p.tiles_a, p.tiles_b, p.group_a, ta, tb);
             const int row_a = ta * GT_BM + wq * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(wq * 32) << 16);
             const float* part = reinterpret_cast<const float*>(tiles + STAGES * S::STAGE_BYTES + 256) + wq * 32 + lane;
@@ -456,6 +495,187 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(S::TMEM_COLS));
+    }
+}
+
+// ----------------------------------------------------------------------------- pairs of CTAs on tiles of 256 x 256
+// Many tokens (tokens on the rows of A, no split of K): the two CTAs of a cluster of two, on neighbouring SMs, work on
+// one tile of 256 tokens by 256 features with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 token rows of A and
+// its own 128 of the tile's 256 weight rows of B (32 KB a k-block instead of the 48 KB that a CTA with a tile of its own
+// loads, and half of B's shared-memory reads), and holds the accumulator rows of its 128 tokens, all 256 columns, in
+// its own tensor memory.  The CTA of rank 0 leads: its "full" barriers count the bytes of both CTAs' loads (the loads
+// carry .cta_group::2, which lets a load signal a barrier of the pair's other CTA), its one thread issues the
+// products for both, and tcgen05.commit with a multicast mask frees the stage and announces the accumulator in both
+// CTAs at once.  The epilogue warps of both CTAs read their own tensor memory and hand the buffer back at the
+// leader's barrier (eight arrivals: four warps each).  Warp roles, the two accumulator buffers, the bounded waits
+// and the status word are those of gemm_tc_kernel; so are the epilogues (plain, SiLU(gate)*up, q,k,v).
+#define GP_BN 256
+#define GP_STAGE_BYTES ((GT_BM + GT_BM) * GT_BK * 2)        // a CTA's share of a k-block: 128 rows of A, 128 of B
+#define GP_MAX_STAGES 6
+
+__global__ void __launch_bounds__(GT_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, GemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* tiles = smem_raw + ((1024u - (gt_smem(smem_raw) & 1023u)) & 1023u);
+    const int STAGES = p.stages;
+    uint64_t* bars = (uint64_t*)(tiles + STAGES * GP_STAGE_BYTES);
+    // bars: full[STAGES] (used in the leader), empty[STAGES], tmem_full[2], tmem_empty[2] (used in the leader)
+    const uint32_t full0 = gt_smem(bars), empty0 = full0 + 8 * STAGES;
+    const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+    __shared__ uint32_t tmem_base_s;
+    __shared__ volatile int abort_s;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();                // 0 leads the pair
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    ACV_TL(TL_GEMM, 64);
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {        // the same warp of both CTAs: the pair's tensor memory is given out to both at once
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gt_smem(&tmem_base_s)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();     // both CTAs' barriers exist before a load or a commit of the other arrives at them
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    pdl_launch_dependents();
+
+    const int tiles_a2 = (p.RA + 2 * GT_BM - 1) / (2 * GT_BM);
+    const int n_items = tiles_a2 * p.tiles_b;
+    const uint32_t tiles_addr = gt_smem(tiles);
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs, each its rows)
+        if (lane == 0) {
+            const uint32_t lead_full0 = cluster_map(full0, 0);
+            int early = 0;              // the first stages' weight rows are asked for while the predecessor still runs
+            if (p.early_w && pair < n_items) {
+                int ta, tb;
+                gt_tile_of(pair, tiles_a2, p.tiles_b, p.group_a, ta, tb);
+                early = min(STAGES, p.n_kb);
+                for (int i = 0; i < early; ++i) {
+                    if (rank == 0) mbar_expect_tx(full0 + 8 * i, 2 * GP_STAGE_BYTES);
+                    tma_load_2d_pair(tiles_addr + i * GP_STAGE_BYTES + GT_BM * GT_BK * 2, &map_b, lead_full0 + 8 * i,
+                                     i * GT_BK, tb * GP_BN + (int)rank * GT_BM);
+                }
+            }
+            pdl_wait();
+            ACV_TL_MARK(TL_M_WAIT_OVER);
+            int s = 0;
+            uint32_t ph = 0;
+            for (int item = pair; item < n_items && !abort_s; item += n_pairs) {
+                int ta, tb;
+                gt_tile_of(item, tiles_a2, p.tiles_b, p.group_a, ta, tb);
+                for (int kb = 0; kb < p.n_kb; ++kb, s = (s + 1 == STAGES ? 0 : s + 1), ph ^= (s == 0)) {
+                    const uint32_t a_dst = tiles_addr + s * GP_STAGE_BYTES;
+                    const bool half_done = early > 0;
+                    if (half_done) {
+                        --early;
+                    } else {
+                        [[maybe_unused]] const unsigned long long tp0 = ACV_TL_NOW();
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 1); break; }
+                        ACV_TL_ADD(TL_M_SUM_FREE_WAIT, tp0);
+                        if (rank == 0) mbar_expect_tx(full0 + 8 * s, 2 * GP_STAGE_BYTES);
+                    }
+                    if (kb == p.skip_kb) continue;          // test of the bounded waits: the bytes announced never come
+                    [[maybe_unused]] const unsigned long long tp1 = ACV_TL_NOW();
+                    tma_load_2d_pair(a_dst, &map_a, lead_full0 + 8 * s, kb * GT_BK, ta * 2 * GT_BM + (int)rank * GT_BM);
+                    if (!half_done)
+                        tma_load_2d_pair(a_dst + GT_BM * GT_BK * 2, &map_b, lead_full0 + 8 * s, kb * GT_BK, tb * GP_BN + (int)rank * GT_BM);
+                    ACV_TL_ADD(TL_M_SUM_LOAD_ISSUE, tp1);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (the leader's one thread)
+        if (lane == 0 && rank == 0) {
+            const uint32_t idesc = umma_idesc(GP_BN, 2 * GT_BM);
+            const uint32_t a_lo0 = umma_desc_lo(tiles_addr), b_lo0 = umma_desc_lo(tiles_addr + GT_BM * GT_BK * 2);
+            constexpr uint32_t STAGE_LO = GP_STAGE_BYTES >> 4;
+            uint32_t local = 0, ph = 0, s_lo = 0;
+            int s = 0;
+            for (int item = pair; item < n_items && !abort_s; item += n_pairs, ++local) {
+                const uint32_t buf = local & 1, use = local >> 1;
+                [[maybe_unused]] const unsigned long long tw0 = ACV_TL_NOW();
+                if (!mbar_wait(tempty0 + 8 * buf, (use & 1) ^ 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 2); break; }
+                ACV_TL_ADD(TL_M_SUM_ACC_WAIT, tw0);
+                tc_fence_after();
+                const uint32_t d = tmem_base + buf * GP_BN;
+                bool failed = false;
+                for (int kb = 0; kb < p.n_kb; ++kb) {
+                    [[maybe_unused]] const unsigned long long tw1 = ACV_TL_NOW();
+                    if (!mbar_wait(full0 + 8 * s, ph, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 3); failed = true; break; }
+                    ACV_TL_ADD(TL_M_SUM_STAGE_WAIT, tw1);
+                    if (local == 0 && kb == 0) ACV_TL_MARK(TL_M_FIRST_FULL);
+                    [[maybe_unused]] const unsigned long long ti0 = ACV_TL_NOW();
+                    const uint32_t a_lo = a_lo0 + s_lo, b_lo = b_lo0 + s_lo;
+                    tc_mma_bf16_pair_h(d, a_lo, b_lo, idesc, kb > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int k = 1; k < GT_BK / 16; ++k) tc_mma_bf16_pair_h(d, a_lo + 2 * k, b_lo + 2 * k, idesc, 1u);
+                    tc_commit_pair(empty0 + 8 * s, 3);      // frees the stage in both CTAs
+                    ACV_TL_ADD(TL_M_SUM_MMA_ISSUE, ti0);
+                    ++s; s_lo += STAGE_LO;
+                    if (s == STAGES) { s = 0; s_lo = 0; ph ^= 1; }
+                }
+                if (failed) break;
+                tc_commit_pair(tfull0 + 8 * buf, 3);        // the accumulator is complete, in both CTAs
+                if (item + n_pairs >= n_items) ACV_TL_MARK(TL_M_LAST_MMA);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+        const int wq = warp & 3;
+        pdl_wait();
+        const uint32_t lead_tempty0 = cluster_map(tempty0, 0);
+        uint32_t local = 0;
+        for (int item = pair; item < n_items && !abort_s; item += n_pairs, ++local) {
+            int ta, tb;
+            gt_tile_of(item, tiles_a2, p.tiles_b, p.group_a, ta, tb);
+            const uint32_t buf = local & 1, use = local >> 1;
+            if (!mbar_wait(tfull0 + 8 * buf, use & 1, &abort_s, p.wait_limit)) { abort_s = 1; atomicExch(p.status, 4); break; }
+            tc_fence_after();
+            [[maybe_unused]] const unsigned long long te0 = ACV_TL_NOW();
+            if (threadIdx.x == 64 && item + n_pairs >= n_items) ACV_TL_MARK(TL_M_ACC_DONE);
+            const int row_a = ta * 2 * GT_BM + (int)rank * GT_BM + wq * 32 + lane;        // the token this thread holds
+            const uint32_t taddr = tmem_base + buf * GP_BN + ((uint32_t)(wq * 32) << 16);
+            if (p.qkv) {
+                if (p.head_dim == 128) gt_store_qkv_rows<GP_BN, 128>(p, taddr, row_a, tb);
+                else gt_store_qkv_rows<GP_BN, 64>(p, taddr, row_a, tb);
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < GP_BN; c0 += 16) {
+                    uint32_t r[16];
+                    tc_ld16(taddr + c0, r);
+                    float v[16];
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) v[c] = __uint_as_float(r[c]);
+                    gt_store16(p, row_a, tb * GP_BN + c0, v, lane);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(tempty0 + 8 * buf);
+                else mbar_arrive_remote(lead_tempty0 + 8 * buf);
+            }
+            if (threadIdx.x == 64) ACV_TL_ADD(TL_M_SUM_EPILOGUE, te0);
+        }
+    }
+    if (threadIdx.x == 64) ACV_TL_MARK(TL_M_STORED);
+    // neither CTA leaves, nor is the pair's tensor memory given back, while the other may still read this one's
+    // shared memory or arrive at its barriers
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512));
     }
 }
 
@@ -496,6 +716,51 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams&
     return acv_launch_status();
 }
 
+// Pairs that can be resident at once: clusters of two need two free SMs side by side, which an odd number of SMs in
+// a part of the chip does not give; the grid is made of that many pairs and each walks the tiles with that stride.
+static int launch_gemm_pair(const CUtensorMap& ma, const CUtensorMap& mb, GemmParams& p, int sm_count, int stages,
+                            cudaStream_t stream) {
+    if (stages < 2) stages = 2;
+    if (stages > GP_MAX_STAGES) stages = GP_MAX_STAGES;
+    p.stages = stages;
+    const int smem = stages * GP_STAGE_BYTES + 1024 + 256;
+    static AcvSmemConfig smem_config;
+    if (int rc = acv_ensure_smem(smem_config, gemm_tc_pair_kernel, smem)) return rc;
+    static std::mutex mu;
+    static int pairs_of_device[64];
+    int dev = 0;
+    cudaGetDevice(&dev);
+    int resident = 0;
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (dev >= 0 && dev < 64) resident = pairs_of_device[dev];
+        if (resident <= 0) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(2 * (sm_count / 2));
+            cfg.blockDim = dim3(GT_THREADS);
+            cfg.dynamicSmemBytes = smem;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeClusterDimension;
+            attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+            cfg.attrs = attr;
+            cfg.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&resident, gemm_tc_pair_kernel, &cfg) != cudaSuccess || resident <= 0) {
+                cudaGetLastError();
+                return ACV_ERR_SIZE;
+            }
+            if (dev >= 0 && dev < 64) pairs_of_device[dev] = resident;
+        }
+    }
+    if (resident > sm_count / 2) resident = sm_count / 2;
+    const long long items = (long long)((p.RA + 2 * GT_BM - 1) / (2 * GT_BM)) * p.tiles_b;
+    const int n_pairs = (int)(items < resident ? items : resident);
+    if (n_pairs < 1) return ACV_ERR_SIZE;
+    p.staged = 0;
+    if (p.qkv && (GP_BN < p.head_dim || GP_BN % p.head_dim || p.act || p.out_f32)) return ACV_ERR_SIZE;
+    acv_launch_cluster(PDL_GEMM, dim3(2, 1, 1), gemm_tc_pair_kernel, 2 * n_pairs, GT_THREADS, smem, stream, ma, mb, p);
+    return acv_launch_status();
+}
+
 // Test of the bounded waits, without a fault: the next product launched from this process (and only that one)
 // polls each mbarrier at most `wait_limit` times and its producer leaves out the loads of k-block `skip_kb`, so the
 // wait for that block runs out, the CTA's roles leave their loops, tensor memory is freed, and `status` holds the
@@ -527,6 +792,8 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
     p.tiles_a = (p.RA + GT_BM - 1) / GT_BM;
     p.tiles_b = (p.RB + bn - 1) / bn;
     p.n_kb = (K + GT_BK - 1) / GT_BK;
+    // rows of tiles walked together: 2048 tokens' worth where tokens are the rows, all of them where weights are
+    p.group_a = swap ? p.tiles_a : ((flags & 4) ? 8 : 16);
     if (splits < 1) splits = 1;
     if (splits > p.n_kb) splits = p.n_kb;
     p.kb_per_split = (p.n_kb + splits - 1) / splits;
@@ -541,6 +808,12 @@ static int gemm_tc_run(GemmParams& p, const void* x, int ldx, const void* w, int
     CUtensorMap ma, mb;
     int rc = make_map(&ma, a_ptr, p.RA, K, swap ? ldw : ldx, GT_BM);
     if (rc) return rc;
+    if (flags & 4) {        // pairs of CTAs on tiles of 256 x 256: tokens on rows, no split of K
+        if (swap || p.splits != 1 || bn != GP_BN) return ACV_ERR_SIZE;
+        rc = make_map(&mb, b_ptr, p.RB, K, ldw, GT_BM);
+        if (rc) return rc;
+        return launch_gemm_pair(ma, mb, p, sm_count, stages, stream);
+    }
     rc = make_map(&mb, b_ptr, p.RB, K, swap ? ldx : ldw, bn);
     if (rc) return rc;
     switch (bn) {

@@ -31,6 +31,8 @@ LIB_PREFIX = "libacvram_b200_"
 if os.environ.get("ACVRAM_B200_TIMELINE", "0") not in ("", "0"):
     NVCC_FLAGS.append("-DACV_TIMELINE")      # diagnostic build: kernels log their CTAs' begin and end times
     LIB_PREFIX = "libacvram_b200tl_"         # a library of its own beside the serving one
+    if os.environ["ACVRAM_B200_TIMELINE"] == "sums":
+        NVCC_FLAGS.append("-DACV_TIMELINE_SUMS")     # and the matrix product sums up what its loops wait for
 
 
 class BuildError(RuntimeError):

@@ -348,16 +348,22 @@ GEMM_FEW_TOKENS_RULES = (
 # 69 us at 256, 63 us at 160).  The width is chosen so that rounds x (width + overhead) comes out least.
 GEMM_TILE_WIDTHS = (256, 224, 192, 160, 128)
 GEMM_TILE_OVERHEAD = 120
+# Pairs of CTAs on tiles of 256 tokens by 256 features (cta_group::2): a round of such tiles takes about 0.92 of a round
+# of 128 x 256 tiles (measured at 2048 and 8192 tokens with the layer sizes of 8B and 14B models: 4 to 11 % less), and
+# there are half as many places for them.
+GEMM_PAIR_ROUND = 0.92
+GEMM_PAIR = 4               # fifth element of a plan: the flag that asks for the pair kernel
 
 
-def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None, bn_multiple: int = 16) -> tuple[int, int, int, int]:
-    """(swap, bn, splits, stages) for x[M,K] @ w[N,K]^T on a device of ``sms`` multiprocessors.
+def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None, bn_multiple: int = 16) -> tuple:
+    """(swap, bn, splits, stages[, mode]) for x[M,K] @ w[N,K]^T on a device of ``sms`` multiprocessors.
 
     Up to 128 tokens the weight rows fill the tensor core's M = 128 and the tokens are the narrow
     side (weights stream once whatever the batch); splits of K are chosen so that the work items fill
     whole waves of the SMs (``GEMM_FEW_TOKENS_RULES``).  Above, tokens are the M side and a tile is 128
     tokens by 128..256 features: the width that needs the least rounds x width (``GEMM_TILE_WIDTHS``;
-    ``bn_multiple``: widths that are multiples of this only, for an epilogue that wants whole heads)."""
+    ``bn_multiple``: widths that are multiples of this only, for an epilogue that wants whole heads),
+    or, where that comes out cheaper, 256 x 256 on a pair of CTAs (``mode`` = ``GEMM_PAIR``)."""
     n_kb = -(-K // 64)
     if M <= 128:
         sms = sms or sm_count()
@@ -379,6 +385,10 @@ def gemm_tc_plan(M: int, N: int, K: int, sms: int | None = None, bn_multiple: in
         cost = -(-tiles // sms) * (bn + GEMM_TILE_OVERHEAD)
         if best_cost is None or cost < 0.97 * best_cost:       # a narrower tile has to win clearly
             best, best_cost = bn, cost
+    if sms >= 2 and 256 % bn_multiple == 0:
+        pair_tiles = -(-M // 256) * -(-N // 256)
+        if -(-pair_tiles // (sms // 2)) * (256 + GEMM_TILE_OVERHEAD) * GEMM_PAIR_ROUND < best_cost:
+            return 0, 256, 1, 6, GEMM_PAIR
     return 0, best, 1, 8
 
 
@@ -426,7 +436,7 @@ def gemm_tc_qkv_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, cos_sin: 
     M, K = x.shape
     N = w.shape[0]
     swap, bn, splits = gemm_tc_plan(M, N, K, bn_multiple=head_dim if M > 128 else 16)[:3]
-    if not swap:            # tokens on M: a thread of the epilogue holds whole heads of one token
+    if not swap:            # tokens on M (one CTA or a pair to a tile): a thread of the epilogue holds whole heads of one token
         return splits == 1 and bn >= head_dim and bn % head_dim == 0
     tiles = -(-N // 128) * -(-M // bn)
     return bn <= 32 and (1 < splits <= 8 or (splits == 1 and tiles <= sm_count(x.device)))
@@ -435,15 +445,17 @@ def gemm_tc_qkv_takes(x: torch.Tensor, w: torch.Tensor, head_dim: int, cos_sin: 
 def gemm_tc_qkv(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int,
                 q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, eps: float, cos_sin: torch.Tensor | None,
                 positions: torch.Tensor, seq_of_token: torch.Tensor, block_table: torch.Tensor, k_pages: torch.Tensor,
-                v_pages: torch.Tensor, static_weights: bool = False, table_rows: torch.Tensor | None = None) -> torch.Tensor:
+                v_pages: torch.Tensor, static_weights: bool = False, table_rows: torch.Tensor | None = None,
+                plan: tuple | None = None) -> torch.Tensor:
     """The stacked q,k,v projection out[M, (NH+2NKV)*D] = x @ w^T with the epilogue of ``qk_norm_rope_append``
     inside the product's kernel: the query columns of out hold the normed, rotated queries, keys and values go
     to their pages (the key and value columns of out are not written).  ``gemm_tc_qkv_takes`` says when."""
     _need_cuda(x, w, out, k_pages, v_pages)
     M, K = x.shape
     N = w.shape[0]
-    swap, bn, splits, stages = gemm_tc_plan(M, N, K, bn_multiple=head_dim if M > 128 else 16)
-    cluster = 1 if swap and 1 < splits <= 8 else 0
+    plan = plan or gemm_tc_plan(M, N, K, bn_multiple=head_dim if M > 128 else 16)
+    swap, bn, splits, stages = plan[:4]
+    cluster = plan[4] if len(plan) > 4 else (1 if swap and 1 < splits <= 8 else 0)
     tiles = (-(-N // 128) * -(-M // bn)) if swap else (-(-M // 128) * -(-N // bn))
     ws, cnt, status = _gemm_buffers(x.device, tiles * splits * bn * 128 if splits > 1 else 0, tiles)
     _check(library().acv_gemm_tc_qkv(

@@ -21,9 +21,9 @@ import numpy as np
 
 from . import ops
 
-MARKS = 8
+MARKS = 12
 RECORD = np.dtype([("t0", "<u8"), ("t1", "<u8"), ("kernel", "<i4"), ("block", "<i4"), ("grid", "<i4"), ("smid", "<i4"),
-                   ("mark", "<u8", (MARKS,))])
+                   ("mark", "<u8", (MARKS,)), ("cycles", "<u8")])
 FILES = ("gemm_tc", "elementwise", "sampling", "attention_decode", "attention_tc", "qk_rope_append")
 NAMES = {1: "gemm", 2: "norm", 3: "rope_append", 4: "attn_decode", 5: "attn_prompt", 6: "attn_chunk", 7: "embed",
          8: "argmax", 9: "swiglu"}

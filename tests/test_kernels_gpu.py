@@ -422,7 +422,8 @@ def test_gemm_tc_at_the_real_vocabulary(ops, M, K):
 
 
 @pytest.mark.parametrize("plan", [(1, 16, 1), (1, 16, 4), (1, 32, 3), (1, 64, 2), (1, 128, 5), (0, 64, 1), (0, 128, 2),
-                                  (0, 256, 1), (0, 256, 3), (0, 160, 1), (0, 192, 1), (0, 224, 1), (0, 160, 2)])
+                                  (0, 256, 1), (0, 256, 3), (0, 160, 1), (0, 192, 1), (0, 224, 1), (0, 160, 2),
+                                  (0, 256, 1, 6, 4), (0, 256, 1, 2, 4)])          # the last two: pairs of CTAs on 256 x 256
 def test_gemm_tc_every_tile_shape_and_split(ops, plan):
     M, N, K = (50 if plan[0] else 300), 700, 1160
     if plan[0] and M > plan[1]:
@@ -437,12 +438,13 @@ def test_gemm_tc_every_tile_shape_and_split(ops, plan):
         torch.testing.assert_close(out.double(), x.double() @ w.double().T, **t)
 
 
-@pytest.mark.parametrize("M,plan", [(8, None), (8, (1, 16, 4, 4, 0)), (300, None)])
+@pytest.mark.parametrize("M,plan", [(8, None), (8, (1, 16, 4, 4, 0)), (300, None), (300, (0, 256, 1, 4, 4))])
 def test_gemm_tc_wait_that_runs_out_leaves_its_code_and_returns(ops, M, plan):
     """A bounded wait made to run out, without a fault: the product is told to poll each barrier a few thousand
     times at most and never to load one k-block.  It has to give up, free what it holds and return, with the
     wait's code in the status word; after the counters are cleared the next launch of the same shape is right.
-    M = 8: swapped roles, the splits of K as a cluster / through the work space; M = 300: tokens on the rows."""
+    M = 8: swapped roles, the splits of K as a cluster / through the work space; M = 300: tokens on the rows, a CTA
+    or a pair of CTAs to a tile (in a pair both CTAs' waits run out, each by itself)."""
     N, K = 512, 4096
     x = rnd(M, K, dtype=torch.bfloat16, seed=190)
     w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=191)
@@ -482,7 +484,7 @@ def test_gemm_tc_rows_do_not_depend_on_the_batch(ops):
     assert torch.equal(whole[3:4], one)
 
 
-@pytest.mark.parametrize("plan", [None, (1, 16, 1), (1, 16, 3), (1, 64, 2), (0, 256, 1), (0, 128, 2), (0, 64, 1)])
+@pytest.mark.parametrize("plan", [None, (1, 16, 1), (1, 16, 3), (1, 64, 2), (0, 256, 1), (0, 128, 2), (0, 64, 1), (0, 256, 1, 6, 4)])
 @pytest.mark.parametrize("M,I,K", [(8, 352, 512), (40, 1000, 264), (300, 520, 1160)])
 def test_gemm_tc_fused_swiglu(ops, plan, M, I, K):
     """The paired epilogue equals the stacked product followed by the SwiGLU kernel, bit for bit."""
@@ -501,6 +503,24 @@ def test_gemm_tc_fused_swiglu(ops, plan, M, I, K):
                                                torch.zeros(M, I, device="cuda", dtype=torch.bfloat16)), **tol(torch.bfloat16))
 
 
+@pytest.mark.parametrize("M,N,K", [(2100, 2304, 200), (5000, 520, 136), (257, 256, 64), (256, 4104, 72), (9000, 264, 4096)])
+def test_gemm_tc_pairs_of_ctas(ops, M, N, K):
+    """Tiles of 256 x 256 on pairs of CTAs (tcgen05 cta_group::2): more tiles than pairs (a pair walks several, the
+    accumulator buffers alternate), groups of tile rows of which the last is short, edges that fill no tile, one
+    k-block and many; and the plan picks this form by itself for a prompt's shapes."""
+    x = rnd(M, K, dtype=torch.bfloat16, seed=196)
+    w = rnd(N, K, dtype=torch.bfloat16, scale=0.05, seed=197)
+    want = x.double() @ w.double().T
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.full((M, N), 3.0, device="cuda", dtype=out_dtype)
+        ops.gemm_tc(x, w, out, (0, 256, 1, 6, ops.GEMM_PAIR), static_weights=out_dtype == torch.bfloat16)
+        assert ops.gemm_status() == 0
+        t = dict(rtol=1e-4, atol=1e-4) if out_dtype == torch.float32 else tol(torch.bfloat16)
+        torch.testing.assert_close(out.double(), want, **t)
+    assert ops.gemm_tc_plan(2048, 4096, 4096, 148)[4:] == (ops.GEMM_PAIR,)
+    assert len(ops.gemm_tc_plan(1056, 34816, 5120, 148)) == 4       # 1280 rows of pair tiles for 1056 tokens: not worth it
+
+
 def test_tensor_core_attention_growing_scores(ops):
     """Keys whose scores grow along a long prompt: the running maximum moves in every tile of keys, far enough
     that the rows of O are rescaled again and again (and by different amounts in the rows of one warp)."""
@@ -513,8 +533,8 @@ def test_tensor_core_attention_growing_scores(ops):
                                           (3, 1, 128, 32, 136),
                                           # many tokens: tokens on the tensor-memory lanes, whole heads inside a thread's row
                                           (8, 2, 128, 300, 512), (6, 2, 64, 129, 264), (5, 1, 64, 700, 128), (3, 1, 128, 257, 136)])
-@pytest.mark.parametrize("normed,rotated", [(True, True), (False, True), (True, False)])
-def test_gemm_tc_qkv_epilogue(ops, NH, NKV, D, T, K, normed, rotated):
+@pytest.mark.parametrize("normed,rotated,pair", [(True, True, False), (False, True, False), (True, False, False), (True, True, True)])
+def test_gemm_tc_qkv_epilogue(ops, NH, NKV, D, T, K, normed, rotated, pair):
     """The stacked projection with norm, rotation and append in its own kernel against the projection followed by the
     rotation kernel: the same queries, and the same keys and values in the same pages (the sums of squares are added
     in another order, so a rounding may move here and there)."""
@@ -537,12 +557,15 @@ def test_gemm_tc_qkv_epilogue(ops, NH, NKV, D, T, K, normed, rotated):
         table[int(seq[2]), int(pos[2]) // page] = -1
     if not ops.gemm_tc_qkv_takes(x, w, D, cos_sin, torch.empty(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)):
         pytest.skip("no fused form for this plan")
+    if pair and T <= 128:
+        pytest.skip("pairs of CTAs serve the tokens-on-rows form")
+    plan = (0, 256, 1, 6, ops.GEMM_PAIR) if pair else None
     kp1 = torch.zeros(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)
     vp1, kp2, vp2 = torch.zeros_like(kp1), torch.zeros_like(kp1), torch.zeros_like(kp1)
     want = ops.gemm_tc(x, w, torch.zeros(T, N, device="cuda", dtype=torch.bfloat16))
     ops.qk_norm_rope_append(want, NH, NKV, D, qw, kw, 1e-6, cos_sin, pos, seq, table, kp1, vp1)
     got = torch.zeros(T, N, device="cuda", dtype=torch.bfloat16)
-    ops.gemm_tc_qkv(x, w, got, NH, NKV, D, qw, kw, 1e-6, cos_sin, pos, seq, table, kp2, vp2)
+    ops.gemm_tc_qkv(x, w, got, NH, NKV, D, qw, kw, 1e-6, cos_sin, pos, seq, table, kp2, vp2, plan=plan)
     assert ops.gemm_status() == 0
     q1, q2 = want[:, :NH * D], got[:, :NH * D]
     torch.testing.assert_close(q2, q1, **tol(torch.bfloat16))
