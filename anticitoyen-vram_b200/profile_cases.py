@@ -93,6 +93,40 @@ def tile_width_case(reps: int) -> dict:
     return out
 
 
+def pair_case(reps: int) -> dict:
+    """The tokens-on-rows product with a CTA to a tile of 128 x 256 and with a pair of CTAs to a tile of 256 x 256
+    (tcgen05 ``cta_group::2``), launch by launch in turn so that both see the same clocks: the shapes of a prompt of
+    2048 and of 8192 tokens (8B sizes) and of a 1024-token portion beside 32 decoding requests (14B sizes)."""
+    out = {}
+    single, pair = (0, 256, 1, 8), (0, 256, 1, 6, ops.GEMM_PAIR)
+    for M, N, K, swiglu in ((2048, 6144, 4096, False), (2048, 4096, 4096, False), (2048, 24576, 4096, True), (2048, 4096, 12288, False),
+                            (8192, 6144, 4096, False), (8192, 24576, 4096, True), (8192, 4096, 12288, False),
+                            (1056, 5120, 5120, False), (1056, 34816, 5120, True), (512, 4096, 12288, False)):
+        copies = max(2, int(300e6 // (N * K * 2)) + 1)
+        ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+        res = torch.empty(M, N // 2 if swiglu else N, device="cuda", dtype=torch.bfloat16)
+        times = {single: [], pair: []}
+        n = 0
+        for it in range(3 + 2 * reps):
+            for plan in (single, pair):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                ops.gemm_tc(x, ws[n % copies], res, plan, swiglu_pairs=swiglu, static_weights=True)
+                b.record()
+                n += 1
+                if it >= 3:
+                    times[plan].append((a, b))
+        torch.cuda.synchronize()
+        med = {plan: sorted(a.elapsed_time(b) for a, b in ev)[len(ev) // 2] * 1e3 for plan, ev in times.items()}
+        chosen = ops.gemm_tc_plan(M, N, K)
+        print(f"gemm_tc M={M} N={N} K={K}{' SiLU(gate)*up' if swiglu else ''}: a CTA to a tile {med[single]:.1f} us "
+              f"({2 * M * N * K / med[single] / 1e6:.0f} TFLOP/s), a pair {med[pair]:.1f} us ({2 * M * N * K / med[pair] / 1e6:.0f} TFLOP/s); "
+              f"the plan takes {'the pair' if len(chosen) > 4 and chosen[4] == ops.GEMM_PAIR else f'tiles of {chosen[1]} columns'}")
+        out[f"{M}x{N}x{K}"] = {"single_us": med[single], "pair_us": med[pair]}
+    return out
+
+
 def sample_case(rows: int, vocab: int, reps: int) -> dict:
     """Temperature 0.7 and top-p 0.9 over rows of a real vocabulary (a cluster of CTAs shares a row)."""
     logits = [torch.randn(rows, vocab, device="cuda") * 3.0 for _ in range(4)]
@@ -156,7 +190,9 @@ CASES = {
     "attention_prefill": lambda r: attention_case(1, 2048, 2048, r),
     "attention_prefill_8k": lambda r: attention_case(1, 2048, 8192, r),
     "attention_prefill_mma_sync": lambda r: attention_case(1, 2048, 2048, r, legacy=True),
+    "gemm_prefill_down": lambda r: gemm_case(2048, 4096, 12288, r),
     "gemm_tile_widths": tile_width_case,
+    "gemm_pairs": pair_case,
     "sample": lambda r: sample_case(8, 151936, r),
     "decode_layer_fused": lambda r: decode_layer_case(8, 2048, r, True),
     "decode_layer_separate": lambda r: decode_layer_case(8, 2048, r, False),
