@@ -1,23 +1,28 @@
 // Paged causal flash attention for portions of prompts on the fifth-generation tensor cores.
 //
 // One CTA per (tile of 128 query tokens of one request, pair of query heads that share a key/value
-// head).  The two heads see the same keys, the same values and the same mask, so a tile of keys is
-// loaded once for both, and while the softmax of one head runs, the tensor core works for the other:
-//   S_h = Q_h K^T   tcgen05.mma, Q and K in shared memory (K-major, 128-byte swizzle), S_h in tensor memory
-//   softmax         four warps per head, one query row per thread: the row of S_h from tensor memory
-//                   (tcgen05.ld), mask by absolute position, running maximum and sum in float; P_h goes
-//                   back into the columns of S_h as packed bfloat16 (tcgen05.st), the A operand of the next
-//                   product; the row of O_h in tensor memory is rescaled only when its maximum has grown
-//                   by more than 2^8 since the last rescale (the sum and O carry the same stale maximum,
-//                   so the quotient at the end is unchanged)
-//   O_h += P_h V    tcgen05.mma with A from tensor memory, V in shared memory as it lies in the pages
-//                   ([keys][D], the MN-major operand)
-// The MMA warp issues, per tile t of keys: P0.V, then S0 of tile t+1, P1.V, S1 of tile t+1; products of
-// one thread run in the order of issue, so the next S_h overwrites P_h only after P_h.V has read it, and
-// a finished S_h(t+1) tells the softmax warps that O_h is at rest.
+// head).  The two heads see the same keys, the same values and the same mask, so a tile of 128 keys is
+// loaded once for both.  Each head works through a tile of keys in two halves of 64, a and b:
+//   S_x = Q_h K_x^T  tcgen05.mma, Q and K in shared memory (K-major, 128-byte swizzle), S_x in 64 columns of
+//                    tensor memory of its own
+//   softmax          four warps per head, one query row per thread: the row of S_x from tensor memory
+//                    (tcgen05.ld), mask by absolute position, running maximum and sum in float; P_x goes
+//                    back into the first columns of S_x as packed bfloat16 (tcgen05.st), the A operand of the
+//                    next product; the row of O_h in tensor memory is rescaled only when its maximum has grown
+//                    by more than 2^8 since the last rescale (the sum and O carry the same stale maximum,
+//                    so the quotient at the end is unchanged)
+//   O_h += P_x V_x   tcgen05.mma with A from tensor memory, V in shared memory as it lies in the pages
+//                    ([keys][D], the MN-major operand)
+// Each head has an issuing thread of its own.  When the softmax hands over P_x it issues P_x.V_x and then S_x of the
+// next tile of keys; products of one thread run in the order of issue, so the next S_x overwrites P_x only after
+// P_x.V_x has read it.  While the softmax warps work on one half, the scores of the other half are already there or on
+// their way: they do not wait for the tensor core between halves, and the tensor core has one head's products to
+// run while the other head's warps take their exponentials.  A row's O is rescaled only while no product on values
+// of its head is in flight (the issuing thread commits each to a barrier that the softmax warps wait on then).
 // Keys and values come straight from the cache pages by TMA, one box per page and 64 columns, two
-// tiles in flight; Q comes by TMA from the step's projection buffer.  Warp 0 issues the loads, warp 1
-// the MMAs, warps 2..5 are head 0's softmax and epilogue, warps 6..9 head 1's.  A group with an odd
+// tiles in flight, keys and values in rings of their own; Q comes by TMA from the step's projection buffer.  Warp 0
+// issues the loads, warps 1 and 10 the MMAs of head 0 and head 1, warps 2..5 are head 0's softmax and epilogue,
+// warps 6..9 head 1's.  A group with an odd
 // number of query heads leaves the second half of its last CTA idle.  The mask follows absolute positions
 // (key j is seen by the query at position p iff j <= p, and j > p - window when a window is set), so a
 // portion may start anywhere in its prompt (acvram/engine/layers.py:1020-1041); the reference runs this
@@ -26,11 +31,12 @@
 #include "tc_ptx.cuh"
 #include "tensor_map.h"
 
-#define AT_THREADS 320
+#define AT_THREADS 352
 #define AT_BM 128
 #define AT_BN 128
 #define AT_LOG2E 1.4426950408889634f
 #define AT_ATOM (128 * 128)          // bytes of one swizzle atom column: 128 rows of 128 bytes
+#define AT_HALF 64                   // keys of a half tile
 #define AT_LAZY 8.0f                 // a row's maximum may lag by this much (log2 units) before O is rescaled
 
 struct AttnTcParams {
@@ -54,25 +60,37 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
     constexpr int DA = D / 64;                         // 64-element column atoms of a head
     constexpr int Q_BYTES = DA * AT_ATOM, KV_BYTES = DA * AT_ATOM;
-    constexpr int TMEM_COLS = 512;                     // S_h: columns [128h, 128h + 128), O_h: [256 + 128h, 256 + 128h + D)
+    constexpr int TMEM_COLS = 512;                     // S_h,x: columns [128h + 64x, + 64), O_h: [256 + 128h, 256 + 128h + D)
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = smem_raw + ((1024u - (gt_smem(smem_raw) & 1023u)) & 1023u);
     const uint32_t q_s = gt_smem(base), kv_s = q_s + 2 * Q_BYTES;   // q_s: [2 heads]; kv_s: [2 stages][K, V]
-    uint64_t* bars = (uint64_t*)(base + 2 * Q_BYTES + 4 * KV_BYTES);
+    uint64_t* bars = (uint64_t*)(base + 2 * Q_BYTES + 4 * KV_BYTES);       // 21 barriers
     const uint32_t bar0 = gt_smem(bars);
-    const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_free = bar0 + 24, s_full = bar0 + 40, p_full = bar0 + 56,
-                   o_full = bar0 + 72;
+    // keys and values have rings of their own: a tile's keys are free once both heads' scores are issued, long before
+    // its values are (after both heads' second P.V)
+    const uint32_t q_full = bar0, k_full = bar0 + 8, k_free = bar0 + 24, v_full = bar0 + 40, v_free = bar0 + 56,
+                   s_full = bar0 + 72 /*[head][half]*/, p_full = bar0 + 104 /*[head][half]*/, o_full = bar0 + 136 /*[head]*/,
+                   pv_done = bar0 + 152 /*[head]*/;
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ACV_TL(TL_ATTN_TC, 64);
+    // the CTA's heads, from its number alone (the barriers' counts depend on it)
+    const int n_rep = p.NH / p.NKV, pairs = (n_rep + 1) >> 1;
+    const int tile = blockIdx.x / (p.NKV * pairs), hp = blockIdx.x - tile * (p.NKV * pairs);
+    const int kvh = hp / pairs, pair = hp - kvh * pairs;
+    const int h0 = kvh * n_rep + 2 * pair;                  // the CTA's first head; the second is h0 + 1
+    const int n_heads = 2 * pair + 1 < n_rep ? 2 : 1;
     if (threadIdx.x == 0) {
         abort_s = 0;
         mbar_init(q_full, 1);
-        for (int s = 0; s < 2; ++s) { mbar_init(kv_full + 8 * s, 1); mbar_init(kv_free + 8 * s, 1); }
-        for (int h = 0; h < 2; ++h) { mbar_init(s_full + 8 * h, 1); mbar_init(p_full + 8 * h, 4); }
-        mbar_init(o_full, 1);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(k_full + 8 * s, 1); mbar_init(k_free + 8 * s, n_heads);      // each head's issuing thread frees
+            mbar_init(v_full + 8 * s, 1); mbar_init(v_free + 8 * s, n_heads);
+        }
+        for (int i = 0; i < 4; ++i) { mbar_init(s_full + 8 * i, 1); mbar_init(p_full + 8 * i, 4); }
+        for (int h = 0; h < 2; ++h) { mbar_init(o_full + 8 * h, 1); mbar_init(pv_done + 8 * h, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -96,12 +114,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // ---- the tile's geometry (the same in every role)
     // blocks are numbered tile-major: the tile list begins with the longest tiles, and the hardware hands
     // out blocks in the order of their numbers, so every head pair of a long tile starts before a short one
-    const int n_rep = p.NH / p.NKV, pairs = (n_rep + 1) >> 1;
-    const int tile = blockIdx.x / (p.NKV * pairs), hp = blockIdx.x - tile * (p.NKV * pairs);
     const int seq = p.tile_seq[tile], q0 = p.tile_q0[tile];
-    const int kvh = hp / pairs, pair = hp - kvh * pairs;
-    const int h0 = kvh * n_rep + 2 * pair;                  // the CTA's first head; the second is h0 + 1
-    const int n_heads = 2 * pair + 1 < n_rep ? 2 : 1;
     const int tok0 = p.cu_q[seq] + q0;
     const int q_len = p.cu_q[seq + 1] - p.cu_q[seq];
     const int rows = min(AT_BM, q_len - q0);
@@ -125,76 +138,85 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         const int ps = p.page_size, pages_per_tile = AT_BN >> p.page_shift;
         for (int t = 0; t < n_tiles; ++t) {
             const int s = t & 1;
-            int go = 1;
-            if (lane == 0) {
-                if (abort_s) go = 0;
-                else if (t >= 2 && !mbar_wait(kv_free + 8 * s, ((t >> 1) - 1) & 1, &abort_s)) {
-                    abort_s = 1; atomicExch(p.status, 11); go = 0;
-                }
-            }
-            if (!__shfl_sync(0xffffffffu, go, 0)) break;
             // pages of this tile that hold keys some row reads; the others are skipped (their rows are masked)
             const int j = j_first + t * AT_BN + lane * ps;
             int pg = -1;
             if (lane < pages_per_tile && j <= hi && j + ps - 1 >= lo) pg = bt[j >> p.page_shift];
             const bool take = pg >= 0 && pg < p.num_pages;
             const uint32_t taken = __ballot_sync(0xffffffffu, take);
-            if (lane == 0) mbar_expect_tx(kv_full + 8 * s, __popc(taken) * 2u * DA * ps * 128u);
-            __syncwarp();
-            if (take) {
-                const uint32_t k_dst = kv_s + s * 2 * KV_BYTES + lane * ps * 128, v_dst = k_dst + KV_BYTES;
-                const int row = (pg * p.NKV + kvh) * ps;
+            const uint32_t k_dst = kv_s + s * 2 * KV_BYTES + lane * ps * 128, v_dst = k_dst + KV_BYTES;
+            const int row = (pg * p.NKV + kvh) * ps;
+            bool stop = false;
+            for (int kv = 0; kv < 2 && !stop; ++kv) {           // the keys, then the values
+                const uint32_t full = (kv ? v_full : k_full) + 8 * s, free_bar = (kv ? v_free : k_free) + 8 * s;
+                int go = 1;
+                if (lane == 0) {
+                    if (abort_s) go = 0;
+                    else if (t >= 2 && !mbar_wait(free_bar, ((t >> 1) - 1) & 1, &abort_s)) {
+                        abort_s = 1; atomicExch(p.status, 11); go = 0;
+                    }
+                    if (go) mbar_expect_tx(full, __popc(taken) * (uint32_t)DA * ps * 128u);
+                }
+                if (!__shfl_sync(0xffffffffu, go, 0)) { stop = true; break; }
+                if (take) {
 #pragma unroll
-                for (int a = 0; a < DA; ++a) {
-                    tma_load_2d(k_dst + a * AT_ATOM, &map_k, kv_full + 8 * s, a * 64, row);
-                    tma_load_2d(v_dst + a * AT_ATOM, &map_v, kv_full + 8 * s, a * 64, row);
+                    for (int a = 0; a < DA; ++a)
+                        tma_load_2d((kv ? v_dst : k_dst) + a * AT_ATOM, kv ? &map_v : &map_k, full, a * 64, row);
                 }
             }
+            if (stop) break;
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            const uint32_t idesc_s = umma_idesc(AT_BN, 128, 0), idesc_o = umma_idesc(D, 128, 1);
-            // S_h = Q_h K^T over the head dimension, for the tile of keys in stage s
-            auto issue_s = [&](int h, int s) {
-                const uint32_t k_lo = umma_desc_lo(kv_s + s * 2 * KV_BYTES), q_lo = umma_desc_lo(q_s + h * Q_BYTES);
+    } else if (warp == 1 || warp == 10) {
+        // ------------------------------------------------------------------ MMA issuers: warp 1 for head 0, warp 10 for head 1
+        const int h = warp == 1 ? 0 : 1;
+        if (lane == 0 && h < n_heads) {
+            const uint32_t idesc_s = umma_idesc(AT_HALF, 128, 0), idesc_o = umma_idesc(D, 128, 1);
+            const uint32_t q_lo = umma_desc_lo(q_s + h * Q_BYTES);
+            // S_x = Q_h K_x^T over the head dimension, for half x of the tile of keys in stage s (the half's 64 key rows
+            // lie 64 x 128 bytes into each column atom)
+            auto issue_s = [&](int x, int s) {
+                const uint32_t k_lo = umma_desc_lo(kv_s + s * 2 * KV_BYTES + x * (AT_HALF * 128));
 #pragma unroll
                 for (int kk = 0; kk < D / 16; ++kk) {
                     const uint32_t off = ((kk >> 2) * AT_ATOM + (kk & 3) * 32) >> 4;
-                    tc_mma_bf16_h(tmem + h * 128, q_lo + off, k_lo + off, idesc_s, kk > 0 ? 1u : 0u);
+                    tc_mma_bf16_h(tmem + h * 128 + x * AT_HALF, q_lo + off, k_lo + off, idesc_s, kk > 0 ? 1u : 0u);
                 }
-                tc_commit(s_full + 8 * h);
+                tc_commit(s_full + 8 * (2 * h + x));
             };
             bool ok = mbar_wait(q_full, 0, &abort_s);
             if (!ok) { abort_s = 1; atomicExch(p.status, 12); }
-            if (ok && !mbar_wait(kv_full, 0, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 13); }
+            if (ok && !mbar_wait(k_full, 0, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 13); }
             if (ok) {
                 tc_fence_after();
-                for (int h = 0; h < n_heads; ++h) issue_s(h, 0);
+                issue_s(0, 0);
+                issue_s(1, 0);
+                tc_commit(k_free);                  // this head has read the first tile's keys
             }
             for (int t = 0; t < n_tiles && ok && !abort_s; ++t) {
                 const int s = t & 1;
-                const uint32_t v_addr = kv_s + s * 2 * KV_BYTES + KV_BYTES;
-                for (int h = 0; h < n_heads && ok; ++h) {
-                    // O_h += P_h V over the tile's keys, once head h's softmax has written P_h
-                    if (!mbar_wait(p_full + 8 * h, t & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 14); break; }
+                const uint32_t v_lo = umma_desc_lo(kv_s + s * 2 * KV_BYTES + KV_BYTES, AT_ATOM);
+                for (int x = 0; x < 2 && ok; ++x) {
+                    // O_h += P_x V_x over the half's keys, once the softmax has written P_x
+                    if (!mbar_wait(p_full + 8 * (2 * h + x), t & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 14); break; }
+                    if (x == 0 && !mbar_wait(v_full + 8 * s, (t >> 1) & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 13); break; }
                     tc_fence_after();
-                    const uint32_t v_lo = umma_desc_lo(v_addr, AT_ATOM);
 #pragma unroll
-                    for (int kk = 0; kk < AT_BN / 16; ++kk)
-                        tc_mma_bf16_ts_h(tmem + 256 + h * 128, tmem + h * 128 + kk * 8, v_lo + kk * (2048 >> 4), idesc_o,
-                                         (t > 0 || kk > 0) ? 1u : 0u);
-                    if (h == n_heads - 1) tc_commit(kv_free + 8 * s);      // this stage's keys and values are read
+                    for (int k4 = 0; k4 < AT_HALF / 16; ++k4)
+                        tc_mma_bf16_ts_h(tmem + 256 + h * 128, tmem + h * 128 + x * AT_HALF + k4 * 8,
+                                         v_lo + (x * (AT_HALF / 16) + k4) * (2048 >> 4), idesc_o, (t > 0 || x > 0 || k4 > 0) ? 1u : 0u);
+                    tc_commit(pv_done + 8 * h);                     // O_h is at rest again when this arrives
+                    if (x == 1) tc_commit(v_free + 8 * s);         // this head has read the stage's values
                     if (t + 1 < n_tiles) {
-                        if (h == 0) {
-                            if (!mbar_wait(kv_full + 8 * (s ^ 1), ((t + 1) >> 1) & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 13); break; }
+                        if (x == 0) {
+                            if (!mbar_wait(k_full + 8 * (s ^ 1), ((t + 1) >> 1) & 1, &abort_s)) { ok = false; abort_s = 1; atomicExch(p.status, 13); break; }
                             tc_fence_after();
                         }
-                        issue_s(h, s ^ 1);
+                        issue_s(x, s ^ 1);
+                        if (x == 1) tc_commit(k_free + 8 * (s ^ 1));
                     }
                 }
             }
-            tc_commit(o_full);
+            tc_commit(o_full + 8 * h);
         }
     } else if (((warp - 2) >> 2) < n_heads) {
         // ------------------------------------------------------------------ softmax and epilogue of one head
@@ -208,34 +230,36 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
         float m_run = -INFINITY, l_run = 0.f;
         bool failed = false;
 #ifdef ACV_TIMELINE
-        unsigned long long tl_acc[7] = {0, 0, 0, 0, 0, 0, 0}, tl_t = acv_tl_now();
+        unsigned long long tl_acc[5] = {0, 0, 0, 0, 0}, tl_t = acv_tl_now();
 #define TL_PHASE(i) do { const unsigned long long n_ = acv_tl_now(); tl_acc[i] += n_ - tl_t; tl_t = n_; } while (0)
 #else
 #define TL_PHASE(i)
 #endif
-        for (int t = 0; t < n_tiles && !abort_s; ++t) {
-            if (!mbar_wait(s_full + 8 * hs, t & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 15); failed = true; break; }
+        for (int tx = 0; tx < 2 * n_tiles && !abort_s; ++tx) {
+            const int t = tx >> 1, x = tx & 1;                  // tile of keys and its half
+            if (!mbar_wait(s_full + 8 * (2 * hs + x), t & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 15); failed = true; break; }
             tc_fence_after();
             TL_PHASE(0);
-            const int j0 = j_first + t * AT_BN;
-            const bool need_mask = j0 + AT_BN - 1 > pos0 || (p.window > 0 && j0 <= pos0 + AT_BM - 1 - p.window);
-            // first pass: the row's maximum
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            const uint32_t tmem_sx = tmem_s + x * AT_HALF;
+            const int j0 = j_first + t * AT_BN + x * AT_HALF;
+            const bool need_mask = j0 + AT_HALF - 1 > pos0 || (p.window > 0 && j0 <= pos0 + AT_BM - 1 - p.window);
+            uint32_t ra[32], rb[32];
+            auto masked = [&](uint32_t (&raw)[32], int c0) {
 #pragma unroll
-            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
-                uint32_t raw[32];
-                tc_ld32(tmem_s + c0, raw);
-                if (need_mask) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int j = j0 + c0 + c;
-                        const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
-                        raw[c] = seen ? raw[c] : 0xff800000u;       // -inf
-                    }
+                for (int c = 0; c < 32; ++c) {
+                    const int j = j0 + c0 + c;
+                    const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
+                    raw[c] = seen ? raw[c] : 0xff800000u;       // -inf
                 }
+            };
+            // first pass: the row's maximum over the half's 64 scores
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            tc_ld32_nowait(tmem_sx, ra);
+            tc_ld32_nowait(tmem_sx + 32, rb);
+            tc_wait_ld();
+            if (need_mask) { masked(ra, 0); masked(rb, 32); }
 #pragma unroll
-                for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(raw[c]));
-            }
+            for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], fmaxf(__uint_as_float(ra[c]), __uint_as_float(rb[c])));
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             TL_PHASE(1);
             // the maximum in use moves only when the true one has run ahead of it by more than AT_LAZY
@@ -246,8 +270,12 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
                 m_run = m_true;
             }
             const float m_use = m_run == -INFINITY ? 0.f : m_run;
-            // rows whose maximum moved rescale what O holds so far (tensor-memory access is warp-wide)
-            if (t > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+            // rows whose maximum moved rescale what O holds so far (tensor-memory access is warp-wide).  O has to be at
+            // rest: the product on values issued last for this head, number tx - 1, must be complete (the one before it
+            // is, since this half's scores were issued after it, and the next waits for this half's P)
+            if (tx > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                if (!mbar_wait(pv_done + 8 * hs, (tx - 1) & 1, &abort_s)) { abort_s = 1; atomicExch(p.status, 17); failed = true; break; }
+                tc_fence_after();
 #pragma unroll
                 for (int c0 = 0; c0 < D; c0 += 32) {
                     uint32_t o[32];
@@ -259,50 +287,38 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
             }
             l_run *= alpha;
             TL_PHASE(2);
-            // second pass: P = 2^(s * scale - m) as packed bfloat16 into the first 64 columns of S (the
-            // columns it overwrites have been read: chunk c of P covers columns [16c, 16c + 16) of [0, 32c + 32))
-#pragma unroll
-            for (int c0 = 0; c0 < AT_BN; c0 += 32) {
-                uint32_t raw[32];
-                tc_ld32(tmem_s + c0, raw);
-                TL_PHASE(5);
-                if (need_mask) {
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) {
-                        const int j = j0 + c0 + c;
-                        const bool seen = j <= pos && (p.window <= 0 || j > pos - p.window);
-                        raw[c] = seen ? raw[c] : 0xff800000u;       // -inf
-                    }
-                }
-                float e[32];
+            // second pass, on the scores still in registers: P = 2^(s * scale - m) as packed bfloat16 into the first 32
+            // columns of S_x
+            auto exp_of = [&](uint32_t (&raw)[32], int c0) {
                 float part[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    e[c] = tc_exp2(fmaf(__uint_as_float(raw[c]), scale_log2, -m_use));
-                    part[c & 3] += e[c];
-                }
-                l_run += (part[0] + part[1]) + (part[2] + part[3]);
                 uint32_t pk[16];
 #pragma unroll
-                for (int c = 0; c < 16; ++c) pk[c] = pack_bf16x2(e[2 * c], e[2 * c + 1]);
-                TL_PHASE(3);
-                tc_st16_nowait(tmem_s + (c0 >> 1), pk);
-                TL_PHASE(6);
-            }
+                for (int c = 0; c < 32; c += 2) {
+                    const float e0 = tc_exp2(fmaf(__uint_as_float(raw[c]), scale_log2, -m_use));
+                    const float e1 = tc_exp2(fmaf(__uint_as_float(raw[c + 1]), scale_log2, -m_use));
+                    part[c & 3] += e0;
+                    part[(c + 1) & 3] += e1;
+                    pk[c >> 1] = pack_bf16x2(e0, e1);
+                }
+                l_run += (part[0] + part[1]) + (part[2] + part[3]);
+                tc_st16_nowait(tmem_sx + (c0 >> 1), pk);
+            };
+            exp_of(ra, 0);
+            exp_of(rb, 32);
+            TL_PHASE(3);
             tc_wait_st();
-            TL_PHASE(6);
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(p_full + 8 * hs);
+            if (lane == 0) mbar_arrive(p_full + 8 * (2 * hs + x));
             TL_PHASE(4);
         }
 #ifdef ACV_TIMELINE
         if (threadIdx.x == 64) {
-            for (int i = 0; i < 7; ++i) acv_tl_marks[i] = tl_acc[i];
-            acv_tl_marks[7] = (unsigned long long)n_tiles;
+            for (int i = 0; i < 5; ++i) acv_tl_marks[i] = tl_acc[i];
+            acv_tl_marks[7] = (unsigned long long)(2 * n_tiles);
         }
 #endif
-        if (!failed && !abort_s && mbar_wait(o_full, 0, &abort_s)) {
+        if (!failed && !abort_s && mbar_wait(o_full + 8 * hs, 0, &abort_s)) {
             tc_fence_after();
             const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
             bf16* dst = p.out + (size_t)(tok0 + r) * p.out_stride + (size_t)(h0 + hs) * D;
@@ -339,7 +355,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
 template <int D>
 static int launch_attn_tc(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const AttnTcParams& p,
                           int n_tiles, cudaStream_t stream) {
-    constexpr int SMEM = 2 * (D / 64) * AT_ATOM /*Q of two heads*/ + 4 * (D / 64) * AT_ATOM /*K,V x2*/ + 1024 + 128;
+    constexpr int SMEM = 2 * (D / 64) * AT_ATOM /*Q of two heads*/ + 4 * (D / 64) * AT_ATOM /*K,V x2*/ + 1024 + 256;
     static AcvSmemConfig smem_config;          // per kernel instance and device
     if (int rc = acv_ensure_smem(smem_config, attn_tc_kernel<D>, SMEM)) return rc;
     const int n_rep = p.NH / p.NKV;

@@ -30,8 +30,8 @@ NAMES = {1: "gemm", 2: "norm", 3: "rope_append", 4: "attn_decode", 5: "attn_prom
 MARK_NAMES = {1: ("first_full", "last_mma", "acc_done", "part_sent", "cluster_met", "stored", "wait_over"),
               4: ("loop_done",)}
 # the prompt attention's marks are not times but sums: nanoseconds its first softmax warp spent in each phase
-# (marks 0..6) and the number of key tiles it went through (mark 7)
-ATTN_PHASES = ("wait for S", "row maximum", "rescale O", "exponentials + pack", "hand P over", "read S again", "write P")
+# (marks 0..4) and the number of half tiles of 64 keys it went through (mark 7)
+ATTN_PHASES = ("wait for S", "row maximum", "rescale O", "exponentials + pack + write P", "hand P over")
 CAP = 1 << 16
 
 
@@ -115,7 +115,7 @@ def report(rec: np.ndarray, file=sys.stdout) -> None:
     attn = rec[rec["kernel"] == 5]
     if len(attn) and attn["mark"][:, 7].sum() > 0:
         tiles = float(attn["mark"][:, 7].sum())
-        print("\nprompt attention, softmax warps of head 0, mean ns per tile of keys: " +
+        print("\nprompt attention, softmax warps of head 0, mean ns per half tile of 64 keys (timer reads included): " +
               ", ".join(f"{name} {attn['mark'][:, i].sum() / tiles:.0f}" for i, name in enumerate(ATTN_PHASES)), file=file)
     whole = (max(L["end"] for L in Ls) - origin) / 1e3
     print(f"\nstep: {whole:.1f} us from the first CTA's begin to the last CTA's end", file=file)
