@@ -20,6 +20,7 @@
 #include "mma_tiles.cuh"
 
 #define AD_THREADS 128
+#define AD_EARLY_KEYS 0
 #define AD_TILE 64          // split boundaries fall on multiples of this many keys
 #define AD_STAGES 3         // buffers in each warp's ring (2 and 4 measured slower on a B200)
 #define AD_LOG2E 1.4426950408889634f
@@ -44,11 +45,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
 
     ACV_TL(TL_ATTN_DECODE, 0);
     pdl_launch_dependents();
-    pdl_wait();
-    // the splits of one cluster write their partial results into rank 0's shared memory at the end: a CTA may do so
-    // only when it knows that rank 0 has started, which is what the first phase of the cluster's barrier tells it
+    // What follows up to pdl_wait reads only what was written before this step's first kernel began (the step's index
+    // arrays, the block table, keys and values of earlier steps): it runs while the projection before this kernel still
+    // does.  The step's own query and its newest key and value are that projection's output and wait for it.
     const bool in_cluster = cluster_merge && n_splits > 1;
-    if (in_cluster) cluster_arrive();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int item = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tok = dec_tokens[item], seq = dec_seqs[item];
@@ -61,14 +61,6 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     const int beg = lo + split * chunk;
     const int end = min(beg + chunk, p + 1);
     const int n_tiles = beg < end ? (end - beg + AD_TILE - 1) / AD_TILE : 0;   // > 0: this split has keys
-
-    // ---- queries of the group into shared memory (rows >= n_rep are zero)
-    for (int id = tid; id < 16 * CH; id += AD_THREADS) {
-        const int r = id / CH, c = id % CH;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * n_rep + r) * D + c * 8);
-        *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
-    }
 
     // the block-table entries of this CTA's keys, read once (a tile's copies then wait for no lookup)
     const int first_pg = page_shift >= 0 ? beg >> page_shift : beg / page_size;
@@ -132,11 +124,38 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         }
     };
 
+    // The first tiles of the ring could go now as far as they hold keys of earlier steps only (the newest key, at p, is
+    // written by the projection before this kernel).  Measured, that gains nothing: the projection is bound by memory
+    // and the early copies take from it what they save here (3.799 against 3.789 ms a step); what pays is that the index
+    // reads above, three dependent round trips, are over when the wait ends (3.739 ms).  AD_EARLY_KEYS keeps the form.
+    int early = 0;
 #pragma unroll
     for (int st = 0; st < AD_STAGES - 1; ++st) {
-        if (st < my_n) load_wt(st, st);
-        cp_async_commit();
+        if (AD_EARLY_KEYS && early == st && st < my_n && beg + (warp + 4 * st) * 16 + 16 <= p) {
+            load_wt(st, st);
+            cp_async_commit();
+            ++early;
+        }
     }
+    pdl_wait();
+    // the splits of one cluster write their partial results into rank 0's shared memory at the end: a CTA may do so
+    // only when it knows that rank 0 has started, which is what the first phase of the cluster's barrier tells it
+    if (in_cluster) cluster_arrive();
+    // ---- queries of the group into shared memory (rows >= n_rep are zero)
+    for (int id = tid; id < 16 * CH; id += AD_THREADS) {
+        const int r = id / CH, c = id % CH;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < n_rep) v = *reinterpret_cast<const uint4*>(q + (size_t)tok * q_stride + (size_t)(kvh * n_rep + r) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+    }
+#pragma unroll
+    for (int st = 0; st < AD_STAGES - 1; ++st) {
+        if (st >= early) {
+            if (st < my_n) load_wt(st, st);
+            cp_async_commit();
+        }
+    }
+    __syncthreads();            // the queries are in shared memory
 
     // ---- query fragments (A operand), kept in registers for the whole kernel
     uint32_t qf[D / 16][4];

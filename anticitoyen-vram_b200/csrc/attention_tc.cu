@@ -109,9 +109,9 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     // only now may the next kernel's CTAs come: one that took tensor memory before this CTA had its own
     // would wait for this grid to end while this CTA waits for its columns
     pdl_launch_dependents();
-    pdl_wait();
 
-    // ---- the tile's geometry (the same in every role)
+    // ---- the tile's geometry (the same in every role), from the step's index arrays, which were written before the
+    // step's first kernel began: read while the projection before this kernel still runs
     // blocks are numbered tile-major: the tile list begins with the longest tiles, and the hardware hands
     // out blocks in the order of their numbers, so every head pair of a long tile starts before a short one
     const int seq = p.tile_seq[tile], q0 = p.tile_q0[tile];
@@ -124,6 +124,7 @@ attn_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant_
     const int j_first = lo & ~(AT_BN - 1);
     const int n_tiles = (hi - j_first) / AT_BN + 1;
     const int* bt = p.block_table + (size_t)(p.bt_rows ? p.bt_rows[seq] : seq) * p.bt_stride;
+    pdl_wait();             // queries, and the keys and values of this step's tokens, are the projection's output
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer

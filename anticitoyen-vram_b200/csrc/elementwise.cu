@@ -81,10 +81,20 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ 
     __shared__ float red[32];
     ACV_TL(TL_NORM, 0);
     pdl_launch_dependents();
+    // the norm's weights were written long before this launch: they are read while the kernel before still runs, so
+    // that one round trip to memory less stands between its end and this kernel's result
+    const int n_chunks = H / E;
+    const float4* w4 = reinterpret_cast<const float4*>(w);
+    float4 wreg[VCH][E / 4];
+#pragma unroll
+    for (int i = 0; i < VCH; ++i) {
+        const int c = threadIdx.x + i * blockDim.x;
+#pragma unroll
+        for (int e4 = 0; e4 < E / 4; ++e4) wreg[i][e4] = c < n_chunks ? w4[c * (E / 4) + e4] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     pdl_wait();
     const int r_out = blockIdx.x;
     const int r_in = rows ? rows[r_out] : r_out;
-    const int n_chunks = H / E;
     uint4* xr = reinterpret_cast<uint4*>(x + (size_t)r_in * H);
     const uint4* dr = delta ? reinterpret_cast<const uint4*>(delta + (size_t)r_in * H) : nullptr;
     float v[VCH][E];
@@ -116,7 +126,6 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ 
     ss = block_sum(ss, red);
     const float rs = rsqrtf(ss / (float)H + eps);
     uint4* o = reinterpret_cast<uint4*>(out + (size_t)r_out * H);
-    const float4* w4 = reinterpret_cast<const float4*>(w);
 #pragma unroll
     for (int i = 0; i < VCH; ++i) {
         const int c = threadIdx.x + i * blockDim.x;
@@ -124,7 +133,7 @@ __global__ void add_rmsnorm_vec_kernel(T* __restrict__ x, const T* __restrict__ 
             T res[E];
 #pragma unroll
             for (int e4 = 0; e4 < E / 4; ++e4) {
-                const float4 ww = w4[c * (E / 4) + e4];
+                const float4 ww = wreg[i][e4];
                 res[e4 * 4 + 0] = from_f32<T>(round_to<T>(v[i][e4 * 4 + 0] * rs) * ww.x);
                 res[e4 * 4 + 1] = from_f32<T>(round_to<T>(v[i][e4 * 4 + 1] * rs) * ww.y);
                 res[e4 * 4 + 2] = from_f32<T>(round_to<T>(v[i][e4 * 4 + 2] * rs) * ww.z);
