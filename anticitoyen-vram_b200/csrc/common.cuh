@@ -170,6 +170,12 @@ __device__ __forceinline__ uint32_t cluster_map(uint32_t local, uint32_t rank) {
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local), "r"(rank));
     return r;
 }
+// a float into another CTA's shared memory whose 4 bytes are counted at an mbarrier of that CTA (both addresses in the
+// cluster's window): the receiver waits on its own barrier for the bytes, no barrier of the whole cluster is needed
+__device__ __forceinline__ void cluster_store_f32_counted(uint32_t addr, float v, uint32_t bar) {
+    asm volatile("st.async.weak.shared::cluster.mbarrier::complete_tx::bytes.b32 [%0], %1, [%2];"
+                 ::"r"(addr), "r"(__float_as_uint(v)), "r"(bar) : "memory");
+}
 __device__ __forceinline__ void cluster_store_f32(uint32_t addr, float v) {
     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }

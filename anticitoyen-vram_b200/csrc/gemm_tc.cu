@@ -184,21 +184,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     // bars: full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2]
     const uint32_t full0 = gt_smem(bars), empty0 = full0 + 8 * STAGES;
     const uint32_t tfull0 = empty0 + 8 * STAGES, tempty0 = tfull0 + 16;
+    const uint32_t part_bar = tempty0 + 16;         // rank 0 of a split's cluster: counts the bytes of the peers' partial tiles
     const uint32_t part0 = gt_smem(tiles) + STAGES * S::STAGE_BYTES + 256;     // [splits-1][BN][128] floats (cluster mode)
     const bool cluster_split = p.cluster && p.splits > 1;
     // the q,k,v epilogue's tables lie behind the partial tiles
     unsigned char* aux = tiles + STAGES * S::STAGE_BYTES + 256 + (cluster_split ? (p.splits - 1) * S::PART_BYTES : 0);
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile int abort_s;
+    __shared__ volatile int never_s;            // stays 0: for the one wait that the CTA's own failure must not cut short
     __shared__ int last_s;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     ACV_TL(TL_GEMM, 64);
     if (threadIdx.x == 0) {
         abort_s = 0;
+        never_s = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tfull0 + 8 * b, 1); mbar_init(tempty0 + 8 * b, 4); }
+        mbar_init(part_bar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // rank 0 of a split's cluster announces the peers' partial tiles at once (their bytes may come before or after)
+        if (cluster_split && cluster_ctarank() == 0) mbar_expect_tx(part_bar, (uint32_t)(p.splits - 1) * S::PART_BYTES);
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(gt_smem(&tmem_base_s)), "r"(S::TMEM_COLS));
@@ -396,19 +402,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 continue;
             }
             if (cluster_split) {
-                // ---- split K inside a cluster: ranks 1.. put their partial tile into rank 0's shared memory;
-                // rank 0 adds them to its own after the cluster barrier below (one item per CTA in this mode)
+                // ---- split K inside a cluster: ranks 1.. put their partial tile into rank 0's shared memory, every store
+                // counted at rank 0's barrier; rank 0 waits there for all the bytes and adds the tiles to its own (one
+                // item per CTA in this mode)
                 const uint32_t rank = cluster_ctarank();
                 cluster_wait();
                 cluster_waited = true;
                 if (rank != 0) {
                     const uint32_t remote = cluster_map(part0, 0) + (rank - 1) * S::PART_BYTES + (wq * 32 + lane) * 4;
+                    const uint32_t remote_bar = cluster_map(part_bar, 0);
 #pragma unroll 1
                     for (int c0 = 0; c0 < BN; c0 += 16) {
                         uint32_t r[16];
                         tc_ld16(taddr + c0, r);
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) cluster_store_f32(remote + (c0 + c) * (GT_BM * 4), __uint_as_float(r[c]));
+                        for (int c = 0; c < 16; ++c)
+                            cluster_store_f32_counted(remote + (c0 + c) * (GT_BM * 4), __uint_as_float(r[c]), remote_bar);
                     }
                 }
                 break;
@@ -456,10 +465,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     if (cluster_split) {
         if (threadIdx.x == 64) ACV_TL_MARK(TL_M_PART_SENT);
-        if (!cluster_waited) cluster_wait();
-        cluster_sync_all();         // every partial tile lies in rank 0's shared memory
+        if (!cluster_waited) cluster_wait();        // every thread that arrived at the cluster's barrier also waits for it
+        // Rank 0 waits for the peers' bytes even when its own part has failed: it must not leave (and give its shared
+        // memory back) while a peer that knows nothing of that may still be storing into it.
+        bool parts_in = true;
+        if (warp >= 2 && cluster_ctarank() == 0 && !mbar_wait(part_bar, 0, &never_s, p.wait_limit)) {
+            abort_s = 1; atomicExch(p.status, 6); parts_in = false;        // the peers' partial tiles did not all come
+        }
         if (threadIdx.x == 64) ACV_TL_MARK(TL_M_CLUSTER_MET);
-        if (warp >= 2 && cluster_ctarank() == 0 && !abort_s) {
+        if (warp >= 2 && cluster_ctarank() == 0 && !abort_s && parts_in) {
             const int wq = warp & 3;
             const int tile = blockIdx.x / p.splits;
             int ta, tb;
