@@ -657,12 +657,18 @@ def attention_work(q_lens, kv_lens, cu_q) -> tuple[dict, dict]:
     import numpy as np
     ql = np.asarray(q_lens, dtype=np.int32)
     dec = np.nonzero(ql == 1)[0].astype(np.int32)
-    tile_seq, tile_q0 = [], []
+    tile_seq, tile_q0, tile_keys = [], [], []
     for i in np.nonzero(ql > 1)[0]:
-        starts_i = np.arange(0, q_lens[i], QUERY_TILE, dtype=np.int32)[::-1]
+        starts_i = np.arange(0, q_lens[i], QUERY_TILE, dtype=np.int32)
         tile_seq.append(np.full(starts_i.size, i, dtype=np.int32))
         tile_q0.append(starts_i)
+        tile_keys.append(int(kv_lens[i]) - int(q_lens[i]) + np.minimum(starts_i + QUERY_TILE, int(q_lens[i])))   # keys a tile's last query sees
     empty = np.zeros(0, np.int32)
+    if tile_seq:
+        # the tiles with most keys first, over all requests: the hardware hands out CTAs in this order, and the kernel
+        # that gives a CTA two tiles pairs the list's front with its back
+        order = np.argsort(-np.concatenate(tile_keys), kind="stable")
+        tile_seq, tile_q0 = [np.concatenate(tile_seq)[order]], [np.concatenate(tile_q0)[order]]
     arrays = {"dec_tokens": np.asarray(cu_q, dtype=np.int32)[:-1][dec], "dec_seqs": dec,
               "tile_seq": np.concatenate(tile_seq) if tile_seq else empty,
               "tile_q0": np.concatenate(tile_q0) if tile_q0 else empty}
