@@ -204,3 +204,25 @@ def test_step_cost_follows_the_plan(tiny_folders, plain_models):
     twice = build(tiny_folders["B"], lambda p: dataclasses.replace(
         p, schedule=p.schedule + (ScheduleEntry(0, p.num_cache_slots, True),)))
     assert twice.step_cost([1], [5], 1)["weight_bytes"] > model.step_cost([1], [5], 1)["weight_bytes"]
+
+
+def test_the_plan_of_a_product_follows_its_shape():
+    """Which tile form a tensor-core product takes, for a device of 148 multiprocessors: weights on the tile's rows up to
+    128 tokens (split along K where the tiles alone do not fill the device), tokens on the rows above; pairs of CTAs on
+    256 x 256 where their rounds cost less than any width of one CTA's tile, whole heads in a tile where the epilogue
+    wants them."""
+    from acvram_b200.kernels import ops
+    plan = lambda *a, **k: ops.gemm_tc_plan(*a, sms=148, **k)
+    for M in (1, 8, 16):
+        swap, bn, splits, stages = plan(M, 4096, 4096)[:4]
+        assert (swap, bn) == (1, 16) and splits > 1, "32 tiles of weights on 148 SMs: the K range is shared out"
+    assert plan(100, 6144, 4096)[:2] == (1, 128)
+    for shape in ((2048, 6144, 4096), (2048, 4096, 4096), (2048, 24576, 4096), (2048, 4096, 12288), (8192, 24576, 4096)):
+        p = plan(*shape)
+        assert p[:3] == (0, 256, 1) and p[4] == ops.GEMM_PAIR, shape
+    assert len(plan(1056, 34816, 5120)) == 4 and plan(1056, 34816, 5120)[:2] == (0, 256)      # 1280 rows of pair tiles for 1056 tokens
+    assert plan(1056, 5120, 5120)[:2] == (0, 160), "a narrower tile where it saves a round"
+    assert plan(1056, 5120, 5120, bn_multiple=128)[1] % 128 == 0
+    assert plan(300, 200, 512)[:2] == (0, 128) and plan(300, 40, 512)[:2] == (0, 64)
+    # a device with one multiprocessor has no pairs
+    assert len(ops.gemm_tc_plan(2048, 4096, 4096, sms=1)) == 4
