@@ -37,10 +37,12 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     constexpr int CH = D / 8;                 // 16-byte chunks per row
     constexpr int WT_BYTES = 16 * D * 2;                         // 16 keys (or values) of one kv-head
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* q_s = smem;                                   // [16][D]
-    unsigned char* ring = smem + 16 * D * 2;                     // [4 warps][AD_STAGES][K, V][16][D]
+    unsigned char* ring = smem;                                  // [4 warps][AD_STAGES][K, V][16][D]
     int* pg_s = reinterpret_cast<int*>(ring + 4 * AD_STAGES * 2 * WT_BYTES);   // [pg_cap] pages of this CTA's keys
-    float* cm_s = reinterpret_cast<float*>(pg_s + ((pg_cap + 3) & ~3));          // [n_splits][NH/NKV][D + 2] (cluster merge)
+    unsigned char* q_s = reinterpret_cast<unsigned char*>(pg_s + ((pg_cap + 31) & ~31));   // [16][D], until they are in registers
+    // cluster merge, in rank 0: the partial results of the splits 1.. as [n_splits - 1][NH/NKV][D + 2], over the queries
+    // (the peers write here at their end, and no sooner than every thread of rank 0 has its queries in registers)
+    float* cm_s = reinterpret_cast<float*>(q_s);
     __shared__ int is_last_s;
 
     ACV_TL(TL_ATTN_DECODE, 0);
@@ -138,9 +140,6 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         }
     }
     pdl_wait();
-    // the splits of one cluster write their partial results into rank 0's shared memory at the end: a CTA may do so
-    // only when it knows that rank 0 has started, which is what the first phase of the cluster's barrier tells it
-    if (in_cluster) cluster_arrive();
     // ---- queries of the group into shared memory (rows >= n_rep are zero)
     for (int id = tid; id < 16 * CH; id += AD_THREADS) {
         const int r = id / CH, c = id % CH;
@@ -164,6 +163,17 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
 #pragma unroll
         for (int kd = 0; kd < D / 16; ++kd)
             ldmatrix_x4(qf[kd], smem_u32(q_s + tile_off<D>((mi & 1) * 8 + r, kd * 2 + (mi >> 1))));
+    }
+    // the splits of one cluster write their partial results into rank 0's shared memory at the end, where its queries
+    // lay: a CTA may do so only when it knows that rank 0 has started and no longer reads them, which is what the first
+    // phase of the cluster's barrier tells it.  Every thread arrives when its own reads have returned (the arrival takes
+    // the loaded registers as operands); it publishes nothing, so it needs no release, which here would wait for the
+    // copies of the first tiles that are under way (measured: half a microsecond a launch).
+    if (in_cluster) {
+        uint32_t seen = 0;
+#pragma unroll
+        for (int kd = 0; kd < D / 16; ++kd) seen |= qf[kd][0] | qf[kd][1] | qf[kd][2] | qf[kd][3];
+        asm volatile("{\n.reg .pred p;\nsetp.eq.u32 p, %0, 0xffffffff;\nbarrier.cluster.arrive.relaxed.aligned;\n}" :: "r"(seen) : "memory");
     }
 
     float acc[D / 8][4];
@@ -257,6 +267,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     float* wm = reinterpret_cast<float*>(ring);           // [4][16]
     float* wl = wm + 64;                                  // [4][16]
     float* wacc = wl + 64;                                // [4][16][D]
+    float* own_s = wacc + 4 * 16 * D;                     // [NH/NKV][D + 2]: rank 0's own partial result (cluster merge)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -299,11 +310,20 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         } else if (cluster_merge) {
             // the splits of a (request, kv-head) are the CTAs of one cluster: each puts its partial into rank 0's
             // shared memory, rank 0 merges them after the cluster barrier
-            const uint32_t dst = cluster_map(smem_u32(cm_s), 0) + ((split * n_rep + r) * (D + 2) + d) * 4;
-            cluster_store_f32(dst, O);
-            if (d == 0) {
-                cluster_store_f32(dst + D * 4, M);
-                cluster_store_f32(dst + (D + 1) * 4, L);
+            if (split == 0) {
+                float* dst = own_s + r * (D + 2);
+                dst[d] = O;
+                if (d == 0) {
+                    dst[D] = M;
+                    dst[D + 1] = L;
+                }
+            } else {
+                const uint32_t dst = cluster_map(smem_u32(cm_s), 0) + (((split - 1) * n_rep + r) * (D + 2) + d) * 4;
+                cluster_store_f32(dst, O);
+                if (d == 0) {
+                    cluster_store_f32(dst + D * 4, M);
+                    cluster_store_f32(dst + (D + 1) * 4, L);
+                }
             }
         } else {
             part_acc[(part * n_rep + r) * D + d] = O;
@@ -319,12 +339,12 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         if (split != 0) return;
         for (int idx = tid; idx < n_rep * D; idx += AD_THREADS) {
             const int r = idx / D, d = idx % D;
-            float M = -INFINITY;
-            for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, cm_s[(sp * n_rep + r) * (D + 2) + D]);
+            float M = own_s[r * (D + 2) + D];
+            for (int sp = 1; sp < n_splits; ++sp) M = fmaxf(M, cm_s[((sp - 1) * n_rep + r) * (D + 2) + D]);
             float L = 0.f, O = 0.f;
             if (M != -INFINITY) {
                 for (int sp = 0; sp < n_splits; ++sp) {          // split order: the sum does not depend on timing
-                    const float* ps = cm_s + (sp * n_rep + r) * (D + 2);
+                    const float* ps = sp == 0 ? own_s + r * (D + 2) : cm_s + ((sp - 1) * n_rep + r) * (D + 2);
                     const float f = exp2f(ps[D] - M);
                     L += ps[D + 1] * f;
                     O += ps[d] * f;
@@ -348,19 +368,131 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     const size_t base = ((size_t)item * NKV + kvh) * n_splits;
     for (int idx = tid; idx < n_rep * D; idx += AD_THREADS) {
         const int r = idx / D, d = idx % D;
+        // eight splits' loads are under way at a time (one after the other, every split would cost a round trip to the
+        // L2 cache); the sums still run in split order
+        const float2* ml = reinterpret_cast<const float2*>(part_ml) + base * n_rep + r;
+        const float* pa = part_acc + (base * n_rep + r) * D + d;
         float M = -INFINITY;
-        for (int sp = 0; sp < n_splits; ++sp) M = fmaxf(M, __ldcg(&part_ml[((base + sp) * n_rep + r) * 2]));
+        for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+            float m[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) m[u] = sp0 + u < n_splits ? __ldcg(&ml[(size_t)(sp0 + u) * n_rep]).x : -INFINITY;
+#pragma unroll
+            for (int u = 0; u < 8; ++u) M = fmaxf(M, m[u]);
+        }
         float L = 0.f, O = 0.f;
         if (M != -INFINITY) {
-            for (int sp = 0; sp < n_splits; ++sp) {
-                const float f = exp2f(__ldcg(&part_ml[((base + sp) * n_rep + r) * 2]) - M);
-                L += __ldcg(&part_ml[((base + sp) * n_rep + r) * 2 + 1]) * f;
-                O += __ldcg(&part_acc[((base + sp) * n_rep + r) * D + d]) * f;
+            for (int sp0 = 0; sp0 < n_splits; sp0 += 8) {
+                float2 v[8];
+                float o[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    const bool ok = sp0 + u < n_splits;
+                    v[u] = ok ? __ldcg(&ml[(size_t)(sp0 + u) * n_rep]) : make_float2(-INFINITY, 0.f);
+                    o[u] = ok ? __ldcg(&pa[(size_t)(sp0 + u) * n_rep * D]) : 0.f;
+                }
+#pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if (sp0 + u < n_splits) {
+                        const float f = exp2f(v[u].x - M);
+                        L += v[u].y * f;
+                        O += o[u] * f;
+                    }
+                }
             }
         }
         out[(size_t)tok * out_stride + (size_t)(kvh * n_rep + r) * D + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
     }
     if (tid == 0) counters[item * NKV + kvh] = 0;   // ready for the next launch
+}
+
+// Dynamic shared memory of a CTA: the four warps' rings, the block-table entries of its keys, and the queries or, with a
+// merge inside the cluster and in their place, the partial results of the other splits (used in rank 0).
+static int decode_smem_bytes(int D, int n_rep, int page_size, int window, int n_splits, int max_kv, int cluster_merge,
+                             int* pg_cap_out) {
+    const int keys = window > 0 && window < max_kv ? window : max_kv;
+    const int chunk = (((keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
+    int pg_cap = chunk / page_size + 2;
+    if (pg_cap > 8192) pg_cap = 8192;
+    *pg_cap_out = pg_cap;
+    const int queries = 16 * D * 2;
+    const int partials = cluster_merge ? (n_splits - 1) * n_rep * (D + 2) * 4 : 0;     // where the queries lay
+    return 4 * AD_STAGES * 2 * 16 * D * 2 + ((pg_cap + 31) & ~31) * 4 + (partials > queries ? partials : queries);
+}
+
+// One record per kernel instance of the shared memory it has been allowed so far: the launch and the residency question
+// must not keep two, the second would lower what the first has raised.
+template <int D>
+static AcvSmemConfig& decode_smem_config() {
+    static AcvSmemConfig config;
+    return config;
+}
+
+template <int D>
+static int decode_resident(int smem, int cluster) {
+    if (int rc = acv_ensure_smem(decode_smem_config<D>(), attn_decode_kernel<D>, smem)) return rc > 0 ? ACV_ERR_SIZE : rc;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
+        cudaGetLastError();
+        return ACV_ERR_SIZE;
+    }
+    if (cluster <= 1) {
+        int per_sm = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<D>, AD_THREADS, smem) != cudaSuccess) {
+            cudaGetLastError();
+            return ACV_ERR_SIZE;
+        }
+        return per_sm * sms;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, cluster);
+    cfg.blockDim = dim3(AD_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = cluster;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    if (cudaOccupancyMaxActiveClusters(&clusters, attn_decode_kernel<D>, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        return ACV_ERR_SIZE;
+    }
+    return clusters * cluster;
+}
+
+// A grid small enough to have an SM for every CTA gets one: with room for two, the CTAs of a cluster are put two to an
+// SM, half the SMs stay empty and the step of a single request measured 1.9 % slower.  The kernel is then given so much
+// shared memory that a second CTA does not fit.  Returns that size, or ``smem`` where the grid is larger than what the
+// device holds that way (asked of the runtime once per device and cluster size).
+template <int D>
+static int decode_smem_spread(int smem, int cluster, long long ctas) {
+    static std::mutex mu;
+    static int fit[64][9];          // [device][cluster size]: CTAs resident with one to an SM; -1 = cannot be had
+    static int alone_bytes[64];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 1 || cluster > 8) return smem;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!alone_bytes[dev]) {
+        int per_sm = 0, reserved = 0, per_block = 0;
+        if (cudaDeviceGetAttribute(&per_sm, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&reserved, cudaDevAttrReservedSharedMemoryPerBlock, dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&per_block, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+            cudaGetLastError();
+            alone_bytes[dev] = -1;
+        } else {
+            const int want = per_sm / 2 - reserved + 128;      // two of these and their reserves exceed an SM
+            alone_bytes[dev] = want <= per_block ? want : -1;
+        }
+    }
+    const int alone = alone_bytes[dev];
+    if (alone <= smem) return smem;                              // already one to an SM, or unknown
+    if (!fit[dev][cluster]) {
+        const int n = decode_resident<D>(alone, cluster);
+        fit[dev][cluster] = n > 0 ? n : -1;
+    }
+    return ctas <= fit[dev][cluster] ? alone : smem;
 }
 
 template <int D>
@@ -372,16 +504,11 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     int page_shift = -1;
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
-    const int keys = window > 0 && window < max_kv ? window : max_kv;
-    const int chunk = (((keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
-    int pg_cap = chunk / page_size + 2;
-    if (pg_cap > 8192) pg_cap = 8192;
     if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
-    const int n_rep = NH / NKV;
-    const int smem = 16 * D * 2 + 4 * AD_STAGES * 2 * 16 * D * 2 + ((pg_cap + 3) & ~3) * 4 +
-                     (cluster_merge ? n_splits * n_rep * (D + 2) * 4 : 0);
-    static AcvSmemConfig smem_config;          // per kernel instance and device
-    if (int rc = acv_ensure_smem(smem_config, attn_decode_kernel<D>, smem)) return rc;
+    int pg_cap = 0;
+    int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, &pg_cap);
+    smem = decode_smem_spread<D>(smem, cluster_merge ? n_splits : 1, (long long)n_dec * NKV * n_splits);
+    if (int rc = acv_ensure_smem(decode_smem_config<D>(), attn_decode_kernel<D>, smem)) return rc;
     dim3 grid(n_dec, NKV, n_splits);
     acv_launch_cluster(PDL_ATTN, dim3(1, 1, cluster_merge ? n_splits : 1), attn_decode_kernel<D>, grid, AD_THREADS, smem, stream,
         (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
@@ -410,6 +537,7 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
         if (parts * n_rep * D > scratch_floats || parts * n_rep * 2 > scratch_ml_floats ||
             (long long)n_dec * NKV > scratch_counters)
             return ACV_ERR_SCRATCH;
+        if ((uintptr_t)part_ml & 7) return ACV_ERR_ALIGN;      // (max, sum) are read as pairs
     }
 #define AD_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
                 bt_stride, bt_rows, NH, NKV, page_size, num_pages, scale, window, n_splits, part_acc, part_ml, counters, max_kv, \
@@ -420,6 +548,22 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
         default: return ACV_ERR_SIZE;
     }
 #undef AD_ARGS
+}
+
+// How many CTAs of the split-KV kernel the device holds at once for these sizes (clusters that fit, times their size,
+// when the splits merge inside clusters): what the choice of the number of splits is made from.  Negative: an error.
+ACV_API int acv_attention_decode_resident(int NH, int NKV, int D, int page_size, int window, int n_splits, int max_kv,
+                                          int cluster_merge) {
+    if (NKV <= 0 || NH % NKV || NH / NKV > 16 || n_splits < 1 || n_splits > 65535 || page_size <= 0) return ACV_ERR_SIZE;
+    if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
+    int pg_cap = 0;
+    const int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, &pg_cap);
+    const int cluster = cluster_merge ? n_splits : 1;
+    switch (D) {
+        case 64: return decode_resident<64>(smem, cluster);
+        case 128: return decode_resident<128>(smem, cluster);
+        default: return ACV_ERR_SIZE;
+    }
 }
 
 // ----------------------------------------------------------------------------- entry point without allocation

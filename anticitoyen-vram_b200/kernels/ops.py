@@ -9,6 +9,7 @@ CUDA device, the first call raises.
 from __future__ import annotations
 
 import ctypes
+import functools
 from ctypes import c_float, c_int, c_void_p
 
 import torch
@@ -92,6 +93,8 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.acv_decode_layer.restype = c_int
     lib.acv_decode_layer_takes.argtypes = [I] * 8
     lib.acv_decode_layer_takes.restype = c_int
+    lib.acv_attention_decode_resident.argtypes = [I] * 8
+    lib.acv_attention_decode_resident.restype = c_int
     lib.acv_random_normal.argtypes = [P, LL, ctypes.c_ulonglong, F, F, P, P, I, P]
     lib.acv_random_normal.restype = c_int
     lib.acv_random_int.argtypes = [P, LL, ctypes.c_ulonglong, ctypes.c_uint, P]
@@ -576,17 +579,77 @@ def _decode_scratch(device, floats: int, ml_floats: int, counters: int):
     return have
 
 
-def decode_splits(n_dec: int, num_kv_heads: int, max_kv: int) -> int:
-    """How many splits of the context: enough CTAs to cover the SMs not quite twice (measured best on a
-    B200: a split costs a fixed few microseconds of merge), and no split shorter than 256 keys.  Up to 8
-    splits merge inside a cluster, which is so much cheaper than the merge through scratch memory that
-    more than 8 pay only when a split would otherwise hold more than 1024 keys."""
-    pairs = max(1, n_dec * num_kv_heads)
-    want = max(1, round(256 / 148 * sm_count() / pairs))
-    splits = max(1, min(want, -(-max_kv // 256)))
-    if splits > 8 and max_kv <= 8 * 1024:
-        splits = 8
-    return splits
+# What the choice of the number of splits reckons with: fitted to a sweep on a B200 over 1 to 64 requests, contexts of
+# 1024 to 65536 keys (8 kv-heads of 128, 4 query heads each, pages of 64) and every way of splitting below.  The reckoned
+# time is within a tenth of the measured one (root mean square); the splits chosen by it took 3 % more time over the
+# whole sweep than the best of each case (the rule before it, "CTAs for not quite twice the SMs": 9 %, and up to 60 %
+# where clusters of 8 did not fit the device at once).
+DECODE_KEY_US = 0.0099           # a CTA alone streams a key and its value in this time (its warps wait for their rings)
+DECODE_STREAM_BYTES_US = 6.4e6   # what all CTAs together stream from memory
+DECODE_BOUNDS_NORM = 5.5         # near both limits a round takes the p-norm of the two times, not the larger
+DECODE_MERGE_US = (6.1, 9.3, 0.35, 10.2, 0.79)  # start to end without splits; merged inside a cluster + per split;
+                                                # through scratch memory + per split
+DECODE_SPLIT_KEYS = 256          # no split shorter than this
+DECODE_CLUSTER_SPLITS = (2, 4, 6, 8)       # 3 and 5 were never better than their even neighbours by more than 2 %
+DECODE_SCRATCH_SPLITS = (2, 4, 8, 12, 16, 24, 32)
+DECODE_WIDE_CLUSTER_FIT = 0.85   # of the clusters of more than 6 CTAs that the runtime says fit at once, this part did
+
+
+@functools.lru_cache(maxsize=None)
+def decode_resident(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, n_splits: int,
+                    pages_of_split: int, cluster_merge: bool) -> int:
+    """How many CTAs of the split-KV kernel the device holds at once (asked of the runtime: a cluster needs its CTAs
+    side by side in one part of the chip, and the partial results of 8 splits leave room for one CTA per SM only)."""
+    n = library().acv_attention_decode_resident(num_heads, num_kv_heads, head_dim, page_size, 0, n_splits,
+                                                pages_of_split * page_size * n_splits, 1 if cluster_merge else 0)
+    if n < 0:
+        raise KernelError(f"attention_decode_resident: {_ERRORS.get(n, f'refused with code {n}')}")
+    return max(1, n)
+
+
+def decode_splits_cost(n_dec: int, num_kv_heads: int, max_kv: int, n_splits: int, cluster_merge: bool, resident: int,
+                       row_bytes: int) -> float:
+    """Reckoned microseconds of the split-KV kernel: the CTAs run in rounds of ``resident``; a round takes as long as
+    one CTA needs for its keys alone, or as the memory needs for the round's bytes; then the merge."""
+    ctas = n_dec * num_kv_heads * n_splits
+    keys = -(-max_kv // n_splits)
+    alone = keys * DECODE_KEY_US
+    p = DECODE_BOUNDS_NORM
+    round_us = lambda n: (alone ** p + (n * keys * row_bytes / DECODE_STREAM_BYTES_US) ** p) ** (1.0 / p)
+    full, rest = divmod(ctas, resident)
+    us = full * round_us(resident) + (round_us(rest) if rest else 0.0)
+    if n_splits == 1:
+        return us + DECODE_MERGE_US[0]
+    if cluster_merge:
+        return us + DECODE_MERGE_US[1] + DECODE_MERGE_US[2] * n_splits
+    return us + DECODE_MERGE_US[3] + DECODE_MERGE_US[4] * n_splits
+
+
+@functools.lru_cache(maxsize=4096)
+def decode_plan(n_dec: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_kv: int,
+                window: int = 0) -> tuple[int, bool]:
+    """(splits of the context, merged inside clusters?) for ``n_dec`` one-token requests with up to ``max_kv`` keys:
+    the cheapest by ``decode_splits_cost`` among no split, up to 8 splits merged inside a cluster and up to 32 merged
+    through scratch memory.  A split more pays while it shortens what a CTA streams alone; it stops paying when the
+    CTAs no longer fit the device at once or the memory is the limit anyway."""
+    keys = min(max_kv, window) if window > 0 else max_kv
+    row_bytes = 2 * head_dim * 2                       # a key and a value of one kv-head in bfloat16
+    best = None
+    for n_splits, cluster in [(1, False)] + [(s, True) for s in DECODE_CLUSTER_SPLITS] + \
+                             [(s, False) for s in DECODE_SCRATCH_SPLITS]:
+        if n_splits > 1 and keys < n_splits * DECODE_SPLIT_KEYS:
+            continue
+        if n_dec * num_kv_heads * n_splits > 65535 * 4:
+            continue
+        pages = -(-(-(-keys // n_splits)) // page_size)
+        resident = decode_resident(num_heads, num_kv_heads, head_dim, page_size, n_splits,
+                                   1 << max(0, pages - 1).bit_length(), cluster)
+        if cluster and n_splits > 6:
+            resident = max(n_splits, int(resident * DECODE_WIDE_CLUSTER_FIT))
+        cost = decode_splits_cost(n_dec, num_kv_heads, keys, n_splits, cluster, resident, row_bytes)
+        if best is None or cost < best[0]:
+            best = (cost, n_splits, cluster)
+    return best[1], best[2]
 
 
 def attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor,
@@ -703,10 +766,11 @@ def attention(qkv: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor, v_pag
     w = work if work is not None else ctx.work
     if w["n_dec"]:
         kv = min(w["max_dec_kv"], window) if window > 0 else w["max_dec_kv"]
+        n_splits, in_clusters = (w["n_splits"], True) if w.get("n_splits") else \
+            decode_plan(w["n_dec"], num_heads, num_kv_heads, head_dim, k_pages.shape[2], kv)
         attention_decode(qkv, out, k_pages, v_pages, w["dec_tokens"], w["dec_seqs"], w["n_dec"], ctx.kv_len,
-                         block_table, num_heads, num_kv_heads, head_dim, scale, window,
-                         w.get("n_splits") or decode_splits(w["n_dec"], num_kv_heads, kv), w["max_dec_kv"],
-                         table_rows=rows)
+                         block_table, num_heads, num_kv_heads, head_dim, scale, window, n_splits, w["max_dec_kv"],
+                         cluster_merge=in_clusters, table_rows=rows)
     if w["n_tiles"] and attention_tc_takes(qkv, out, k_pages, head_dim):
         attention_tc(qkv, out, k_pages, v_pages, w["tile_seq"], w["tile_q0"], w["n_tiles"], ctx.cu_q, ctx.kv_len,
                      block_table, num_heads, num_kv_heads, head_dim, scale, window, table_rows=rows)

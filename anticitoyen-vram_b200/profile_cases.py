@@ -61,12 +61,12 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
     cu_q = (torch.arange(batch + 1, dtype=torch.int32, device="cuda") * q_len)
     if q_len == 1:
         rows = torch.arange(batch, dtype=torch.int32, device="cuda")
-        splits = ops.decode_splits(batch, NKV, context)
+        splits, in_clusters = ops.decode_plan(batch, NH, NKV, D, page, context)
         fn = lambda i: ops.attention_decode(qkv, out, *pools[i % sets], rows, rows, batch, kv_len, table, NH, NKV, D,
-                                            D ** -0.5, 0, splits, context)
+                                            D ** -0.5, 0, splits, context, cluster_merge=in_clusters)
         us = _time(fn, reps)
         gb = batch * context * NKV * D * 2 * 2 / 1e9
-        print(f"attention_decode batch={batch} context={context} page={page} splits={splits}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of pages")
+        print(f"attention_decode batch={batch} context={context} page={page} splits={splits}{' in clusters' if in_clusters else ''}: {us:.1f} us, {gb / us * 1e6:.0f} GB/s of pages")
         return {"kernel": "attention_decode", "batch": batch, "context": context, "us": us, "pages_gbs": gb / us * 1e6}
     else:
         tiles = [(b, s) for b in range(batch) for s in range(0, q_len, QUERY_TILE)][::-1]

@@ -226,3 +226,33 @@ def test_the_plan_of_a_product_follows_its_shape():
     assert plan(300, 200, 512)[:2] == (0, 128) and plan(300, 40, 512)[:2] == (0, 64)
     # a device with one multiprocessor has no pairs
     assert len(ops.gemm_tc_plan(2048, 4096, 4096, sms=1)) == 4
+
+
+def test_the_splits_of_decode_attention_follow_what_fits_the_device(monkeypatch):
+    """How the split-KV kernel cuts the context, for a device that holds 296 of its CTAs at once (stubbed: the real
+    figure is asked of the runtime): a few long requests are split so far that a CTA's own streaming is short, many
+    requests not at all; more than 8 splits, through scratch memory, only where 8 leave a CTA thousands of keys; and
+    where the clusters of some size fit the device badly, that size is passed over."""
+    from acvram_b200.kernels import ops
+    fits = {}
+
+    def resident(num_heads, num_kv_heads, head_dim, page_size, n_splits, pages_of_split, cluster_merge):
+        return fits.get((n_splits, cluster_merge), 296)
+    monkeypatch.setattr(ops, "decode_resident", resident)
+    plan = lambda n_dec, max_kv: ops.decode_plan.__wrapped__(n_dec, 32, 8, 128, 64, max_kv)
+    assert plan(64, 2048) == (1, False) and plan(64, 16384) == (1, False)
+    n, in_clusters = plan(8, 2048)
+    assert 2 <= n <= 4 and in_clusters
+    n, in_clusters = plan(1, 8192)
+    assert n == 8 and in_clusters
+    n, in_clusters = plan(1, 65536)
+    assert n > 8 and not in_clusters
+    assert plan(1, 300) == (1, False), "no split shorter than 256 keys"
+    # 24 clusters of 8 for 3 requests: all at once on this device, not on one that holds 15 of them
+    assert plan(3, 16384) == (8, True)
+    fits[(8, True)] = 120
+    assert plan(3, 16384)[0] != 8 or not plan(3, 16384)[1]
+    # the cost itself: a second round costs, and so does every split's share of the merge
+    one = ops.decode_splits_cost(2, 8, 8192, 8, True, 296, 512)
+    assert ops.decode_splits_cost(2, 8, 8192, 8, True, 64, 512) > 1.3 * one
+    assert ops.decode_splits_cost(2, 8, 8192, 8, False, 296, 512) > one

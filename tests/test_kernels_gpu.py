@@ -354,7 +354,7 @@ def _decode_direct(ops, NH, NKV, D, page, lens, n_splits, cluster_merge, seed, s
     kv_len, ar = i32(lens), i32(list(range(B)))
     out1 = torch.full((B, NH * D), 7.0, device="cuda", dtype=dtype)
     out2 = torch.zeros_like(out1)
-    splits = n_splits or ops.decode_splits(B, NKV, max(lens))
+    splits = n_splits or ops.decode_plan(B, NH, NKV, D, page, max(lens))[0]
     ops.attention_decode(q, out1, kp, vp, ar, ar, B, kv_len, table, NH, NKV, D, D ** -0.5, 0, splits, max(lens),
                          cluster_merge=cluster_merge)
     ref.attention_generic(q, out2, kp, vp, i32([l - 1 for l in lens]), ar, table, NH, NKV, D, D ** -0.5, 0)
@@ -373,14 +373,14 @@ def test_decode_attention_merge_through_scratch_memory(ops, n_splits):
 
 
 def test_decode_attention_long_context_chooses_many_splits(ops):
-    """About 10 000 keys: the split count that serving computes is above 8, the merge goes through scratch memory
+    """About 20 000 keys: the split count that serving computes is above 8, the merge goes through scratch memory
     and block-table entries beyond the part cached in shared memory are read; one far key at a split's edge carries
     the answer for request 0."""
-    lens = [10000, 517]
-    assert ops.decode_splits(len(lens), 2, max(lens)) > 8
-    n = ops.decode_splits(len(lens), 2, max(lens))
+    lens = [20000, 517]
+    n, in_clusters = ops.decode_plan(len(lens), 8, 2, 128, 16, max(lens))
+    assert n > 8 and not in_clusters
     per = -(-max(lens) // n)
-    for j in (per - 1, per, 5 * per, 9999, 0):
+    for j in (per - 1, per, 5 * per, 19999, 0):
         o1, o2, splits = _decode_direct(ops, 8, 2, 128, 16, lens, None, cluster_merge=True, seed=85 + j % 7, spike=(0, j))
         assert splits == n
         torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
