@@ -81,6 +81,46 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
         return {"kernel": kernel.__name__, "batch": batch, "q_len": q_len, "context": context, "us": us, "tflops": flops / us / 1e6}
 
 
+def decode_split_case(reps: int) -> dict:
+    """The split-KV kernel with every way of cutting the context that ``ops.decode_plan`` chooses from, for a few
+    batches and context lengths (Qwen3-8B head sizes, pages of 64, rotating pools larger than L2): microseconds a
+    launch, with the time the plan reckons and the way it takes."""
+    NH, NKV, D, page = 32, 8, 128, 64
+    out = {}
+    for batch, context in ((1, 8192), (2, 8192), (4, 8192), (4, 16384), (8, 2048), (8, 8192), (12, 8192), (32, 8192), (1, 65536)):
+        pages_per = context // page
+        n_pages = batch * pages_per
+        pools = [(torch.randn(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16),
+                  torch.randn(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)) for _ in range(3)]
+        table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(batch, pages_per)
+        qkv = torch.randn(batch, (NH + 2 * NKV) * D, device="cuda", dtype=torch.bfloat16)
+        o = torch.empty(batch, NH * D, device="cuda", dtype=torch.bfloat16)
+        kv_len = torch.full((batch,), context, dtype=torch.int32, device="cuda")
+        rows = torch.arange(batch, dtype=torch.int32, device="cuda")
+        chosen = ops.decode_plan(batch, NH, NKV, D, page, context)
+        cells = []
+        for n_splits, cluster in [(1, False)] + [(s, True) for s in ops.DECODE_CLUSTER_SPLITS] + \
+                                 [(s, False) for s in ops.DECODE_SCRATCH_SPLITS]:
+            if context < n_splits * ops.DECODE_SPLIT_KEYS:
+                continue
+            fn = lambda i: ops.attention_decode(qkv, o, *pools[i % 3], rows, rows, batch, kv_len, table, NH, NKV, D,
+                                                D ** -0.5, 0, n_splits, context, cluster_merge=cluster)
+            us = min(_time(fn, reps), _time(fn, reps))
+            pages = -(-(-(-context // n_splits)) // page)
+            fit = ops.decode_resident(NH, NKV, D, page, n_splits, 1 << max(0, pages - 1).bit_length(), cluster)
+            if cluster and n_splits > 6:
+                fit = max(n_splits, int(fit * ops.DECODE_WIDE_CLUSTER_FIT))
+            reckoned = ops.decode_splits_cost(batch, NKV, context, n_splits, cluster, fit, 2 * D * 2)
+            name = f"{n_splits}{'c' if cluster else 's' if n_splits > 1 else ''}"
+            out[f"b{batch} c{context} {name}"] = us
+            cells.append(f"{name}{'*' if (n_splits, cluster) == chosen else ''} {us:.0f}/{reckoned:.0f}")
+        print(f"batch {batch:2d} context {context:6d}: " + "  ".join(cells))
+        del pools
+        torch.cuda.empty_cache()
+    print("   (splits, c = merged inside a cluster, s = through scratch memory, * = the plan's choice: measured / reckoned us)")
+    return out
+
+
 def tile_width_case(reps: int) -> dict:
     """The tokens-on-rows product at every tile width, for the shapes of a 2048-token prefill (8B sizes) and of a
     1024-token portion beside 32 decoding requests (14B sizes): what ``ops.GEMM_TILE_OVERHEAD`` was read from."""
@@ -187,10 +227,13 @@ CASES = {
     "gemm_prefill": lambda r: gemm_case(2048, 24576, 4096, r),
     "attention_decode": lambda r: attention_case(8, 1, 2048, r),
     "attention_decode_b64": lambda r: attention_case(64, 1, 2048, r),
+    "attention_decode_32k": lambda r: attention_case(8, 1, 32768, r),
+    "attention_decode_b1_128k": lambda r: attention_case(1, 1, 131072, r),
     "attention_prefill": lambda r: attention_case(1, 2048, 2048, r),
     "attention_prefill_8k": lambda r: attention_case(1, 2048, 8192, r),
     "attention_prefill_mma_sync": lambda r: attention_case(1, 2048, 2048, r, legacy=True),
     "gemm_prefill_down": lambda r: gemm_case(2048, 4096, 12288, r),
+    "attention_decode_splits": decode_split_case,
     "gemm_tile_widths": tile_width_case,
     "gemm_pairs": pair_case,
     "sample": lambda r: sample_case(8, 151936, r),
