@@ -300,7 +300,7 @@ def _tc_case(ops, NH, NKV, D, page, lens, q_lens, window, seed, n_splits=None, s
 
 @pytest.mark.parametrize("NH,NKV,D,page", [(8, 2, 128, 16), (6, 2, 64, 8), (5, 1, 64, 16), (16, 1, 128, 32), (4, 4, 128, 4),
                                           (3, 3, 64, 16)])
-@pytest.mark.parametrize("n_splits", [1, 2, 5, None])
+@pytest.mark.parametrize("n_splits", [1, 2, 5, 8, None])
 def test_attention_decode_kernel(ops, NH, NKV, D, page, n_splits):
     o1, o2 = _tc_case(ops, NH, NKV, D, page, lens=[1, 77, 300, 64, 65, 513], q_lens=[1] * 6, window=0, seed=60,
                       n_splits=n_splits)
@@ -370,6 +370,20 @@ def test_decode_attention_merge_through_scratch_memory(ops, n_splits):
                                          (84, 8, 2, 128, 16, [640, 33])):
         o1, o2, _ = _decode_direct(ops, NH, NKV, D, page, lens, n_splits, cluster_merge=False, seed=seed)
         torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
+
+
+@pytest.mark.parametrize("n_splits", [2, 6, 8])
+def test_decode_attention_merge_inside_clusters(ops, n_splits):
+    """The splits of a request are the CTAs of a cluster: rank 0 keeps its own partial result, the others write theirs
+    where rank 0's queries lay.  One far key carries the answer of request 0, in rank 0's part, at the edges of the
+    parts and in the last one; 4 and 16 query heads to a kv-head (the partial results are smaller and larger than the
+    queries' buffer)."""
+    for NH, NKV in ((8, 2), (16, 1)):
+        lens = [3000, 517, 40]
+        per = -(-max(lens) // n_splits)
+        for j in (0, 7, per - 1, per, 2999):
+            o1, o2, _ = _decode_direct(ops, NH, NKV, 128, 16, lens, n_splits, cluster_merge=True, seed=90 + j % 5, spike=(0, j))
+            torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
 
 
 def test_decode_attention_long_context_chooses_many_splits(ops):
