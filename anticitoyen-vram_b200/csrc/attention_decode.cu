@@ -19,14 +19,15 @@
 // through the block table one by one, so any page size works.
 #include "mma_tiles.cuh"
 
-#define AD_THREADS 128
 #define AD_EARLY_KEYS 0
 #define AD_TILE 64          // split boundaries fall on multiples of this many keys
 #define AD_STAGES 3         // buffers in each warp's ring (2 and 4 measured slower on a B200)
+#define AD_WARPS 4          // warps of a CTA where two CTAs share an SM
+#define AD_WARPS_ALONE 8    // where a CTA has its SM to itself (a grid of no more CTAs than SMs)
 #define AD_LOG2E 1.4426950408889634f
 
-template <int D>
-__global__ void __launch_bounds__(AD_THREADS)
+template <int D, int NW>
+__global__ void __launch_bounds__(NW * 32)
 attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ out, int out_stride,
                    const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                    const int* __restrict__ dec_tokens, const int* __restrict__ dec_seqs,
@@ -35,10 +36,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
                    float* __restrict__ part_acc, float* __restrict__ part_ml, int* __restrict__ counters,
                    int cluster_merge) {
     constexpr int CH = D / 8;                 // 16-byte chunks per row
+    constexpr int AD_THREADS = NW * 32;
     constexpr int WT_BYTES = 16 * D * 2;                         // 16 keys (or values) of one kv-head
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* ring = smem;                                  // [4 warps][AD_STAGES][K, V][16][D]
-    int* pg_s = reinterpret_cast<int*>(ring + 4 * AD_STAGES * 2 * WT_BYTES);   // [pg_cap] pages of this CTA's keys
+    unsigned char* ring = smem;                                  // [NW warps][AD_STAGES][K, V][16][D]
+    int* pg_s = reinterpret_cast<int*>(ring + NW * AD_STAGES * 2 * WT_BYTES);   // [pg_cap] pages of this CTA's keys
     unsigned char* q_s = reinterpret_cast<unsigned char*>(pg_s + ((pg_cap + 31) & ~31));   // [16][D], until they are in registers
     // cluster merge, in rank 0: the partial results of the splits 1.. as [n_splits - 1][NH/NKV][D + 2], over the queries
     // (the peers write here at their end, and no sooner than every thread of rank 0 has its queries in registers)
@@ -73,10 +75,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     __syncthreads();
 
     // Each warp streams its own keys: the CTA's range is cut into tiles of 16 keys, warp w takes the
-    // tiles w, w+4, w+8 ... through a ring of AD_STAGES buffers of its own, so that several tiles
+    // tiles w, w+NW, w+2NW ... through a ring of AD_STAGES buffers of its own, so that several tiles
     // are in flight for every warp and no warp waits for another inside the loop.
     const int n_wt = beg < end ? (end - beg + 15) / 16 : 0;
-    const int my_n = n_wt > warp ? (n_wt - warp + 3) / 4 : 0;
+    const int my_n = n_wt > warp ? (n_wt - warp + NW - 1) / NW : 0;
     unsigned char* my_ring = ring + warp * (AD_STAGES * 2 * WT_BYTES);
 
     // With pages of 16 keys or a multiple, and a range that starts on a multiple of 16, a tile lies
@@ -87,7 +89,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     constexpr int ROWS_PER_IT = 32 / CH;                      // rows a warp covers with one copy instruction
 
     auto load_wt = [&](int i, int stage) {
-        const int j0 = beg + (warp + 4 * i) * 16;
+        const int j0 = beg + (warp + NW * i) * 16;
         unsigned char* kdst = my_ring + stage * 2 * WT_BYTES;
         unsigned char* vdst = kdst + WT_BYTES;
         if (contiguous) {
@@ -133,7 +135,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     int early = 0;
 #pragma unroll
     for (int st = 0; st < AD_STAGES - 1; ++st) {
-        if (AD_EARLY_KEYS && early == st && st < my_n && beg + (warp + 4 * st) * 16 + 16 <= p) {
+        if (AD_EARLY_KEYS && early == st && st < my_n && beg + (warp + NW * st) * 16 + 16 <= p) {
             load_wt(st, st);
             cp_async_commit();
             ++early;
@@ -197,7 +199,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         cp_async_wait<AD_STAGES - 1>();
         __syncwarp();
         const uint32_t kb = smem_u32(my_ring + stage * 2 * WT_BYTES), vb = kb + WT_BYTES;
-        const int jw = beg + (warp + 4 * i) * 16;       // first key of this tile
+        const int jw = beg + (warp + NW * i) * 16;       // first key of this tile
         {
             float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -264,10 +266,10 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
     if (tid == 0) ACV_TL_MARK(TL_M_ATTN_LOOP_DONE);
 
     // ---- merge the four warps through shared memory (the tiles are no longer needed)
-    float* wm = reinterpret_cast<float*>(ring);           // [4][16]
-    float* wl = wm + 64;                                  // [4][16]
-    float* wacc = wl + 64;                                // [4][16][D]
-    float* own_s = wacc + 4 * 16 * D;                     // [NH/NKV][D + 2]: rank 0's own partial result (cluster merge)
+    float* wm = reinterpret_cast<float*>(ring);           // [NW][16]
+    float* wl = wm + NW * 16;                             // [NW][16]
+    float* wacc = wl + NW * 16;                           // [NW][16][D]
+    float* own_s = wacc + NW * 16 * D;                    // [NH/NKV][D + 2]: rank 0's own partial result (cluster merge)
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -295,11 +297,11 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
         const int r = idx / D, d = idx % D;
         float M = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) M = fmaxf(M, wm[w * 16 + r]);
+        for (int w = 0; w < NW; ++w) M = fmaxf(M, wm[w * 16 + r]);
         float L = 0.f, O = 0.f;
         if (M != -INFINITY) {
 #pragma unroll
-            for (int w = 0; w < 4; ++w) {
+            for (int w = 0; w < NW; ++w) {
                 const float f = exp2f(wm[w * 16 + r] - M);
                 L += wl[w * 16 + r] * f;
                 O += wacc[(w * 16 + r) * D + d] * f;
@@ -409,7 +411,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, bf16* __restrict__ 
 // Dynamic shared memory of a CTA: the four warps' rings, the block-table entries of its keys, and the queries or, with a
 // merge inside the cluster and in their place, the partial results of the other splits (used in rank 0).
 static int decode_smem_bytes(int D, int n_rep, int page_size, int window, int n_splits, int max_kv, int cluster_merge,
-                             int* pg_cap_out) {
+                             int warps, int* pg_cap_out) {
     const int keys = window > 0 && window < max_kv ? window : max_kv;
     const int chunk = (((keys + n_splits - 1) / n_splits) + AD_TILE - 1) & ~(AD_TILE - 1);
     int pg_cap = chunk / page_size + 2;
@@ -417,20 +419,20 @@ static int decode_smem_bytes(int D, int n_rep, int page_size, int window, int n_
     *pg_cap_out = pg_cap;
     const int queries = 16 * D * 2;
     const int partials = cluster_merge ? (n_splits - 1) * n_rep * (D + 2) * 4 : 0;     // where the queries lay
-    return 4 * AD_STAGES * 2 * 16 * D * 2 + ((pg_cap + 31) & ~31) * 4 + (partials > queries ? partials : queries);
+    return warps * AD_STAGES * 2 * 16 * D * 2 + ((pg_cap + 31) & ~31) * 4 + (partials > queries ? partials : queries);
 }
 
 // One record per kernel instance of the shared memory it has been allowed so far: the launch and the residency question
 // must not keep two, the second would lower what the first has raised.
-template <int D>
+template <int D, int NW>
 static AcvSmemConfig& decode_smem_config() {
     static AcvSmemConfig config;
     return config;
 }
 
-template <int D>
+template <int D, int NW>
 static int decode_resident(int smem, int cluster) {
-    if (int rc = acv_ensure_smem(decode_smem_config<D>(), attn_decode_kernel<D>, smem)) return rc > 0 ? ACV_ERR_SIZE : rc;
+    if (int rc = acv_ensure_smem(decode_smem_config<D, NW>(), attn_decode_kernel<D, NW>, smem)) return rc > 0 ? ACV_ERR_SIZE : rc;
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) {
@@ -439,7 +441,7 @@ static int decode_resident(int smem, int cluster) {
     }
     if (cluster <= 1) {
         int per_sm = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<D>, AD_THREADS, smem) != cudaSuccess) {
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, attn_decode_kernel<D, NW>, NW * 32, smem) != cudaSuccess) {
             cudaGetLastError();
             return ACV_ERR_SIZE;
         }
@@ -447,7 +449,7 @@ static int decode_resident(int smem, int cluster) {
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1, 1, cluster);
-    cfg.blockDim = dim3(AD_THREADS);
+    cfg.blockDim = dim3(NW * 32);
     cfg.dynamicSmemBytes = smem;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -455,7 +457,7 @@ static int decode_resident(int smem, int cluster) {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int clusters = 0;
-    if (cudaOccupancyMaxActiveClusters(&clusters, attn_decode_kernel<D>, &cfg) != cudaSuccess) {
+    if (cudaOccupancyMaxActiveClusters(&clusters, attn_decode_kernel<D, NW>, &cfg) != cudaSuccess) {
         cudaGetLastError();
         return ACV_ERR_SIZE;
     }
@@ -463,16 +465,17 @@ static int decode_resident(int smem, int cluster) {
 }
 
 // A grid small enough to have an SM for every CTA gets one: with room for two, the CTAs of a cluster are put two to an
-// SM, half the SMs stay empty and the step of a single request measured 1.9 % slower.  The kernel is then given so much
-// shared memory that a second CTA does not fit.  Returns that size, or ``smem`` where the grid is larger than what the
-// device holds that way (asked of the runtime once per device and cluster size).
+// SM, half the SMs stay empty and the step of a single request measured 1.9 % slower.  Such a grid runs the kernel with
+// twice the warps and rings, whose shared memory leaves no room for a second CTA (and is raised to that size where a
+// small head would).  Returns whether the grid is one: no more CTAs than the device holds one to an SM in clusters of this size
+// (asked of the runtime once per device and cluster size).  ``alone`` receives the least size that keeps an SM for one CTA.
 template <int D>
-static int decode_smem_spread(int smem, int cluster, long long ctas) {
+static bool decode_grid_has_sms(int cluster, long long ctas, int* alone) {
     static std::mutex mu;
     static int fit[64][9];          // [device][cluster size]: CTAs resident with one to an SM; -1 = cannot be had
     static int alone_bytes[64];
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 1 || cluster > 8) return smem;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || cluster < 1 || cluster > 8) return false;
     std::lock_guard<std::mutex> lock(mu);
     if (!alone_bytes[dev]) {
         int per_sm = 0, reserved = 0, per_block = 0;
@@ -486,13 +489,29 @@ static int decode_smem_spread(int smem, int cluster, long long ctas) {
             alone_bytes[dev] = want <= per_block ? want : -1;
         }
     }
-    const int alone = alone_bytes[dev];
-    if (alone <= smem) return smem;                              // already one to an SM, or unknown
+    if (alone_bytes[dev] < 0) return false;
+    *alone = alone_bytes[dev];
     if (!fit[dev][cluster]) {
-        const int n = decode_resident<D>(alone, cluster);
+        const int n = decode_resident<D, AD_WARPS_ALONE>(alone_bytes[dev], cluster);
         fit[dev][cluster] = n > 0 ? n : -1;
     }
-    return ctas <= fit[dev][cluster] ? alone : smem;
+    return ctas <= fit[dev][cluster];
+}
+
+template <int D, int NW>
+static int launch_decode_with(const void* q, int q_stride, void* out, int out_stride, const void* k_pages,
+                              const void* v_pages, const int* dec_tokens, const int* dec_seqs, int n_dec, const int* kv_len,
+                              const int* block_table, int bt_stride, const int* bt_rows, int NH, int NKV, int page_size,
+                              int page_shift, int pg_cap, int num_pages, float scale, int window, int n_splits,
+                              float* part_acc, float* part_ml, int* counters, int cluster_merge, int smem,
+                              cudaStream_t stream) {
+    if (int rc = acv_ensure_smem(decode_smem_config<D, NW>(), attn_decode_kernel<D, NW>, smem)) return rc;
+    dim3 grid(n_dec, NKV, n_splits);
+    acv_launch_cluster(PDL_ATTN, dim3(1, 1, cluster_merge ? n_splits : 1), attn_decode_kernel<D, NW>, grid, NW * 32, smem,
+        stream, (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
+        dec_seqs, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
+        n_splits, part_acc, part_ml, counters, cluster_merge);
+    return acv_launch_status();
 }
 
 template <int D>
@@ -505,16 +524,25 @@ static int launch_decode(const void* q, int q_stride, void* out, int out_stride,
     for (int b = 0; b < 31; ++b)
         if ((1 << b) == page_size) page_shift = b;
     if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
-    int pg_cap = 0;
-    int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, &pg_cap);
-    smem = decode_smem_spread<D>(smem, cluster_merge ? n_splits : 1, (long long)n_dec * NKV * n_splits);
-    if (int rc = acv_ensure_smem(decode_smem_config<D>(), attn_decode_kernel<D>, smem)) return rc;
-    dim3 grid(n_dec, NKV, n_splits);
-    acv_launch_cluster(PDL_ATTN, dim3(1, 1, cluster_merge ? n_splits : 1), attn_decode_kernel<D>, grid, AD_THREADS, smem, stream,
-        (const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)k_pages, (const bf16*)v_pages, dec_tokens,
-        dec_seqs, kv_len, block_table, bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window,
-        n_splits, part_acc, part_ml, counters, cluster_merge);
-    return acv_launch_status();
+    int pg_cap = 0, alone = 0;
+    const int cluster = cluster_merge ? n_splits : 1;
+#define AD_LAUNCH_ARGS q, q_stride, out, out_stride, k_pages, v_pages, dec_tokens, dec_seqs, n_dec, kv_len, block_table, \
+                       bt_stride, bt_rows, NH, NKV, page_size, page_shift, pg_cap, num_pages, scale, window, n_splits, \
+                       part_acc, part_ml, counters, cluster_merge
+    if (decode_grid_has_sms<D>(cluster, (long long)n_dec * NKV * n_splits, &alone)) {
+        int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS_ALONE, &pg_cap);
+        if (smem < alone) smem = alone;
+        int dev = 0, per_block = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&per_block, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev);
+        if (smem <= per_block) return launch_decode_with<D, AD_WARPS_ALONE>(AD_LAUNCH_ARGS, smem, stream);
+        // too many partial results beside eight rings: four warps, still one CTA to an SM
+        smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS, &pg_cap);
+        return launch_decode_with<D, AD_WARPS>(AD_LAUNCH_ARGS, smem < alone ? alone : smem, stream);
+    }
+    const int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS, &pg_cap);
+    return launch_decode_with<D, AD_WARPS>(AD_LAUNCH_ARGS, smem, stream);
+#undef AD_LAUNCH_ARGS
 }
 
 // bt_rows (may be null): the row of block_table that belongs to each request of the batch (null: row = its index).
@@ -551,19 +579,32 @@ ACV_API int acv_attention_decode(const void* q, int q_stride, void* out, int out
 }
 
 // How many CTAs of the split-KV kernel the device holds at once for these sizes (clusters that fit, times their size,
-// when the splits merge inside clusters): what the choice of the number of splits is made from.  Negative: an error.
+// when the splits merge inside clusters): what the choice of the number of splits is made from.  With ``alone``: how many
+// it holds one to an SM, which is the largest grid that runs with eight warps to a CTA (0: that form does not fit these
+// sizes).  Negative: an error.
 ACV_API int acv_attention_decode_resident(int NH, int NKV, int D, int page_size, int window, int n_splits, int max_kv,
-                                          int cluster_merge) {
+                                          int cluster_merge, int alone) {
     if (NKV <= 0 || NH % NKV || NH / NKV > 16 || n_splits < 1 || n_splits > 65535 || page_size <= 0) return ACV_ERR_SIZE;
+    if (D != 64 && D != 128) return ACV_ERR_SIZE;
     if (n_splits < 2 || n_splits > 8) cluster_merge = 0;
     int pg_cap = 0;
-    const int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, &pg_cap);
     const int cluster = cluster_merge ? n_splits : 1;
-    switch (D) {
-        case 64: return decode_resident<64>(smem, cluster);
-        case 128: return decode_resident<128>(smem, cluster);
-        default: return ACV_ERR_SIZE;
+    if (alone) {
+        int alone_bytes = 0, dev = 0, per_block = 0;
+        const bool any = D == 64 ? decode_grid_has_sms<64>(cluster, 1, &alone_bytes) : decode_grid_has_sms<128>(cluster, 1, &alone_bytes);
+        if (!any) return 0;
+        const int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS_ALONE, &pg_cap);
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&per_block, cudaDevAttrMaxSharedMemoryPerBlockOptin, dev) != cudaSuccess) {
+            cudaGetLastError();
+            return ACV_ERR_SIZE;
+        }
+        if (smem > per_block) return 0;
+        const int use = smem < alone_bytes ? alone_bytes : smem;
+        return D == 64 ? decode_resident<64, AD_WARPS_ALONE>(use, cluster) : decode_resident<128, AD_WARPS_ALONE>(use, cluster);
     }
+    const int smem = decode_smem_bytes(D, NH / NKV, page_size, window, n_splits, max_kv, cluster_merge, AD_WARPS, &pg_cap);
+    return D == 64 ? decode_resident<64, AD_WARPS>(smem, cluster) : decode_resident<128, AD_WARPS>(smem, cluster);
 }
 
 // ----------------------------------------------------------------------------- entry point without allocation

@@ -93,7 +93,7 @@ def _declare(lib: ctypes.CDLL) -> None:
     lib.acv_decode_layer.restype = c_int
     lib.acv_decode_layer_takes.argtypes = [I] * 8
     lib.acv_decode_layer_takes.restype = c_int
-    lib.acv_attention_decode_resident.argtypes = [I] * 8
+    lib.acv_attention_decode_resident.argtypes = [I] * 9
     lib.acv_attention_decode_resident.restype = c_int
     lib.acv_random_normal.argtypes = [P, LL, ctypes.c_ulonglong, F, F, P, P, I, P]
     lib.acv_random_normal.restype = c_int
@@ -580,40 +580,49 @@ def _decode_scratch(device, floats: int, ml_floats: int, counters: int):
 
 
 # What the choice of the number of splits reckons with: fitted to a sweep on a B200 over 1 to 64 requests, contexts of
-# 1024 to 65536 keys (8 kv-heads of 128, 4 query heads each, pages of 64) and every way of splitting below.  The reckoned
-# time is within a tenth of the measured one (root mean square); the splits chosen by it took 3 % more time over the
-# whole sweep than the best of each case (the rule before it, "CTAs for not quite twice the SMs": 9 %, and up to 60 %
-# where clusters of 8 did not fit the device at once).
-DECODE_KEY_US = 0.0099           # a CTA alone streams a key and its value in this time (its warps wait for their rings)
-DECODE_STREAM_BYTES_US = 6.4e6   # what all CTAs together stream from memory
-DECODE_BOUNDS_NORM = 5.5         # near both limits a round takes the p-norm of the two times, not the larger
-DECODE_MERGE_US = (6.1, 9.3, 0.35, 10.2, 0.79)  # start to end without splits; merged inside a cluster + per split;
+# 1024 to 65536 keys (8 kv-heads of 128, 4 query heads each, pages of 64; launches that overlap as in a step, pages
+# that no launch finds in L2) and every way of splitting below.  The reckoned time is within 11 % of the measured one
+# (root mean square); the splits chosen took 2.7 % more time over the whole sweep than the best of each case (the rule
+# before it, "CTAs for not quite twice the SMs": 9 %, and up to 60 % where clusters of 8 did not fit the device at once).
+DECODE_KEY_US = 0.0117           # a CTA alone streams a key and its value in this time (its warps wait for their rings)
+DECODE_KEY_US_ALONE = 0.00645    # the same where a CTA has an SM to itself and eight warps
+DECODE_STREAM_BYTES_US = 6.45e6  # what all CTAs together stream from memory
+DECODE_BOUNDS_NORM = 24.0        # a round takes the p-norm of the two times: with this p, the larger
+DECODE_MERGE_US = (6.6, 8.0, 0.45, 8.5, 0.81)   # start to end without splits; merged inside a cluster + per split;
                                                 # through scratch memory + per split
 DECODE_SPLIT_KEYS = 256          # no split shorter than this
 DECODE_CLUSTER_SPLITS = (2, 4, 6, 8)       # 3 and 5 were never better than their even neighbours by more than 2 %
 DECODE_SCRATCH_SPLITS = (2, 4, 8, 12, 16, 24, 32)
 DECODE_WIDE_CLUSTER_FIT = 0.85   # of the clusters of more than 6 CTAs that the runtime says fit at once, this part did
+# Inside a step the kernel's end is what the next kernel waits for, and there shorter CTAs won where the sweep saw a tie
+# (8 requests of 2100 keys: 4 splits 3.716 ms a step, 2 splits 3.743, none 3.821).  Among the ways that the reckoning
+# puts within this factor of the cheapest, the one with the most splits is taken if it merges in clusters and its CTAs
+# all fit the device at once.
+DECODE_MORE_SPLITS_WITHIN = 1.05
 
 
 @functools.lru_cache(maxsize=None)
 def decode_resident(num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, n_splits: int,
-                    pages_of_split: int, cluster_merge: bool) -> int:
+                    pages_of_split: int, cluster_merge: bool, alone: bool = False) -> int:
     """How many CTAs of the split-KV kernel the device holds at once (asked of the runtime: a cluster needs its CTAs
-    side by side in one part of the chip, and the partial results of 8 splits leave room for one CTA per SM only)."""
+    side by side in one part of the chip).  ``alone``: how many it holds one to an SM; a grid of no more CTAs runs with
+    eight warps to a CTA instead of four (0: that form does not fit these sizes)."""
     n = library().acv_attention_decode_resident(num_heads, num_kv_heads, head_dim, page_size, 0, n_splits,
-                                                pages_of_split * page_size * n_splits, 1 if cluster_merge else 0)
+                                                pages_of_split * page_size * n_splits, 1 if cluster_merge else 0,
+                                                1 if alone else 0)
     if n < 0:
         raise KernelError(f"attention_decode_resident: {_ERRORS.get(n, f'refused with code {n}')}")
-    return max(1, n)
+    return n if alone else max(1, n)
 
 
 def decode_splits_cost(n_dec: int, num_kv_heads: int, max_kv: int, n_splits: int, cluster_merge: bool, resident: int,
-                       row_bytes: int) -> float:
+                       row_bytes: int, resident_alone: int = 0) -> float:
     """Reckoned microseconds of the split-KV kernel: the CTAs run in rounds of ``resident``; a round takes as long as
-    one CTA needs for its keys alone, or as the memory needs for the round's bytes; then the merge."""
+    one CTA needs for its keys alone, or as the memory needs for the round's bytes; then the merge.  A grid of up to
+    ``resident_alone`` CTAs has an SM for each, eight warps to a CTA, and streams faster."""
     ctas = n_dec * num_kv_heads * n_splits
     keys = -(-max_kv // n_splits)
-    alone = keys * DECODE_KEY_US
+    alone = keys * (DECODE_KEY_US_ALONE if ctas <= resident_alone else DECODE_KEY_US)
     p = DECODE_BOUNDS_NORM
     round_us = lambda n: (alone ** p + (n * keys * row_bytes / DECODE_STREAM_BYTES_US) ** p) ** (1.0 / p)
     full, rest = divmod(ctas, resident)
@@ -625,16 +634,11 @@ def decode_splits_cost(n_dec: int, num_kv_heads: int, max_kv: int, n_splits: int
     return us + DECODE_MERGE_US[3] + DECODE_MERGE_US[4] * n_splits
 
 
-@functools.lru_cache(maxsize=4096)
-def decode_plan(n_dec: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_kv: int,
-                window: int = 0) -> tuple[int, bool]:
-    """(splits of the context, merged inside clusters?) for ``n_dec`` one-token requests with up to ``max_kv`` keys:
-    the cheapest by ``decode_splits_cost`` among no split, up to 8 splits merged inside a cluster and up to 32 merged
-    through scratch memory.  A split more pays while it shortens what a CTA streams alone; it stops paying when the
-    CTAs no longer fit the device at once or the memory is the limit anyway."""
-    keys = min(max_kv, window) if window > 0 else max_kv
+def decode_ways(n_dec: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, keys: int) -> list:
+    """Every way of splitting ``keys`` keys of ``n_dec`` requests that the plan chooses from, as (reckoned microseconds,
+    splits, merged inside clusters?, all CTAs fit the device at once?)."""
     row_bytes = 2 * head_dim * 2                       # a key and a value of one kv-head in bfloat16
-    best = None
+    ways = []
     for n_splits, cluster in [(1, False)] + [(s, True) for s in DECODE_CLUSTER_SPLITS] + \
                              [(s, False) for s in DECODE_SCRATCH_SPLITS]:
         if n_splits > 1 and keys < n_splits * DECODE_SPLIT_KEYS:
@@ -642,13 +646,30 @@ def decode_plan(n_dec: int, num_heads: int, num_kv_heads: int, head_dim: int, pa
         if n_dec * num_kv_heads * n_splits > 65535 * 4:
             continue
         pages = -(-(-(-keys // n_splits)) // page_size)
-        resident = decode_resident(num_heads, num_kv_heads, head_dim, page_size, n_splits,
-                                   1 << max(0, pages - 1).bit_length(), cluster)
+        pages = 1 << max(0, pages - 1).bit_length()
+        resident = decode_resident(num_heads, num_kv_heads, head_dim, page_size, n_splits, pages, cluster)
+        alone = decode_resident(num_heads, num_kv_heads, head_dim, page_size, n_splits, pages, cluster, True)
         if cluster and n_splits > 6:
             resident = max(n_splits, int(resident * DECODE_WIDE_CLUSTER_FIT))
-        cost = decode_splits_cost(n_dec, num_kv_heads, keys, n_splits, cluster, resident, row_bytes)
-        if best is None or cost < best[0]:
-            best = (cost, n_splits, cluster)
+            alone = min(alone, resident)
+        resident = max(resident, alone)
+        cost = decode_splits_cost(n_dec, num_kv_heads, keys, n_splits, cluster, resident, row_bytes, alone)
+        ways.append((cost, n_splits, cluster, n_dec * num_kv_heads * n_splits <= resident))
+    return ways
+
+
+@functools.lru_cache(maxsize=4096)
+def decode_plan(n_dec: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, max_kv: int,
+                window: int = 0) -> tuple[int, bool]:
+    """(splits of the context, merged inside clusters?) for ``n_dec`` one-token requests with up to ``max_kv`` keys:
+    by ``decode_splits_cost`` among no split, up to 8 splits merged inside a cluster and up to 32 merged through
+    scratch memory.  A split more pays while it shortens what a CTA streams alone; it stops paying when the CTAs no
+    longer fit the device at once or the memory is the limit anyway."""
+    keys = min(max_kv, window) if window > 0 else max_kv
+    ways = decode_ways(n_dec, num_heads, num_kv_heads, head_dim, page_size, keys)
+    cheapest = min(ways)
+    near = [w for w in ways if w is cheapest or (w[0] <= DECODE_MORE_SPLITS_WITHIN * cheapest[0] and w[2] and w[3])]
+    best = max(near, key=lambda w: w[1])
     return best[1], best[2]
 
 

@@ -50,7 +50,8 @@ def attention_case(batch: int, q_len: int, context: int, reps: int, legacy: bool
     NH, NKV, D = 32, 8, 128
     pages_per = (context + page - 1) // page
     n_pages = batch * pages_per
-    sets = 3       # rotate over three pools so that a launch finds nothing of its pages in L2
+    # rotate over so many pools that a launch finds nothing of its pages in L2 (126 MB): 600 MB in all, three at least
+    sets = max(3, -(-600_000_000 // (2 * n_pages * NKV * page * D * 2)))
     pools = [(torch.randn(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16),
               torch.randn(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)) for _ in range(sets)]
     table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(batch, pages_per)
@@ -90,8 +91,9 @@ def decode_split_case(reps: int) -> dict:
     for batch, context in ((1, 8192), (2, 8192), (4, 8192), (4, 16384), (8, 2048), (8, 8192), (12, 8192), (32, 8192), (1, 65536)):
         pages_per = context // page
         n_pages = batch * pages_per
+        sets = max(3, -(-600_000_000 // (2 * n_pages * NKV * page * D * 2)))       # 600 MB in all: nothing is found in L2
         pools = [(torch.randn(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16),
-                  torch.randn(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)) for _ in range(3)]
+                  torch.randn(n_pages, NKV, page, D, device="cuda", dtype=torch.bfloat16)) for _ in range(sets)]
         table = torch.randperm(n_pages, device="cuda").to(torch.int32).view(batch, pages_per)
         qkv = torch.randn(batch, (NH + 2 * NKV) * D, device="cuda", dtype=torch.bfloat16)
         o = torch.empty(batch, NH * D, device="cuda", dtype=torch.bfloat16)
@@ -99,18 +101,10 @@ def decode_split_case(reps: int) -> dict:
         rows = torch.arange(batch, dtype=torch.int32, device="cuda")
         chosen = ops.decode_plan(batch, NH, NKV, D, page, context)
         cells = []
-        for n_splits, cluster in [(1, False)] + [(s, True) for s in ops.DECODE_CLUSTER_SPLITS] + \
-                                 [(s, False) for s in ops.DECODE_SCRATCH_SPLITS]:
-            if context < n_splits * ops.DECODE_SPLIT_KEYS:
-                continue
-            fn = lambda i: ops.attention_decode(qkv, o, *pools[i % 3], rows, rows, batch, kv_len, table, NH, NKV, D,
+        for reckoned, n_splits, cluster, _ in ops.decode_ways(batch, NH, NKV, D, page, context):
+            fn = lambda i: ops.attention_decode(qkv, o, *pools[i % sets], rows, rows, batch, kv_len, table, NH, NKV, D,
                                                 D ** -0.5, 0, n_splits, context, cluster_merge=cluster)
-            us = min(_time(fn, reps), _time(fn, reps))
-            pages = -(-(-(-context // n_splits)) // page)
-            fit = ops.decode_resident(NH, NKV, D, page, n_splits, 1 << max(0, pages - 1).bit_length(), cluster)
-            if cluster and n_splits > 6:
-                fit = max(n_splits, int(fit * ops.DECODE_WIDE_CLUSTER_FIT))
-            reckoned = ops.decode_splits_cost(batch, NKV, context, n_splits, cluster, fit, 2 * D * 2)
+            us = min(_time(fn, max(reps, sets)), _time(fn, max(reps, sets)))
             name = f"{n_splits}{'c' if cluster else 's' if n_splits > 1 else ''}"
             out[f"b{batch} c{context} {name}"] = us
             cells.append(f"{name}{'*' if (n_splits, cluster) == chosen else ''} {us:.0f}/{reckoned:.0f}")

@@ -236,7 +236,9 @@ def test_the_splits_of_decode_attention_follow_what_fits_the_device(monkeypatch)
     from acvram_b200.kernels import ops
     fits = {}
 
-    def resident(num_heads, num_kv_heads, head_dim, page_size, n_splits, pages_of_split, cluster_merge):
+    def resident(num_heads, num_kv_heads, head_dim, page_size, n_splits, pages_of_split, cluster_merge, alone=False):
+        if alone:       # one CTA to an SM, 148 SMs: whole clusters only
+            return {1: 148, 2: 148, 4: 132, 6: 132, 8: 120}[n_splits if cluster_merge else 1]
         return fits.get((n_splits, cluster_merge), 296)
     monkeypatch.setattr(ops, "decode_resident", resident)
     plan = lambda n_dec, max_kv: ops.decode_plan.__wrapped__(n_dec, 32, 8, 128, 64, max_kv)

@@ -387,14 +387,14 @@ def test_decode_attention_merge_inside_clusters(ops, n_splits):
 
 
 def test_decode_attention_long_context_chooses_many_splits(ops):
-    """About 20 000 keys: the split count that serving computes is above 8, the merge goes through scratch memory
+    """About 60 000 keys: the split count that serving computes is above 8, the merge goes through scratch memory
     and block-table entries beyond the part cached in shared memory are read; one far key at a split's edge carries
     the answer for request 0."""
-    lens = [20000, 517]
+    lens = [60000, 517]
     n, in_clusters = ops.decode_plan(len(lens), 8, 2, 128, 16, max(lens))
     assert n > 8 and not in_clusters
     per = -(-max(lens) // n)
-    for j in (per - 1, per, 5 * per, 19999, 0):
+    for j in (per - 1, per, 5 * per, 59999, 0):
         o1, o2, splits = _decode_direct(ops, 8, 2, 128, 16, lens, None, cluster_merge=True, seed=85 + j % 7, spike=(0, j))
         assert splits == n
         torch.testing.assert_close(o1, o2, **tol(torch.bfloat16))
