@@ -58,17 +58,32 @@ __device__ __forceinline__ bf16 swiglu_pair(float gate, float up) {
     return __float2bfloat16_rn(s * u);
 }
 
+// Swapped roles: features lie on lanes, an even lane holds the gate of 16 tokens and the next lane their up.  The two
+// share the work: each sends the other the eight values that it does not need, the even lane makes the tokens 0..7,
+// the odd lane the tokens 8..15 (all exchanges first, then the arithmetic, so that the eight chains run side by
+// side: done token by token, with the odd lane idle, this took 75 ns a token).  Returns the first of this lane's tokens.
+__device__ __forceinline__ int swiglu_lane_pair(const float (&v)[16], int lane, bf16 (&o)[8]) {
+    const bool odd = lane & 1;
+    float other[8];
+#pragma unroll
+    for (int c = 0; c < 8; ++c) other[c] = __shfl_xor_sync(0xffffffffu, odd ? v[c] : v[c + 8], 1);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) o[c] = swiglu_pair(odd ? other[c] : v[c], odd ? v[c + 8] : other[c]);
+    return odd ? 8 : 0;
+}
+
 // Write 16 accumulator columns of one tensor-memory lane: row_a is the A-operand row the lane holds,
 // col0 the B-operand row of v[0].  Executed by whole warps (the paired form shuffles between lanes).
 __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int col0, const float (&v)[16], int lane) {
     if (p.act) {
         if (p.swap) {       // features lie on lanes: an even lane holds a gate, the next lane its up
+            bf16 o[8];
+            const int first = swiglu_lane_pair(v, lane, o);
+            const int f = row_a & ~1;           // the pair's gate row
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-                const float up = __shfl_down_sync(0xffffffffu, v[c], 1);
-                const int m = col0 + c;
-                if (!(lane & 1) && row_a + 1 < p.N && m < p.M)
-                    ((bf16*)p.C)[(size_t)m * p.ldc + (row_a >> 1)] = swiglu_pair(v[c], up);
+            for (int c = 0; c < 8; ++c) {
+                const int m = col0 + first + c;
+                if (f + 1 < p.N && m < p.M) ((bf16*)p.C)[(size_t)m * p.ldc + (f >> 1)] = o[c];
             }
         } else if (row_a < p.M) {   // features lie on columns: (v[0], v[1]), (v[2], v[3]) ...
             bf16* dst = (bf16*)p.C + (size_t)row_a * p.ldc + (col0 >> 1);
@@ -127,11 +142,10 @@ __device__ __forceinline__ void gt_store16(const GemmParams& p, int row_a, int c
 // gt_stage16: 16 tokens (col0 ..) of the feature this lane holds (f = 0..127 within the tile).
 __device__ __forceinline__ void gt_stage16(const GemmParams& p, unsigned char* stage, int f, int col0, const float (&v)[16], int lane) {
     if (p.act) {            // an even lane holds a gate, the next lane its up: 64 output features per tile
+        bf16 o[8];
+        const int first = swiglu_lane_pair(v, lane, o);
 #pragma unroll
-        for (int c = 0; c < 16; ++c) {
-            const float up = __shfl_down_sync(0xffffffffu, v[c], 1);
-            if (!(lane & 1)) reinterpret_cast<bf16*>(stage)[(col0 + c) * 64 + (f >> 1)] = swiglu_pair(v[c], up);
-        }
+        for (int c = 0; c < 8; ++c) reinterpret_cast<bf16*>(stage)[(col0 + first + c) * 64 + (f >> 1)] = o[c];
     } else if (p.out_f32) {
 #pragma unroll
         for (int c = 0; c < 16; ++c) reinterpret_cast<float*>(stage)[(col0 + c) * 128 + f] = v[c];
