@@ -283,6 +283,7 @@ struct AcvTlScope {
 #define TL_M_CLUSTER_MET 4     // ... and the cluster's CTAs have met
 #define TL_M_STORED 5          // the CTA's results are written
 #define TL_M_WAIT_OVER 6       // the producer's wait for the predecessor has ended
+#define TL_M_STAGED 7          // split K in a cluster, rank 0: the summed tile lies in shared memory, its way out begins
 // sums of nanoseconds (tokens on rows, no split of K, where marks 3 and 4 are free)
 #define TL_M_SUM_STAGE_WAIT 3  // the issuing thread waited for operand stages
 #define TL_M_SUM_ACC_WAIT 4    // the issuing thread waited for an accumulator buffer

@@ -199,7 +199,9 @@ __device__ __forceinline__ void gt_flush_qkv(const GemmParams& p, const unsigned
     for (int e = 0; e < 8; ++e) wv[e] = (w && in_n) ? w[off + e] : 1.f;
     const int i0 = off & ((D >> 1) - 1);                    // index of the first angle
     const bool first_half = off < (D >> 1);
-    for (int q = et; q < ((bn * 16 + 127) & ~127); q += 128) {     // every thread takes every turn: the shuffles need all lanes
+    // a turn is eight rows; every thread takes every turn that has a token (the shuffles need all lanes), none takes the
+    // turns beyond the tokens: with 8 requests in a tile of 16 that is one turn of this chain of shuffles instead of two
+    for (int q = et; q < ((rows * 16 + 127) & ~127); q += 128) {
         const int r = q >> 4;
         const bool live = r < rows && in_n;
         float a[8];

@@ -497,6 +497,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 else gt_store16(p, row_a, tb * BN + c0, sum, lane);
             }
             if (p.staged) {
+                if (threadIdx.x == 64) ACV_TL_MARK(TL_M_STAGED);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (p.qkv) gt_flush_qkv(p, tiles, aux, ta, tb, BN, threadIdx.x - 64);
                 else gt_flush(p, tiles, ta, tb, BN, threadIdx.x - 64);

@@ -27,7 +27,7 @@ RECORD = np.dtype([("t0", "<u8"), ("t1", "<u8"), ("kernel", "<i4"), ("block", "<
 FILES = ("gemm_tc", "elementwise", "sampling", "attention_decode", "attention_tc", "qk_rope_append")
 NAMES = {1: "gemm", 2: "norm", 3: "rope_append", 4: "attn_decode", 5: "attn_prompt", 6: "attn_chunk", 7: "embed",
          8: "argmax", 9: "swiglu"}
-MARK_NAMES = {1: ("first_full", "last_mma", "acc_done", "part_sent", "cluster_met", "stored", "wait_over"),
+MARK_NAMES = {1: ("first_full", "last_mma", "acc_done", "part_sent", "cluster_met", "stored", "wait_over", "staged"),
               4: ("loop_done",)}
 # the prompt attention's marks are not times but sums: nanoseconds its first softmax warp spent in each phase
 # (marks 0..4) and the number of half tiles of 64 keys it went through (mark 7)
